@@ -1,0 +1,258 @@
+// Prefill kernels: many tokens of one sequence at a time. Row-wise norms,
+// the int8-weight GEMM on CUDA cores (fp32 FMA), q/k norm + RoPE + cache fill,
+// causal / sliding-window attention over the prompt, GeGLU.
+#pragma once
+#include "tg_common.cuh"
+
+namespace tg {
+
+// ops::embedding_prefill, reference ops.hpp:529-571
+__global__ void embed_prefill_kernel(const int8_t *wte, const float *scales, const int *ids, float *h, int S, int D,
+                                     int V, float sqrtD, int *err_flag) {
+	int s = blockIdx.x;
+	int tok = ids[s];
+	if (tok < 0 || tok >= V) {
+		if (threadIdx.x == 0) *err_flag = 1;
+		tok = 0;
+	}
+	const int8_t *row = wte + size_t(tok) * D;
+	for (int d = threadIdx.x; d < D; d += blockDim.x) h[size_t(s) * D + d] = scales[d] * (sqrtD * float(row[d]));
+}
+
+// out[s,:] = (res ? res[s,:] : 0) + rmsnorm(in[s,:]; w). One CTA of 256 threads
+// per row. ops::rmsnorm (+ ops::add), reference ops.hpp:126-222, 84-103.
+// `out` may alias `res` or `in`.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *out, const float *in, const float *w, const float *res,
+                                                            int dim) {
+	__shared__ float bred[8];
+	const size_t off = size_t(blockIdx.x) * dim;
+	float ss = 0.0f;
+	for (int d = threadIdx.x; d < dim; d += 256) {
+		float v = in[off + d];
+		ss = fmaf(v, v, ss);
+	}
+	ss = block_sum<8>(ss, bred);
+	const float r = inv_rms(ss, dim);
+	for (int d = threadIdx.x; d < dim; d += 256) {
+		float y = (in[off + d] * r) * (w[d] + 1.0f);
+		out[off + d] = res ? (res[off + d] + y) : y;
+	}
+}
+
+// ---------------------------------------------------------------- GEMM (CUDA cores)
+// C[M,N] = scale[n] * sum_k A[m,k] * W[k,n]   (gemm::qgemmnn, reference linalg.hpp:210-308)
+// 64x128 output tile per CTA, K stepped by 32; W converted int8->fp32 once per
+// tile on its way into shared memory; each of 256 threads owns a 4x8 block.
+// Optional split along K (grid.z) with partials summed by a second kernel.
+constexpr int GM_BM = 64, GM_BN = 128, GM_BK = 32;
+
+__global__ void __launch_bounds__(256) qgemm_simt_kernel(float *C, const float *A, const int8_t *W, const float *scales,
+                                                         int M, int K, int N, int kc, float *partial) {
+	__shared__ __align__(16) float As[GM_BK][GM_BM + 4];
+	__shared__ __align__(16) float Ws[GM_BK][GM_BN];
+	const int tid = threadIdx.x;
+	const int n0 = blockIdx.x * GM_BN, m0 = blockIdx.y * GM_BM;
+	const int kbeg = blockIdx.z * kc, kend = min(K, kbeg + kc);
+	const int ty = tid >> 4, tx = tid & 15;  // 16 x 16 threads: rows 4*ty.., cols 8*tx..
+	float acc[4][8];
+#pragma unroll
+	for (int i = 0; i < 4; i++)
+#pragma unroll
+		for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+	for (int kk = kbeg; kk < kend; kk += GM_BK) {
+		// A tile: 64 rows x 32 k -> As[k][m]; thread loads 8 floats (2 float4)
+#pragma unroll
+		for (int r = 0; r < 2; r++) {
+			int idx = tid + r * 256;        // 0..511 float4 slots
+			int m = idx >> 3, k4 = idx & 7;  // 64 rows x 8 float4
+			float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+			if (m0 + m < M) v = *reinterpret_cast<const float4 *>(A + size_t(m0 + m) * K + kk + 4 * k4);
+			As[4 * k4 + 0][m] = v.x;
+			As[4 * k4 + 1][m] = v.y;
+			As[4 * k4 + 2][m] = v.z;
+			As[4 * k4 + 3][m] = v.w;
+		}
+		// W tile: 32 k x 128 cols int8 = 256 int4 -> one per thread
+		{
+			int k = tid >> 3, c16 = tid & 7;
+			int4 v = ld_stream_int4(W + size_t(kk + k) * N + n0 + 16 * c16);
+			const uint32_t words[4] = {uint32_t(v.x), uint32_t(v.y), uint32_t(v.z), uint32_t(v.w)};
+#pragma unroll
+			for (int j = 0; j < 4; j++) {
+				float f[4];
+				i8x4_to_f32(words[j], f);
+				*reinterpret_cast<float4 *>(&Ws[k][16 * c16 + 4 * j]) = make_float4(f[0], f[1], f[2], f[3]);
+			}
+		}
+		__syncthreads();
+#pragma unroll
+		for (int k = 0; k < GM_BK; k++) {
+			float4 a4 = *reinterpret_cast<const float4 *>(&As[k][4 * ty]);
+			float4 w0 = *reinterpret_cast<const float4 *>(&Ws[k][8 * tx]);
+			float4 w1 = *reinterpret_cast<const float4 *>(&Ws[k][8 * tx + 4]);
+			const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+			const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+			for (int i = 0; i < 4; i++)
+#pragma unroll
+				for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int i = 0; i < 4; i++) {
+		int m = m0 + 4 * ty + i;
+		if (m >= M) continue;
+		if (gridDim.z == 1) {
+#pragma unroll
+			for (int j = 0; j < 8; j++) C[size_t(m) * N + n0 + 8 * tx + j] = acc[i][j] * scales[n0 + 8 * tx + j];
+		} else {
+			float *p = partial + (size_t(blockIdx.z) * M + m) * N + n0 + 8 * tx;
+#pragma unroll
+			for (int j = 0; j < 8; j++) p[j] = acc[i][j];
+		}
+	}
+}
+
+__global__ void qgemm_splitk_reduce_kernel(float *C, const float *partial, const float *scales, int M, int N, int nsplit) {
+	size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= size_t(M) * N) return;
+	float s = 0.0f;
+	for (int sp = 0; sp < nsplit; sp++) s += partial[size_t(sp) * M * N + i];
+	C[i] = s * scales[i % N];
+}
+
+// ops::gelu (LUT) + ops::mul, reference ops.hpp:62-123: gate = lut(gate) * up
+__global__ void geglu_kernel(float *gate, const float *up, size_t n, GeluLut lut) {
+	size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i < n) gate[i] = lut(gate[i]) * up[i];
+}
+
+// q/k per-head RMSNorm + RoPE at position s (offset 0) in place on
+// q [S][4*256] and k [S][256], and KVCache::update_prefill (reference
+// decode.hpp:72-105): the last min(S, slots) prompt positions go to cache
+// slots 0.. in order. One CTA (5 warps + 1) per prompt position.
+__global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, float *k, const float *v, const float *rmsq,
+                                                                    const float *rmsk, const float *cosT,
+                                                                    const float *sinT, float *kcache, float *vcache,
+                                                                    int S, int slots) {
+	const int s = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const float *cosr = cosT + size_t(s) * 256, *sinr = sinT + size_t(s) * 256;
+	const int start = (S >= slots) ? (S - slots) : 0;
+	const int c = s - start;  // cache slot, if >= 0
+	auto norm_rope = [&](float *x, const float *w) {
+		float lo[4], hi[4];
+		float ss = 0.0f;
+#pragma unroll
+		for (int i = 0; i < 4; i++) {
+			lo[i] = x[4 * lane + i];
+			hi[i] = x[128 + 4 * lane + i];
+			ss = fmaf(lo[i], lo[i], ss);
+			ss = fmaf(hi[i], hi[i], ss);
+		}
+		ss = warp_sum(ss);
+		const float r = inv_rms(ss, 256);
+#pragma unroll
+		for (int i = 0; i < 4; i++) {
+			const int d = 4 * lane + i;
+			float a = (lo[i] * r) * (w[d] + 1.0f);
+			float b = (hi[i] * r) * (w[d + 128] + 1.0f);
+			x[d] = fmaf(-1.0f * b, sinr[d], cosr[d] * a);
+			x[d + 128] = fmaf(a, sinr[d + 128], cosr[d + 128] * b);
+		}
+	};
+	if (warp < 4) {
+		norm_rope(q + size_t(s) * 1024 + warp * 256, rmsq);
+	} else if (warp == 4) {
+		float *kr = k + size_t(s) * 256;
+		norm_rope(kr, rmsk);
+		__syncwarp();
+		if (c >= 0)
+			for (int d = lane; d < 256; d += 32) kcache[size_t(c) * 256 + d] = kr[d];
+	} else {
+		if (c >= 0)
+			for (int d = lane; d < 256; d += 32) vcache[size_t(c) * 256 + d] = v[size_t(s) * 256 + d];
+	}
+}
+
+// ops::attention_prefill, reference ops.hpp:377-526: causal; on sliding-window
+// layers query s sees keys max(0, s - window) .. s (window + 1 keys, :437-443).
+// q,o [S][4][256], k,v [S][256] (the prompt's own activations, not the cache).
+// One warp per query position handles the 4 heads that share the KV head;
+// 8 warps per CTA take 8 consecutive queries so their key ranges overlap in L1/L2.
+__global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float *q, const float *k, const float *v, int S,
+                                                           int is_local, int window) {
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int s = blockIdx.x * 8 + warp;
+	if (s >= S) return;
+	float4 q0[4], q1[4], o0[4], o1[4];
+	float m[4], l[4];
+#pragma unroll
+	for (int h = 0; h < 4; h++) {
+		const float *qr = q + size_t(s) * 1024 + h * 256;
+		q0[h] = *reinterpret_cast<const float4 *>(qr + 4 * lane);
+		q1[h] = *reinterpret_cast<const float4 *>(qr + 128 + 4 * lane);
+		// reference multiplies the score by 1/16 after the dot product (ops.hpp:463); scaling q
+		// by the same power of two first is exact
+		q0[h].x *= 0.0625f; q0[h].y *= 0.0625f; q0[h].z *= 0.0625f; q0[h].w *= 0.0625f;
+		q1[h].x *= 0.0625f; q1[h].y *= 0.0625f; q1[h].z *= 0.0625f; q1[h].w *= 0.0625f;
+		o0[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+		o1[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+		m[h] = -INFINITY;
+		l[h] = 0.0f;
+	}
+	int j0 = 0;
+	if (is_local) j0 = (s >= window) ? s - window : 0;
+	for (int j = j0; j <= s; j++) {
+		const float *kr = k + size_t(j) * 256, *vr = v + size_t(j) * 256;
+		float4 k0v = *reinterpret_cast<const float4 *>(kr + 4 * lane);
+		float4 k1v = *reinterpret_cast<const float4 *>(kr + 128 + 4 * lane);
+		float4 v0v = *reinterpret_cast<const float4 *>(vr + 4 * lane);
+		float4 v1v = *reinterpret_cast<const float4 *>(vr + 128 + 4 * lane);
+		float sc[4];
+#pragma unroll
+		for (int h = 0; h < 4; h++) {
+			float t = q0[h].x * k0v.x;
+			t = fmaf(q0[h].y, k0v.y, t);
+			t = fmaf(q0[h].z, k0v.z, t);
+			t = fmaf(q0[h].w, k0v.w, t);
+			t = fmaf(q1[h].x, k1v.x, t);
+			t = fmaf(q1[h].y, k1v.y, t);
+			t = fmaf(q1[h].z, k1v.z, t);
+			t = fmaf(q1[h].w, k1v.w, t);
+			sc[h] = t;
+		}
+#pragma unroll
+		for (int of = 16; of > 0; of >>= 1) {
+#pragma unroll
+			for (int h = 0; h < 4; h++) sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], of);
+		}
+#pragma unroll
+		for (int h = 0; h < 4; h++) {
+			float mn = fmaxf(m[h], sc[h]);
+			float corr = expf(m[h] - mn);
+			float p = expf(sc[h] - mn);
+			l[h] = fmaf(l[h], corr, p);
+			o0[h].x = fmaf(p, v0v.x, o0[h].x * corr);
+			o0[h].y = fmaf(p, v0v.y, o0[h].y * corr);
+			o0[h].z = fmaf(p, v0v.z, o0[h].z * corr);
+			o0[h].w = fmaf(p, v0v.w, o0[h].w * corr);
+			o1[h].x = fmaf(p, v1v.x, o1[h].x * corr);
+			o1[h].y = fmaf(p, v1v.y, o1[h].y * corr);
+			o1[h].z = fmaf(p, v1v.z, o1[h].z * corr);
+			o1[h].w = fmaf(p, v1v.w, o1[h].w * corr);
+			m[h] = mn;
+		}
+	}
+#pragma unroll
+	for (int h = 0; h < 4; h++) {
+		const float inv = 1.0f / l[h];
+		float *orow = o + size_t(s) * 1024 + h * 256;
+		*reinterpret_cast<float4 *>(orow + 4 * lane) = make_float4(o0[h].x * inv, o0[h].y * inv, o0[h].z * inv, o0[h].w * inv);
+		*reinterpret_cast<float4 *>(orow + 128 + 4 * lane) =
+		    make_float4(o1[h].x * inv, o1[h].y * inv, o1[h].z * inv, o1[h].w * inv);
+	}
+}
+
+}  // namespace tg

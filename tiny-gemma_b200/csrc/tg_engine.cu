@@ -1,0 +1,1378 @@
+// libtinygemma_b200: host-side engine and the extern "C" boundary declared in
+// include/tiny_gemma_b200.h. Owns the device weight store (gemma_i8.bin bytes
+// unchanged in HBM), the per-state KV caches and scratch, the launch plans and
+// the CUDA graph of one decode step.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/tiny_gemma_b200.h"
+#include "kernels_decode.cuh"
+#include "kernels_prefill.cuh"
+#include "kernels_sampler.cuh"
+
+using namespace tg;
+
+// ===================================================================== errors
+namespace {
+
+thread_local std::string g_err;
+std::atomic<long long> g_launches{0};
+
+int fail(int code, const std::string &msg) {
+	g_err = msg;
+	return code;
+}
+
+#define TG_CUDA(call)                                                                                   \
+	do {                                                                                                \
+		cudaError_t e__ = (call);                                                                       \
+		if (e__ != cudaSuccess)                                                                         \
+			return fail(TG_ECUDA, std::string(#call) + ": " + cudaGetErrorString(e__));                 \
+	} while (0)
+
+#define TG_TRY(call)                \
+	do {                            \
+		int rc__ = (call);          \
+		if (rc__ != TG_OK) return rc__; \
+	} while (0)
+
+inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int check_launch(const char *what) {
+	cudaError_t e = cudaGetLastError();
+	if (e != cudaSuccess) return fail(TG_ECUDA, std::string(what) + " launch: " + cudaGetErrorString(e));
+	return TG_OK;
+}
+
+// tunables (set through the environment for experiments; defaults are the tuned values)
+int env_int(const char *name, int dflt) {
+	const char *v = std::getenv(name);
+	return v ? std::atoi(v) : dflt;
+}
+
+int g_num_sms = 148;
+
+}  // namespace
+
+// ===================================================================== model
+struct QW {
+	const int8_t *q = nullptr;
+	const float *s = nullptr;
+	int K = 0, N = 0;
+};
+
+struct LayerW {
+	QW Q, K, V, O, U, G, Dn;
+	const float *rmsq, *rmsk, *attn_pre, *attn_post, *mlp_pre, *mlp_post;
+	bool is_local;
+};
+
+struct tg_model {
+	tg_config cfg;
+	int device = 0;
+	uint8_t *blob = nullptr;
+	size_t nbytes = 0;
+	const int8_t *wte = nullptr;
+	const float *wte_s = nullptr, *final_norm = nullptr;
+	std::vector<LayerW> layers;
+	QW lm_head;
+	float *rope[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};  // [is_local][cos,sin]
+	int rope_npos[2] = {0, 0};
+	float *gelu = nullptr;
+	float gelu_min = -4.0f, gelu_max = 4.0f, gelu_eps = 0.0f;
+	int gelu_size = 0;
+	bool loaded = false;
+};
+
+namespace {
+
+size_t model_file_bytes(const tg_config &c) {
+	size_t qd = size_t(c.n_head) * c.head_dim, kd = size_t(c.n_kv) * c.head_dim;
+	size_t D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
+	size_t per_layer = (D * qd + 4 * qd) + 2 * (D * kd + 4 * kd) + (qd * D + 4 * D) + 2 * 4 * size_t(c.head_dim) +
+	                   2 * 4 * D + 2 * (D * I + 4 * I) + (I * D + 4 * D) + 2 * 4 * D;
+	return V * D + 4 * D + 4 * D + size_t(c.n_layers) * per_layer + D * V + 4 * V;
+}
+
+// transformer.hpp:99-165 read order; pointers into the device blob
+void bind_model(tg_model *m) {
+	const tg_config &c = m->cfg;
+	const uint8_t *p = m->blob;
+	auto take = [&](size_t n) {
+		const uint8_t *r = p;
+		p += n;
+		return r;
+	};
+	auto takeq = [&](int K, int N) {
+		QW w;
+		w.K = K;
+		w.N = N;
+		w.q = reinterpret_cast<const int8_t *>(take(size_t(K) * N));
+		w.s = reinterpret_cast<const float *>(take(4 * size_t(N)));
+		return w;
+	};
+	auto takef = [&](int n) { return reinterpret_cast<const float *>(take(4 * size_t(n))); };
+	const int D = c.hidden_size, I = c.intermediate_size, qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	m->wte = reinterpret_cast<const int8_t *>(take(size_t(c.n_vocab) * D));
+	m->wte_s = takef(D);
+	m->final_norm = takef(D);
+	m->layers.resize(c.n_layers);
+	for (int l = 0; l < c.n_layers; l++) {
+		LayerW &w = m->layers[l];
+		w.Q = takeq(D, qd);
+		w.K = takeq(D, kd);
+		w.V = takeq(D, kd);
+		w.O = takeq(qd, D);
+		w.rmsq = takef(c.head_dim);
+		w.rmsk = takef(c.head_dim);
+		w.attn_pre = takef(D);
+		w.attn_post = takef(D);
+		w.U = takeq(D, I);
+		w.G = takeq(D, I);
+		w.Dn = takeq(I, D);
+		w.mlp_pre = takef(D);
+		w.mlp_post = takef(D);
+		w.is_local = (l % c.window_pattern) != (c.window_pattern - 1);  // transformer.hpp:43
+	}
+	m->lm_head = takeq(D, c.n_vocab);
+}
+
+bool supported_k(int K) { return K == 640 || K == 2048 || K == 1024 || K == 256 || K == 1152 || K == 6912; }
+bool supported_n(int N) {
+	return N == 640 || N == 262144 || N == 2048 || N == 256 || N == 1024 || N == 1152 || N == 6912;
+}
+
+int ensure_device(int device) {
+	int n = 0;
+	cudaError_t e = cudaGetDeviceCount(&n);
+	if (e != cudaSuccess || n == 0) {
+		cudaGetLastError();
+		return fail(TG_ENODEVICE, "no CUDA device available (this library has no CPU path)");
+	}
+	if (device < 0 || device >= n) return fail(TG_EINVAL, "device index out of range");
+	TG_CUDA(cudaSetDevice(device));
+	int sms = 0;
+	if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && sms > 0) g_num_sms = sms;
+	return TG_OK;
+}
+
+// ------------------------------------------------------------- matvec planning
+struct MvPlan {
+	int nsplit, kc, grid_x;
+};
+
+// Pick the K-split so that the launch fills the GPU in whole waves. kc must be a
+// multiple of 32 rows and divide K.
+MvPlan plan_matvec(int K, int ntiles, int target_ctas) {
+	MvPlan best{1, K, ntiles};
+	if (ntiles >= target_ctas) return best;
+	double best_score = -1e9;
+	const int units = K / 32;
+	for (int ns = 1; ns <= units; ns++) {
+		if (units % ns) continue;
+		int ctas = ntiles * ns;
+		int waves = (ctas + g_num_sms - 1) / g_num_sms;
+		double eff = double(ctas) / (double(waves) * g_num_sms);
+		double fill = std::min(1.0, double(ctas) / target_ctas);
+		double score = eff * fill - 0.01 * std::log2(double(ns));
+		if (score > best_score) {
+			best_score = score;
+			best = MvPlan{ns, K / ns, ntiles};
+		}
+	}
+	return best;
+}
+
+size_t mv_smem_bytes(int MB, int pro, int epi, int K, int kc) {
+	size_t f = size_t(MB) * kc;
+	if (pro != PRO_PLAIN) f += size_t(MB) * K;
+	f += size_t(MB) * MV_NWARPS * MV_TN * (epi == EPI_GEGLU ? 2 : 1);
+	return f * sizeof(float);
+}
+
+template <int MB, int PRO, int EPI>
+int launch_mv_t(const MvArgs &a, dim3 grid, size_t smem, cudaStream_t st) {
+	static size_t configured = 0;
+	if (smem > 48 * 1024 && smem > configured) {
+		TG_CUDA(cudaFuncSetAttribute(qmatvec_kernel<MB, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+		configured = smem;
+	}
+	qmatvec_kernel<MB, PRO, EPI><<<grid, MV_THREADS, smem, st>>>(a);
+	count_launch();
+	return check_launch("qmatvec");
+}
+
+template <int MB>
+int launch_mv_b(const MvArgs &a, int pro, int epi, dim3 grid, size_t smem, cudaStream_t st) {
+	if (epi == EPI_GEGLU) {
+		if (pro == PRO_RESNORM) return launch_mv_t<MB, PRO_RESNORM, EPI_GEGLU>(a, grid, smem, st);
+		if (pro == PRO_NORM) return launch_mv_t<MB, PRO_NORM, EPI_GEGLU>(a, grid, smem, st);
+		return launch_mv_t<MB, PRO_PLAIN, EPI_GEGLU>(a, grid, smem, st);
+	}
+	if (pro == PRO_RESNORM) return launch_mv_t<MB, PRO_RESNORM, EPI_SCALE>(a, grid, smem, st);
+	if (pro == PRO_NORM) return launch_mv_t<MB, PRO_NORM, EPI_SCALE>(a, grid, smem, st);
+	return launch_mv_t<MB, PRO_PLAIN, EPI_SCALE>(a, grid, smem, st);
+}
+
+// a.B may be 1..4 per launch
+int launch_mv(MvArgs a, int pro, int epi, cudaStream_t st) {
+	dim3 grid(std::min(a.ntiles, 65535), a.nsplit);
+	const int MB = a.B <= 1 ? 1 : (a.B == 2 ? 2 : 4);
+	size_t smem = mv_smem_bytes(MB, pro, epi, a.K, a.kc);
+	switch (MB) {
+		case 1:
+			return launch_mv_b<1>(a, pro, epi, grid, smem, st);
+		case 2:
+			return launch_mv_b<2>(a, pro, epi, grid, smem, st);
+		default:
+			return launch_mv_b<4>(a, pro, epi, grid, smem, st);
+	}
+}
+
+constexpr int MV_MAX_B = 4;
+
+}  // namespace
+
+// ===================================================================== state
+struct tg_state {
+	tg_model *m = nullptr;
+	int B = 1;
+	int max_pos_global = 0;
+	cudaStream_t stream = nullptr;
+	// per-layer caches
+	std::vector<float *> kcache, vcache;  // [B][slots][256]
+	std::vector<int> slots;
+	// decode activations
+	float *h[2] = {nullptr, nullptr};  // residual stream ping-pong [B][D]
+	float *qkv = nullptr;              // [B][qd+2kd]
+	float *attn_out = nullptr;         // [B][qd]
+	float *t = nullptr;                // [B][D]
+	float *act = nullptr;              // [B][I]
+	float *xnorm = nullptr;            // [B][D] final-normed hidden (parity read-back)
+	float *logits = nullptr;           // [B][V]
+	float *partial = nullptr;          // split-K scratch
+	size_t partial_floats = 0;
+	unsigned *tickets = nullptr;       // [max tiles] + [B] for attention
+	unsigned *attn_tickets = nullptr;
+	float *attn_part = nullptr;        // [B][nsplit_max][1032]
+	int attn_nsplit_local = 16, attn_nsplit_global = 64;
+	int *step_pos = nullptr, *next_pos = nullptr, *ring_base = nullptr;  // [B]
+	int *tok = nullptr;                // [B]
+	int *tok_log = nullptr;            // [log_cap][B]
+	int log_cap = 0;
+	int *log_count = nullptr;          // [B]
+	float *randf = nullptr;            // [randf_cap][B]
+	int randf_cap = 0;
+	int *randf_count = nullptr;        // [B]
+	int *err_flag = nullptr;
+	int *host_pin = nullptr;           // pinned staging, 64 KiB
+	// prefill scratch (grow-only)
+	float *pf = nullptr;
+	size_t pf_floats = 0;
+	int *pf_ids = nullptr;
+	int pf_ids_cap = 0;
+	// plans
+	MvPlan plan_qkv, plan_o, plan_gu, plan_dn, plan_lm;
+	// decode graph
+	cudaGraphExec_t graph = nullptr;
+	bool use_graph = true;
+	bool warmed = false;
+	std::vector<int> host_pos;  // mirror of next_pos for call-order checks
+};
+
+namespace {
+
+int state_alloc(tg_state *s) {
+	tg_model *m = s->m;
+	const tg_config &c = m->cfg;
+	const int B = s->B, D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	TG_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+	s->kcache.resize(c.n_layers);
+	s->vcache.resize(c.n_layers);
+	s->slots.resize(c.n_layers);
+	for (int l = 0; l < c.n_layers; l++) {
+		int slots = m->layers[l].is_local ? c.n_pos_local : s->max_pos_global;
+		s->slots[l] = slots;
+		size_t n = size_t(B) * slots * c.head_dim * c.n_kv;
+		TG_CUDA(cudaMalloc(&s->kcache[l], n * 4));
+		TG_CUDA(cudaMalloc(&s->vcache[l], n * 4));
+		TG_CUDA(cudaMemsetAsync(s->kcache[l], 0, n * 4, s->stream));
+		TG_CUDA(cudaMemsetAsync(s->vcache[l], 0, n * 4, s->stream));
+	}
+	auto allocf = [&](float **p, size_t n) -> int {
+		TG_CUDA(cudaMalloc(p, n * 4));
+		TG_CUDA(cudaMemsetAsync(*p, 0, n * 4, s->stream));
+		return TG_OK;
+	};
+	TG_TRY(allocf(&s->h[0], size_t(B) * D));
+	TG_TRY(allocf(&s->h[1], size_t(B) * D));
+	TG_TRY(allocf(&s->qkv, size_t(B) * (qd + 2 * kd)));
+	TG_TRY(allocf(&s->attn_out, size_t(B) * qd));
+	TG_TRY(allocf(&s->t, size_t(B) * D));
+	TG_TRY(allocf(&s->act, size_t(B) * I));
+	TG_TRY(allocf(&s->xnorm, size_t(B) * D));
+	TG_TRY(allocf(&s->logits, size_t(B) * V));
+
+	const int target = env_int("TG_MV_TARGET_CTAS", 2 * g_num_sms);
+	s->plan_qkv = plan_matvec(D, (qd + 2 * kd) / MV_TN, target);
+	s->plan_o = plan_matvec(qd, D / MV_TN, target);
+	s->plan_gu = plan_matvec(D, I / MV_TN, target);
+	s->plan_dn = plan_matvec(I, D / MV_TN, target);
+	s->plan_lm = plan_matvec(D, V / MV_TN, target);
+	const int mb = std::min(B, MV_MAX_B);
+	size_t pf = 0;
+	pf = std::max(pf, size_t(s->plan_qkv.nsplit) * mb * (qd + 2 * kd));
+	pf = std::max(pf, size_t(s->plan_o.nsplit) * mb * D);
+	pf = std::max(pf, size_t(s->plan_gu.nsplit) * mb * 2 * I);
+	pf = std::max(pf, size_t(s->plan_dn.nsplit) * mb * D);
+	s->partial_floats = pf;
+	TG_TRY(allocf(&s->partial, pf));
+	TG_CUDA(cudaMalloc(&s->tickets, sizeof(unsigned) * (V / MV_TN)));
+	TG_CUDA(cudaMemsetAsync(s->tickets, 0, sizeof(unsigned) * (V / MV_TN), s->stream));
+	TG_CUDA(cudaMalloc(&s->attn_tickets, sizeof(unsigned) * B));
+	TG_CUDA(cudaMemsetAsync(s->attn_tickets, 0, sizeof(unsigned) * B, s->stream));
+	s->attn_nsplit_local = env_int("TG_ATTN_SPLIT_LOCAL", 16);
+	s->attn_nsplit_global = env_int("TG_ATTN_SPLIT_GLOBAL", 64);
+	int nsmax = std::max(s->attn_nsplit_local, s->attn_nsplit_global);
+	TG_TRY(allocf(&s->attn_part, size_t(B) * nsmax * (AT_NH * AT_HD + 8)));
+	auto alloci = [&](int **p, size_t n) -> int {
+		TG_CUDA(cudaMalloc(p, n * 4));
+		TG_CUDA(cudaMemsetAsync(*p, 0, n * 4, s->stream));
+		return TG_OK;
+	};
+	TG_TRY(alloci(&s->step_pos, B));
+	TG_TRY(alloci(&s->next_pos, B));
+	TG_TRY(alloci(&s->ring_base, B));
+	TG_TRY(alloci(&s->tok, B));
+	TG_TRY(alloci(&s->log_count, B));
+	TG_TRY(alloci(&s->randf_count, B));
+	TG_TRY(alloci(&s->err_flag, 1));
+	TG_CUDA(cudaMallocHost(&s->host_pin, 64 * 1024));
+	s->host_pos.assign(B, 0);
+	s->use_graph = env_int("TG_USE_GRAPH", 1) != 0;
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+GeluLut make_lut(const tg_model *m) { return GeluLut{m->gelu, m->gelu_min, m->gelu_eps, m->gelu_size}; }
+
+int check_ready(const tg_model *m) {
+	if (!m->rope[0][0] || !m->rope[1][0] || !m->gelu)
+		return fail(TG_ESTATE, "RoPE / GeLU tables not set (tg_model_set_rope, tg_model_set_gelu_table or tg_model_build_tables)");
+	return TG_OK;
+}
+
+// ------------------------------------------------------------- decode step
+// One token for sequences [b0, b0+nb) (nb <= MV_MAX_B). Kernel sequence per
+// layer: QKV matvec (norm prologue) -> attention -> O matvec -> gate/up matvec
+// (residual+norm prologue, GeGLU epilogue) -> down matvec; then the lm_head
+// matvec with the last residual+norm prologue.
+int enqueue_decode_chunk(tg_state *s, int b0, int nb) {
+	tg_model *m = s->m;
+	const tg_config &c = m->cfg;
+	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	cudaStream_t st = s->stream;
+	const GeluLut lut = make_lut(m);
+
+	EmbedArgs ea;
+	ea.wte = m->wte;
+	ea.scales = m->wte_s;
+	ea.tok = s->tok + b0;
+	ea.h = s->h[0] + size_t(b0) * D;
+	ea.step_pos = s->step_pos + b0;
+	ea.next_pos = s->next_pos + b0;
+	ea.err_flag = s->err_flag;
+	ea.D = D;
+	ea.V = V;
+	ea.sqrtD = float(std::sqrt(double(D)));  // ops.hpp:584 `const float scale = sqrt(dims)`
+	embed_decode_kernel<<<nb, 256, 0, st>>>(ea);
+	count_launch();
+	TG_TRY(check_launch("embed_decode"));
+
+	int cur = 0;  // index of the buffer holding the residual stream
+	for (int l = 0; l < c.n_layers; l++) {
+		const LayerW &w = m->layers[l];
+		// ---- QKV
+		{
+			MvArgs a{};
+			a.seg[0] = MvSeg{w.Q.q, w.Q.s, qd, 0, 0};
+			a.seg[1] = MvSeg{w.K.q, w.K.s, kd, qd, qd / MV_TN};
+			a.seg[2] = MvSeg{w.V.q, w.V.s, kd, qd + kd, (qd + kd) / MV_TN};
+			a.nseg = 3;
+			a.ntiles = (qd + 2 * kd) / MV_TN;
+			a.K = D;
+			a.kc = s->plan_qkv.kc;
+			a.nsplit = s->plan_qkv.nsplit;
+			a.B = nb;
+			a.part_stride = qd + 2 * kd;
+			a.out_stride = qd + 2 * kd;
+			a.h = s->h[cur] + size_t(b0) * D;
+			a.w_pre = w.attn_pre;
+			a.partial = s->partial;
+			a.tickets = s->tickets;
+			a.out = s->qkv + size_t(b0) * (qd + 2 * kd);
+			int pro = PRO_NORM;
+			if (l > 0) {
+				pro = PRO_RESNORM;
+				a.t = s->t + size_t(b0) * D;
+				a.w_post = m->layers[l - 1].mlp_post;
+				a.h_out = s->h[cur ^ 1] + size_t(b0) * D;
+			}
+			TG_TRY(launch_mv(a, pro, EPI_SCALE, st));
+			if (l > 0) cur ^= 1;
+		}
+		// ---- attention over the cache
+		{
+			AttnArgs a{};
+			a.qkv = s->qkv + size_t(b0) * (qd + 2 * kd);
+			a.rmsq = w.rmsq;
+			a.rmsk = w.rmsk;
+			a.cosT = m->rope[w.is_local ? 1 : 0][0];
+			a.sinT = m->rope[w.is_local ? 1 : 0][1];
+			a.slots = s->slots[l];
+			a.kcache = s->kcache[l] + size_t(b0) * a.slots * AT_HD;
+			a.vcache = s->vcache[l] + size_t(b0) * a.slots * AT_HD;
+			a.is_local = w.is_local ? 1 : 0;
+			a.step_pos = s->step_pos + b0;
+			a.ring_base = s->ring_base + b0;
+			a.nsplit = w.is_local ? s->attn_nsplit_local : s->attn_nsplit_global;
+			a.part = s->attn_part + size_t(b0) * a.nsplit * (AT_NH * AT_HD + 8);
+			a.tickets = s->attn_tickets + b0;
+			a.out = s->attn_out + size_t(b0) * qd;
+			a.err_flag = s->err_flag;
+			attn_decode_kernel<<<dim3(a.nsplit, nb), AT_THREADS, 0, st>>>(a);
+			count_launch();
+			TG_TRY(check_launch("attn_decode"));
+		}
+		// ---- O projection
+		{
+			MvArgs a{};
+			a.seg[0] = MvSeg{w.O.q, w.O.s, D, 0, 0};
+			a.nseg = 1;
+			a.ntiles = D / MV_TN;
+			a.K = qd;
+			a.kc = s->plan_o.kc;
+			a.nsplit = s->plan_o.nsplit;
+			a.B = nb;
+			a.part_stride = D;
+			a.out_stride = D;
+			a.x = s->attn_out + size_t(b0) * qd;
+			a.partial = s->partial;
+			a.tickets = s->tickets;
+			a.out = s->t + size_t(b0) * D;
+			TG_TRY(launch_mv(a, PRO_PLAIN, EPI_SCALE, st));
+		}
+		// ---- gate/up with GeGLU
+		{
+			MvArgs a{};
+			a.seg[0] = MvSeg{w.U.q, w.U.s, I, 0, 0};
+			a.seg[1] = MvSeg{w.G.q, w.G.s, I, I, 0};
+			a.nseg = 2;
+			a.ntiles = I / MV_TN;
+			a.K = D;
+			a.kc = s->plan_gu.kc;
+			a.nsplit = s->plan_gu.nsplit;
+			a.B = nb;
+			a.part_stride = 2 * I;
+			a.out_stride = I;
+			a.h = s->h[cur] + size_t(b0) * D;
+			a.t = s->t + size_t(b0) * D;
+			a.w_post = w.attn_post;
+			a.w_pre = w.mlp_pre;
+			a.h_out = s->h[cur ^ 1] + size_t(b0) * D;
+			a.partial = s->partial;
+			a.tickets = s->tickets;
+			a.out = s->act + size_t(b0) * I;
+			a.lut = lut;
+			TG_TRY(launch_mv(a, PRO_RESNORM, EPI_GEGLU, st));
+			cur ^= 1;
+		}
+		// ---- down projection
+		{
+			MvArgs a{};
+			a.seg[0] = MvSeg{w.Dn.q, w.Dn.s, D, 0, 0};
+			a.nseg = 1;
+			a.ntiles = D / MV_TN;
+			a.K = I;
+			a.kc = s->plan_dn.kc;
+			a.nsplit = s->plan_dn.nsplit;
+			a.B = nb;
+			a.part_stride = D;
+			a.out_stride = D;
+			a.x = s->act + size_t(b0) * I;
+			a.partial = s->partial;
+			a.tickets = s->tickets;
+			a.out = s->t + size_t(b0) * D;
+			TG_TRY(launch_mv(a, PRO_PLAIN, EPI_SCALE, st));
+		}
+	}
+	// ---- lm_head (final residual add + final norm in the prologue)
+	{
+		MvArgs a{};
+		a.seg[0] = MvSeg{m->lm_head.q, m->lm_head.s, V, 0, 0};
+		a.nseg = 1;
+		a.ntiles = V / MV_TN;
+		a.K = D;
+		a.kc = s->plan_lm.kc;
+		a.nsplit = s->plan_lm.nsplit;
+		a.B = nb;
+		a.part_stride = V;
+		a.out_stride = V;
+		a.h = s->h[cur] + size_t(b0) * D;
+		a.t = s->t + size_t(b0) * D;
+		a.w_post = m->layers[c.n_layers - 1].mlp_post;
+		a.w_pre = m->final_norm;
+		a.h_out = s->h[cur ^ 1] + size_t(b0) * D;
+		a.x_out = s->xnorm + size_t(b0) * D;
+		a.partial = s->partial;
+		a.tickets = s->tickets;
+		a.out = s->logits + size_t(b0) * V;
+		TG_TRY(launch_mv(a, PRO_RESNORM, EPI_SCALE, st));
+	}
+	return TG_OK;
+}
+
+int decode_launches_per_chunk(const tg_config &c) { return 1 + 5 * c.n_layers + 1; }
+
+int enqueue_decode_all(tg_state *s) {
+	for (int b0 = 0; b0 < s->B; b0 += MV_MAX_B) TG_TRY(enqueue_decode_chunk(s, b0, std::min(MV_MAX_B, s->B - b0)));
+	return TG_OK;
+}
+
+int enqueue_decode_step(tg_state *s) {
+	// The first step of a state runs eagerly so that lazy module loading and
+	// cudaFuncSetAttribute happen outside stream capture; the graph is captured
+	// on the second step and replayed from then on.
+	if (!s->use_graph || !s->warmed) {
+		s->warmed = true;
+		return enqueue_decode_all(s);
+	}
+	if (!s->graph) {
+		cudaGraph_t g = nullptr;
+		long long before = g_launches.load();
+		TG_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+		int rc = enqueue_decode_all(s);
+		cudaError_t e = cudaStreamEndCapture(s->stream, &g);
+		g_launches.store(before);
+		if (rc != TG_OK) {
+			if (g) cudaGraphDestroy(g);
+			return rc;
+		}
+		if (e != cudaSuccess) return fail(TG_ECUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e));
+		e = cudaGraphInstantiate(&s->graph, g, 0);
+		cudaGraphDestroy(g);
+		if (e != cudaSuccess) return fail(TG_ECUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+	}
+	TG_CUDA(cudaGraphLaunch(s->graph, s->stream));
+	const int chunks = (s->B + MV_MAX_B - 1) / MV_MAX_B;
+	count_launch(chunks * decode_launches_per_chunk(s->m->cfg));
+	return TG_OK;
+}
+
+SampleArgs sample_args(tg_state *s, float minp, float temp, bool log_tokens) {
+	SampleArgs a{};
+	a.logits = s->logits;
+	a.V = s->m->cfg.n_vocab;
+	a.tok_out = s->tok;
+	a.tok_log = log_tokens ? s->tok_log : nullptr;
+	a.log_count = s->log_count;
+	a.log_cap = s->log_cap;
+	a.B = s->B;
+	a.minp = minp;
+	a.temp = temp;
+	a.randf = s->randf;
+	a.randf_count = s->randf_count;
+	a.randf_cap = s->randf_cap;
+	return a;
+}
+
+int enqueue_sampler(tg_state *s, float minp, float temp, bool log_tokens) {
+	SampleArgs a = sample_args(s, minp, temp, log_tokens);
+	if (minp < 1.0f) {  // transformer.hpp:208,229: min-p sampling iff minp < 1
+		minp_kernel<<<s->B, SM_THREADS, 0, s->stream>>>(a);
+		count_launch();
+		return check_launch("minp");
+	}
+	argmax_kernel<<<s->B, SM_THREADS, 0, s->stream>>>(a);
+	count_launch();
+	return check_launch("argmax");
+}
+
+int check_err_flag(tg_state *s) {
+	int flag = 0;
+	TG_CUDA(cudaMemcpyAsync(s->host_pin + 8192, s->err_flag, 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	flag = s->host_pin[8192];
+	if (flag) {
+		cudaMemsetAsync(s->err_flag, 0, 4, s->stream);
+		return fail(TG_EINVAL, flag == 1 ? "token id out of range" : "global KV cache full (max_pos_global reached)");
+	}
+	return TG_OK;
+}
+
+int ensure_log(tg_state *s, int steps) {
+	if (steps <= s->log_cap) return TG_OK;
+	if (s->tok_log) cudaFree(s->tok_log);
+	s->tok_log = nullptr;
+	TG_CUDA(cudaMalloc(&s->tok_log, size_t(steps) * s->B * 4));
+	s->log_cap = steps;
+	return TG_OK;
+}
+
+// ------------------------------------------------------------- prefill
+int launch_gemm(float *C, const float *A, const QW &w, int M, float *partial, size_t partial_floats, cudaStream_t st) {
+	const int K = w.K, N = w.N;
+	dim3 grid(N / GM_BN, (M + GM_BM - 1) / GM_BM, 1);
+	int ctas = grid.x * grid.y;
+	int nsplit = 1;
+	const int units = K / GM_BK;
+	if (ctas < g_num_sms) {
+		int want = (2 * g_num_sms + ctas - 1) / ctas;
+		for (int ns = 1; ns <= units; ns++)
+			if (units % ns == 0 && size_t(ns) * M * N <= partial_floats) {
+				nsplit = ns;
+				if (ns >= want) break;
+			}
+	}
+	grid.z = nsplit;
+	qgemm_simt_kernel<<<grid, 256, 0, st>>>(C, A, w.q, w.s, M, K, N, K / nsplit, partial);
+	count_launch();
+	TG_TRY(check_launch("qgemm_simt"));
+	if (nsplit > 1) {
+		size_t n = size_t(M) * N;
+		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, partial, w.s, M, N, nsplit);
+		count_launch();
+		TG_TRY(check_launch("qgemm_reduce"));
+	}
+	return TG_OK;
+}
+
+// prefill of one sequence b with S tokens already in s->pf_ids (device)
+int enqueue_prefill_seq(tg_state *s, int b, int S) {
+	tg_model *m = s->m;
+	const tg_config &c = m->cfg;
+	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	cudaStream_t st = s->stream;
+	const GeluLut lut = make_lut(m);
+	// scratch carve-up
+	float *p = s->pf;
+	float *h = p;        p += size_t(S) * D;
+	float *xn = p;       p += size_t(S) * D;
+	float *q = p;        p += size_t(S) * qd;
+	float *k = p;        p += size_t(S) * kd;
+	float *v = p;        p += size_t(S) * kd;
+	float *ao = p;       p += size_t(S) * qd;
+	float *tt = p;       p += size_t(S) * D;
+	float *up = p;       p += size_t(S) * I;
+	float *gate = p;     p += size_t(S) * I;
+	float *part = p;
+	size_t part_floats = s->pf_floats - size_t(part - s->pf);
+
+	embed_prefill_kernel<<<S, 256, 0, st>>>(m->wte, m->wte_s, s->pf_ids + size_t(b) * S, h, S, D, V,
+	                                        float(std::sqrt(double(D))), s->err_flag);
+	count_launch();
+	TG_TRY(check_launch("embed_prefill"));
+	for (int l = 0; l < c.n_layers; l++) {
+		const LayerW &w = m->layers[l];
+		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.attn_pre, nullptr, D);
+		count_launch();
+		TG_TRY(launch_gemm(q, xn, w.Q, S, part, part_floats, st));
+		TG_TRY(launch_gemm(k, xn, w.K, S, part, part_floats, st));
+		TG_TRY(launch_gemm(v, xn, w.V, S, part, part_floats, st));
+		const int slots = s->slots[l];
+		qk_norm_rope_prefill_kernel<<<S, 192, 0, st>>>(q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
+		                                               m->rope[w.is_local ? 1 : 0][1],
+		                                               s->kcache[l] + size_t(b) * slots * AT_HD,
+		                                               s->vcache[l] + size_t(b) * slots * AT_HD, S, slots);
+		count_launch();
+		attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+		count_launch();
+		TG_TRY(check_launch("attn_prefill"));
+		TG_TRY(launch_gemm(tt, ao, w.O, S, part, part_floats, st));
+		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.attn_post, h, D);
+		count_launch();
+		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.mlp_pre, nullptr, D);
+		count_launch();
+		TG_TRY(launch_gemm(up, xn, w.U, S, part, part_floats, st));
+		TG_TRY(launch_gemm(gate, xn, w.G, S, part, part_floats, st));
+		size_t n = size_t(S) * I;
+		geglu_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(gate, up, n, lut);
+		count_launch();
+		TG_TRY(launch_gemm(tt, gate, w.Dn, S, part, part_floats, st));
+		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.mlp_post, h, D);
+		count_launch();
+		TG_TRY(check_launch("prefill layer"));
+	}
+	// lm_head on the last position (modules.hpp:232-240)
+	{
+		MvArgs a{};
+		a.seg[0] = MvSeg{m->lm_head.q, m->lm_head.s, V, 0, 0};
+		a.nseg = 1;
+		a.ntiles = V / MV_TN;
+		a.K = D;
+		a.kc = s->plan_lm.kc;
+		a.nsplit = s->plan_lm.nsplit;
+		a.B = 1;
+		a.part_stride = V;
+		a.out_stride = V;
+		a.h = h + size_t(S - 1) * D;
+		a.w_pre = m->final_norm;
+		a.x_out = s->xnorm + size_t(b) * D;
+		a.partial = s->partial;
+		a.tickets = s->tickets;
+		a.out = s->logits + size_t(b) * V;
+		TG_TRY(launch_mv(a, PRO_NORM, EPI_SCALE, st));
+	}
+	return TG_OK;
+}
+
+}  // namespace
+
+// ===================================================================== C ABI
+extern "C" {
+
+const char *tg_last_error(void) { return g_err.c_str(); }
+const char *tg_version(void) { return "tiny-gemma_b200 0.1 (sm_100a)"; }
+
+int tg_device_count(int *count) {
+	if (!count) return fail(TG_EINVAL, "count is null");
+	int n = 0;
+	cudaError_t e = cudaGetDeviceCount(&n);
+	if (e != cudaSuccess) {
+		cudaGetLastError();
+		n = 0;
+	}
+	*count = n;
+	return TG_OK;
+}
+
+int tg_config_by_name(const char *name, tg_config *out) {
+	if (!name || !out) return fail(TG_EINVAL, "null argument");
+	// reference config.hpp:46-48
+	if (std::strcmp(name, "270m") == 0) {
+		*out = tg_config{640, 2048, 18, 262144, 32768, 512, 256, 4, 1, 1000000.0f, 10000.0f, 6};
+		return TG_OK;
+	}
+	if (std::strcmp(name, "1B") == 0) {
+		*out = tg_config{1152, 6912, 26, 262144, 32768, 512, 256, 4, 1, 1000000.0f, 10000.0f, 6};
+		return TG_OK;
+	}
+	return fail(TG_EINVAL, std::string("unknown model size: ") + name);
+}
+
+int tg_model_file_bytes(const tg_config *cfg, size_t *nbytes) {
+	if (!cfg || !nbytes) return fail(TG_EINVAL, "null argument");
+	*nbytes = model_file_bytes(*cfg);
+	return TG_OK;
+}
+
+int tg_model_create(const tg_config *cfg, int device, tg_model **out) {
+	if (!cfg || !out) return fail(TG_EINVAL, "null argument");
+	const tg_config &c = *cfg;
+	if (c.head_dim != 256 || c.n_head != 4 || c.n_kv != 1)
+		return fail(TG_ESHAPE, "kernels are specialised for 4 query heads, 1 KV head, head_dim 256");
+	if (!supported_k(c.hidden_size) || !supported_n(c.hidden_size) || !supported_k(c.intermediate_size) ||
+	    !supported_n(c.intermediate_size) || c.n_vocab % 8192 != 0 || c.n_layers < 1 || c.window_pattern < 1)
+		return fail(TG_ESHAPE, "unsupported model dimensions");
+	TG_TRY(ensure_device(device));
+	tg_model *m = new tg_model();
+	m->cfg = c;
+	m->device = device;
+	m->nbytes = model_file_bytes(c);
+	cudaError_t e = cudaMalloc(&m->blob, m->nbytes);
+	if (e != cudaSuccess) {
+		delete m;
+		return fail(TG_ENOMEM, std::string("cudaMalloc(weights): ") + cudaGetErrorString(e));
+	}
+	cudaMemset(m->blob, 0, m->nbytes);
+	bind_model(m);
+	*out = m;
+	return TG_OK;
+}
+
+int tg_model_free(tg_model *m) {
+	if (!m) return TG_OK;
+	cudaSetDevice(m->device);
+	cudaFree(m->blob);
+	for (int i = 0; i < 2; i++)
+		for (int j = 0; j < 2; j++) cudaFree(m->rope[i][j]);
+	cudaFree(m->gelu);
+	delete m;
+	return TG_OK;
+}
+
+int tg_model_load_memory(tg_model *m, const void *bytes, size_t nbytes) {
+	if (!m || !bytes) return fail(TG_EINVAL, "null argument");
+	if (nbytes < m->nbytes) return fail(TG_EIO, "weights image shorter than the model needs");
+	TG_CUDA(cudaSetDevice(m->device));
+	TG_CUDA(cudaMemcpy(m->blob, bytes, m->nbytes, cudaMemcpyHostToDevice));
+	m->loaded = true;
+	return TG_OK;
+}
+
+int tg_model_load_file(tg_model *m, const char *path) {
+	if (!m || !path) return fail(TG_EINVAL, "null argument");
+	FILE *f = std::fopen(path, "rb");
+	if (!f) return fail(TG_EIO, "Could not open file.");
+	TG_CUDA(cudaSetDevice(m->device));
+	// stream the file through two pinned buffers so the disk read and the copy overlap
+	const size_t CH = size_t(64) << 20;
+	uint8_t *pin[2] = {nullptr, nullptr};
+	cudaStream_t st;
+	cudaEvent_t ev[2];
+	if (cudaMallocHost(&pin[0], CH) != cudaSuccess || cudaMallocHost(&pin[1], CH) != cudaSuccess) {
+		std::fclose(f);
+		cudaFreeHost(pin[0]);
+		return fail(TG_ENOMEM, "cudaMallocHost(staging)");
+	}
+	cudaStreamCreate(&st);
+	cudaEventCreate(&ev[0]);
+	cudaEventCreate(&ev[1]);
+	size_t off = 0;
+	int rc = TG_OK;
+	for (int i = 0; off < m->nbytes; i ^= 1) {
+		size_t want = std::min(CH, m->nbytes - off);
+		cudaEventSynchronize(ev[i]);
+		size_t got = std::fread(pin[i], 1, want, f);
+		if (got != want) {
+			rc = fail(TG_EIO, "weights file is shorter than the model needs");
+			break;
+		}
+		if (cudaMemcpyAsync(m->blob + off, pin[i], want, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+			rc = fail(TG_ECUDA, "cudaMemcpyAsync(weights)");
+			break;
+		}
+		cudaEventRecord(ev[i], st);
+		off += want;
+	}
+	cudaStreamSynchronize(st);
+	std::fclose(f);
+	cudaEventDestroy(ev[0]);
+	cudaEventDestroy(ev[1]);
+	cudaStreamDestroy(st);
+	cudaFreeHost(pin[0]);
+	cudaFreeHost(pin[1]);
+	if (rc == TG_OK) m->loaded = true;
+	return rc;
+}
+
+int tg_model_set_rope(tg_model *m, int is_local, const float *cos_host, const float *sin_host, int n_pos) {
+	if (!m || !cos_host || !sin_host || n_pos <= 0) return fail(TG_EINVAL, "bad argument");
+	TG_CUDA(cudaSetDevice(m->device));
+	const int i = is_local ? 1 : 0;
+	size_t n = size_t(n_pos) * m->cfg.head_dim * 4;
+	const float *src[2] = {cos_host, sin_host};
+	for (int j = 0; j < 2; j++) {
+		if (m->rope[i][j]) cudaFree(m->rope[i][j]);
+		m->rope[i][j] = nullptr;
+		TG_CUDA(cudaMalloc(&m->rope[i][j], n));
+		TG_CUDA(cudaMemcpy(m->rope[i][j], src[j], n, cudaMemcpyHostToDevice));
+	}
+	m->rope_npos[i] = n_pos;
+	return TG_OK;
+}
+
+int tg_model_set_gelu_table(tg_model *m, float mn, float mx, const float *table, int size) {
+	if (!m || !table || size <= 0) return fail(TG_EINVAL, "bad argument");
+	TG_CUDA(cudaSetDevice(m->device));
+	if (m->gelu) cudaFree(m->gelu);
+	m->gelu = nullptr;
+	TG_CUDA(cudaMalloc(&m->gelu, size_t(size) * 4));
+	TG_CUDA(cudaMemcpy(m->gelu, table, size_t(size) * 4, cudaMemcpyHostToDevice));
+	m->gelu_min = mn;
+	m->gelu_max = mx;
+	m->gelu_size = size;
+	m->gelu_eps = float(mx - mn) / float(size);  // ops.hpp:33
+	return TG_OK;
+}
+
+int tg_model_build_tables(tg_model *m, int gelu_size) {
+	if (!m || gelu_size <= 0) return fail(TG_EINVAL, "bad argument");
+	const tg_config &c = m->cfg;
+	const int hd = c.head_dim, half = hd / 2;
+	std::vector<float> ct(size_t(c.n_pos) * hd), st(size_t(c.n_pos) * hd), freqs(half);
+	for (int loc = 0; loc < 2; loc++) {
+		// decode.hpp:176-201
+		const float theta = loc ? c.rope_theta_local : c.rope_theta;
+		for (int i = 0; i < half; i++) {
+			float denom = std::pow(theta, float(2 * i) / hd);
+			freqs[i] = float(1.0 / denom);
+		}
+		for (int p = 0; p < c.n_pos; p++)
+			for (int d = 0; d < half; d++) {
+				float outer = p * freqs[d];
+				float cv = std::cos(outer), sv = std::sin(outer);
+				ct[size_t(p) * hd + d] = cv;
+				ct[size_t(p) * hd + d + half] = cv;
+				st[size_t(p) * hd + d] = sv;
+				st[size_t(p) * hd + d + half] = sv;
+			}
+		TG_TRY(tg_model_set_rope(m, loc, ct.data(), st.data(), c.n_pos));
+	}
+	// ops.hpp:16-39
+	std::vector<float> tab(gelu_size);
+	const float mn = -4.0f, mx = 4.0f, eps = float(mx - mn) / float(gelu_size);
+	for (int i = 0; i < gelu_size; i++) {
+		float a = mn + i * eps;
+		double inner = double(0.7978845608f) * (double(a) + double(0.044715f) * std::pow(double(a), 3.0));
+		tab[i] = float((0.5 * double(a)) * (1.0 + std::tanh(inner)));
+	}
+	return tg_model_set_gelu_table(m, mn, mx, tab.data(), gelu_size);
+}
+
+// ---------------------------------------------------------------- state
+int tg_state_create(tg_model *m, int batch, int max_pos_global, tg_state **out) {
+	if (!m || !out || batch < 1 || batch > 2048) return fail(TG_EINVAL, "bad argument (batch must be 1..2048)");
+	if (max_pos_global <= 0) max_pos_global = m->cfg.n_pos;
+	if (max_pos_global > m->cfg.n_pos) return fail(TG_EINVAL, "max_pos_global exceeds n_pos");
+	TG_CUDA(cudaSetDevice(m->device));
+	tg_state *s = new tg_state();
+	s->m = m;
+	s->B = batch;
+	s->max_pos_global = max_pos_global;
+	int rc = state_alloc(s);
+	if (rc != TG_OK) {
+		std::string keep = g_err;
+		tg_state_free(s);
+		g_err = keep;
+		return rc;
+	}
+	*out = s;
+	return TG_OK;
+}
+
+int tg_state_free(tg_state *s) {
+	if (!s) return TG_OK;
+	cudaSetDevice(s->m->device);
+	if (s->stream) cudaStreamSynchronize(s->stream);
+	if (s->graph) cudaGraphExecDestroy(s->graph);
+	for (float *p : s->kcache) cudaFree(p);
+	for (float *p : s->vcache) cudaFree(p);
+	cudaFree(s->h[0]);
+	cudaFree(s->h[1]);
+	cudaFree(s->qkv);
+	cudaFree(s->attn_out);
+	cudaFree(s->t);
+	cudaFree(s->act);
+	cudaFree(s->xnorm);
+	cudaFree(s->logits);
+	cudaFree(s->partial);
+	cudaFree(s->tickets);
+	cudaFree(s->attn_tickets);
+	cudaFree(s->attn_part);
+	cudaFree(s->step_pos);
+	cudaFree(s->next_pos);
+	cudaFree(s->ring_base);
+	cudaFree(s->tok);
+	cudaFree(s->tok_log);
+	cudaFree(s->log_count);
+	cudaFree(s->randf);
+	cudaFree(s->randf_count);
+	cudaFree(s->err_flag);
+	cudaFree(s->pf);
+	cudaFree(s->pf_ids);
+	if (s->host_pin) cudaFreeHost(s->host_pin);
+	if (s->stream) cudaStreamDestroy(s->stream);
+	delete s;
+	return TG_OK;
+}
+
+int tg_state_reset(tg_state *s) {
+	if (!s) return fail(TG_EINVAL, "null state");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	const int B = s->B;
+	TG_CUDA(cudaMemsetAsync(s->step_pos, 0, 4 * B, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->next_pos, 0, 4 * B, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->ring_base, 0, 4 * B, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->log_count, 0, 4 * B, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->randf_count, 0, 4 * B, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->err_flag, 0, 4, s->stream));
+	// the reference's caches are zero-initialised (tensor.hpp:66-74); stale rows
+	// are never read (valid_pos bounds every loop) so they are left in place
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	s->host_pos.assign(B, 0);
+	return TG_OK;
+}
+
+int tg_state_position(tg_state *s, int b, int *position) {
+	if (!s || !position || b < 0 || b >= s->B) return fail(TG_EINVAL, "bad argument");
+	*position = s->host_pos[b];
+	return TG_OK;
+}
+
+int tg_state_stream(tg_state *s, void **stream) {
+	if (!s || !stream) return fail(TG_EINVAL, "null argument");
+	*stream = (void *)s->stream;
+	return TG_OK;
+}
+
+int tg_prefill(tg_state *s, const int *ids, int S, float *logits_host) {
+	if (!s || !ids || S < 1) return fail(TG_EINVAL, "bad argument");
+	tg_model *m = s->m;
+	TG_TRY(check_ready(m));
+	const tg_config &c = m->cfg;
+	if (S > c.n_pos) return fail(TG_EINVAL, "prompt longer than n_pos");
+	if (S > s->max_pos_global) return fail(TG_EINVAL, "prompt longer than max_pos_global");
+	for (int b = 0; b < s->B; b++)
+		if (s->host_pos[b] != 0) return fail(TG_ESTATE, "prefill needs an empty KV cache (decode.hpp:78-79)");
+	TG_CUDA(cudaSetDevice(m->device));
+	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	if (S == 1) {
+		// a one-token prompt takes the reference's decode branch (modules.hpp:135)
+		TG_TRY(tg_decode(s, ids, logits_host));
+		return TG_OK;
+	}
+	size_t need = size_t(S) * (3 * size_t(D) + 2 * qd + 2 * kd + 2 * size_t(I));
+	size_t part = std::max(size_t(4) * S * D, size_t(1) << 22);  // split-K scratch
+	need += part;
+	if (need > s->pf_floats) {
+		if (s->pf) cudaFree(s->pf);
+		s->pf = nullptr;
+		s->pf_floats = 0;
+		cudaError_t e = cudaMalloc(&s->pf, need * 4);
+		if (e != cudaSuccess) return fail(TG_ENOMEM, std::string("cudaMalloc(prefill scratch): ") + cudaGetErrorString(e));
+		s->pf_floats = need;
+	}
+	if (S * s->B > s->pf_ids_cap) {
+		if (s->pf_ids) cudaFree(s->pf_ids);
+		s->pf_ids = nullptr;
+		TG_CUDA(cudaMalloc(&s->pf_ids, size_t(S) * s->B * 4));
+		s->pf_ids_cap = S * s->B;
+	}
+	TG_CUDA(cudaMemcpyAsync(s->pf_ids, ids, size_t(S) * s->B * 4, cudaMemcpyHostToDevice, s->stream));
+	for (int b = 0; b < s->B; b++) TG_TRY(enqueue_prefill_seq(s, b, S));
+	// position_ptr = S; ring base per decode.hpp:98-103
+	std::vector<int> pos(s->B, S), rb(s->B, S >= c.n_pos_local ? S : 0);
+	std::memcpy(s->host_pin, pos.data(), 4 * s->B);
+	std::memcpy(s->host_pin + s->B, rb.data(), 4 * s->B);
+	TG_CUDA(cudaMemcpyAsync(s->next_pos, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
+	TG_CUDA(cudaMemcpyAsync(s->step_pos, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
+	TG_CUDA(cudaMemcpyAsync(s->ring_base, s->host_pin + s->B, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
+	if (logits_host)
+		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * V * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_TRY(check_err_flag(s));
+	s->host_pos.assign(s->B, S);
+	return TG_OK;
+}
+
+int tg_decode(tg_state *s, const int *ids, float *logits_host) {
+	if (!s) return fail(TG_EINVAL, "null state");
+	tg_model *m = s->m;
+	TG_TRY(check_ready(m));
+	TG_CUDA(cudaSetDevice(m->device));
+	for (int b = 0; b < s->B; b++)
+		if (s->host_pos[b] >= s->max_pos_global) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
+	if (ids) {
+		std::memcpy(s->host_pin, ids, 4 * s->B);
+		TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
+	}
+	TG_TRY(enqueue_decode_step(s));
+	if (logits_host)
+		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_TRY(check_err_flag(s));
+	for (int b = 0; b < s->B; b++) s->host_pos[b] += 1;
+	return TG_OK;
+}
+
+int tg_sample_argmax(tg_state *s, int *toks_host) {
+	if (!s) return fail(TG_EINVAL, "null state");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	TG_TRY(enqueue_sampler(s, 2.0f, 1.0f, false));
+	TG_CUDA(cudaMemcpyAsync(s->host_pin, s->tok, 4 * s->B, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	if (toks_host) std::memcpy(toks_host, s->host_pin, 4 * s->B);
+	return TG_OK;
+}
+
+int tg_state_set_randf(tg_state *s, const float *randf_host, int n) {
+	if (!s || !randf_host || n < 1) return fail(TG_EINVAL, "bad argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	if (n > s->randf_cap) {
+		if (s->randf) cudaFree(s->randf);
+		s->randf = nullptr;
+		TG_CUDA(cudaMalloc(&s->randf, size_t(n) * s->B * 4));
+		s->randf_cap = n;
+		// captured graphs do not hold this pointer (the sampler is launched outside the graph)
+	}
+	TG_CUDA(cudaMemcpyAsync(s->randf, randf_host, size_t(n) * s->B * 4, cudaMemcpyHostToDevice, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->randf_count, 0, 4 * s->B, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+int tg_sample_minp(tg_state *s, float minp, float temp, const float *randf_host, int *toks_host) {
+	if (!s || !randf_host) return fail(TG_EINVAL, "bad argument");
+	if (!(minp < 1.0f)) return fail(TG_EINVAL, "minp must be < 1 (the reference uses argmax otherwise, transformer.hpp:208)");
+	TG_TRY(tg_state_set_randf(s, randf_host, 1));
+	TG_TRY(enqueue_sampler(s, minp, temp, false));
+	TG_CUDA(cudaMemcpyAsync(s->host_pin, s->tok, 4 * s->B, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	if (toks_host) std::memcpy(toks_host, s->host_pin, 4 * s->B);
+	return TG_OK;
+}
+
+int tg_logits_read(tg_state *s, float *logits_host) {
+	if (!s || !logits_host) return fail(TG_EINVAL, "null argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * s->m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+int tg_generate_async(tg_state *s, int n_steps, float minp, float temp) {
+	if (!s || n_steps < 1) return fail(TG_EINVAL, "bad argument");
+	TG_TRY(check_ready(s->m));
+	TG_CUDA(cudaSetDevice(s->m->device));
+	if (s->host_pos[0] + n_steps > s->max_pos_global) return fail(TG_ESTATE, "global KV cache too small for n_steps");
+	if (minp < 1.0f && s->randf_cap < n_steps) return fail(TG_ESTATE, "upload uniforms first (tg_state_set_randf)");
+	TG_TRY(ensure_log(s, n_steps));
+	TG_CUDA(cudaMemsetAsync(s->log_count, 0, 4 * s->B, s->stream));
+	for (int i = 0; i < n_steps; i++) {
+		TG_TRY(enqueue_decode_step(s));
+		TG_TRY(enqueue_sampler(s, minp, temp, true));
+	}
+	for (int b = 0; b < s->B; b++) s->host_pos[b] += n_steps;
+	return TG_OK;
+}
+
+int tg_state_tokens(tg_state *s, int n_steps, int *toks_host) {
+	if (!s || !toks_host || n_steps < 1 || n_steps > s->log_cap) return fail(TG_EINVAL, "bad argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	TG_CUDA(cudaMemcpyAsync(toks_host, s->tok_log, size_t(n_steps) * s->B * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_TRY(check_err_flag(s));
+	return TG_OK;
+}
+
+int tg_generate(tg_state *s, const int *first_ids, int n_steps, float minp, float temp, const float *randf_host,
+                int *toks_host) {
+	if (!s || !first_ids || n_steps < 1) return fail(TG_EINVAL, "bad argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	if (minp < 1.0f) {
+		if (!randf_host) return fail(TG_EINVAL, "min-p sampling needs uniforms");
+		TG_TRY(tg_state_set_randf(s, randf_host, n_steps));
+	}
+	std::memcpy(s->host_pin, first_ids, 4 * s->B);
+	TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
+	TG_TRY(tg_generate_async(s, n_steps, minp, temp));
+	if (toks_host) return tg_state_tokens(s, n_steps, toks_host);
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+int tg_kv_read(tg_state *s, int b, int layer, int slot0, int nslots, float *k_host, float *v_host) {
+	if (!s || !k_host || !v_host || b < 0 || b >= s->B || layer < 0 || layer >= s->m->cfg.n_layers)
+		return fail(TG_EINVAL, "bad argument");
+	const int slots = s->slots[layer];
+	if (slot0 < 0 || nslots < 1 || slot0 + nslots > slots) return fail(TG_EINVAL, "slot range out of bounds");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	size_t off = (size_t(b) * slots + slot0) * AT_HD;
+	TG_CUDA(cudaMemcpyAsync(k_host, s->kcache[layer] + off, size_t(nslots) * AT_HD * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaMemcpyAsync(v_host, s->vcache[layer] + off, size_t(nslots) * AT_HD * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+int tg_hidden_read(tg_state *s, float *hidden_host) {
+	if (!s || !hidden_host) return fail(TG_EINVAL, "null argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	TG_CUDA(cudaMemcpyAsync(hidden_host, s->xnorm, size_t(s->B) * s->m->cfg.hidden_size * 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+// ---------------------------------------------------------------- isolated ops
+int tg_dev_qmatvec(float *y, const float *x, const int8_t *w, const float *scales, int K, int N, void *stream) {
+	if (!y || !x || !w || !scales) return fail(TG_EINVAL, "null argument");
+	if (!supported_k(K)) return fail(TG_ESHAPE, "Unsupported ROW dimension: " + std::to_string(K));
+	if (!supported_n(N)) return fail(TG_ESHAPE, "Unsupported COL dimension: " + std::to_string(N));
+	// scratch for split-K, per device, grown on demand
+	static float *partial[64] = {nullptr};
+	static size_t partial_floats[64] = {0};
+	static unsigned *tickets[64] = {nullptr};
+	int dev = 0;
+	TG_CUDA(cudaGetDevice(&dev));
+	int sms = 0;
+	if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) g_num_sms = sms;
+	MvPlan p = plan_matvec(K, N / MV_TN, env_int("TG_MV_TARGET_CTAS", 2 * g_num_sms));
+	size_t need = size_t(p.nsplit) * N;
+	if (need > partial_floats[dev]) {
+		if (partial[dev]) cudaFree(partial[dev]);
+		partial[dev] = nullptr;
+		TG_CUDA(cudaMalloc(&partial[dev], need * 4));
+		partial_floats[dev] = need;
+	}
+	if (!tickets[dev]) {
+		TG_CUDA(cudaMalloc(&tickets[dev], sizeof(unsigned) * 2048));
+		TG_CUDA(cudaMemset(tickets[dev], 0, sizeof(unsigned) * 2048));
+	}
+	MvArgs a{};
+	a.seg[0] = MvSeg{w, scales, N, 0, 0};
+	a.nseg = 1;
+	a.ntiles = N / MV_TN;
+	a.K = K;
+	a.kc = p.kc;
+	a.nsplit = p.nsplit;
+	a.B = 1;
+	a.part_stride = N;
+	a.out_stride = N;
+	a.x = x;
+	a.partial = partial[dev];
+	a.tickets = tickets[dev];
+	a.out = y;
+	return launch_mv(a, PRO_PLAIN, EPI_SCALE, (cudaStream_t)stream);
+}
+
+int tg_dev_qgemm(float *c, const float *a, const int8_t *w, const float *scales, int M, int K, int N, void *stream) {
+	if (!c || !a || !w || !scales || M < 1) return fail(TG_EINVAL, "bad argument");
+	if (!supported_k(K)) return fail(TG_ESHAPE, "Unsupported ROW dimension: " + std::to_string(K));
+	if (!supported_n(N)) return fail(TG_ESHAPE, "Unsupported COL dimension: " + std::to_string(N));
+	static float *partial[64] = {nullptr};
+	static size_t partial_floats[64] = {0};
+	int dev = 0;
+	TG_CUDA(cudaGetDevice(&dev));
+	size_t need = std::max(size_t(4) * M * N, size_t(1) << 20);
+	if ((N / GM_BN) * ((M + GM_BM - 1) / GM_BM) >= g_num_sms) need = 0;
+	if (need > partial_floats[dev]) {
+		if (partial[dev]) cudaFree(partial[dev]);
+		partial[dev] = nullptr;
+		TG_CUDA(cudaMalloc(&partial[dev], need * 4));
+		partial_floats[dev] = need;
+	}
+	QW q{w, scales, K, N};
+	return launch_gemm(c, a, q, M, partial[dev], partial_floats[dev], (cudaStream_t)stream);
+}
+
+namespace {
+struct DevBuf {
+	void *p = nullptr;
+	~DevBuf() {
+		if (p) cudaFree(p);
+	}
+	int alloc(size_t n) {
+		TG_CUDA(cudaMalloc(&p, n));
+		return TG_OK;
+	}
+};
+}  // namespace
+
+int tg_qmatvec(float *y, const float *x, const int8_t *w, const float *scales, int K, int N) {
+	if (!y || !x || !w || !scales) return fail(TG_EINVAL, "null argument");
+	if (!supported_k(K)) return fail(TG_ESHAPE, "Unsupported ROW dimension: " + std::to_string(K));
+	if (!supported_n(N)) return fail(TG_ESHAPE, "Unsupported COL dimension: " + std::to_string(N));
+	TG_TRY(ensure_device(0));
+	DevBuf dy, dx, dw, ds;
+	TG_TRY(dy.alloc(size_t(N) * 4));
+	TG_TRY(dx.alloc(size_t(K) * 4));
+	TG_TRY(dw.alloc(size_t(K) * N));
+	TG_TRY(ds.alloc(size_t(N) * 4));
+	TG_CUDA(cudaMemcpy(dx.p, x, size_t(K) * 4, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemcpy(dw.p, w, size_t(K) * N, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemcpy(ds.p, scales, size_t(N) * 4, cudaMemcpyHostToDevice));
+	TG_TRY(tg_dev_qmatvec((float *)dy.p, (const float *)dx.p, (const int8_t *)dw.p, (const float *)ds.p, K, N, nullptr));
+	TG_CUDA(cudaDeviceSynchronize());
+	TG_CUDA(cudaMemcpy(y, dy.p, size_t(N) * 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_qgemm(float *c, const float *a, const int8_t *w, const float *scales, int M, int K, int N) {
+	if (!c || !a || !w || !scales || M < 1) return fail(TG_EINVAL, "bad argument");
+	if (!supported_k(K)) return fail(TG_ESHAPE, "Unsupported ROW dimension: " + std::to_string(K));
+	if (!supported_n(N)) return fail(TG_ESHAPE, "Unsupported COL dimension: " + std::to_string(N));
+	TG_TRY(ensure_device(0));
+	DevBuf dc, da, dw, ds;
+	TG_TRY(dc.alloc(size_t(M) * N * 4));
+	TG_TRY(da.alloc(size_t(M) * K * 4));
+	TG_TRY(dw.alloc(size_t(K) * N));
+	TG_TRY(ds.alloc(size_t(N) * 4));
+	TG_CUDA(cudaMemcpy(da.p, a, size_t(M) * K * 4, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemcpy(dw.p, w, size_t(K) * N, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemcpy(ds.p, scales, size_t(N) * 4, cudaMemcpyHostToDevice));
+	TG_TRY(tg_dev_qgemm((float *)dc.p, (const float *)da.p, (const int8_t *)dw.p, (const float *)ds.p, M, K, N, nullptr));
+	TG_CUDA(cudaDeviceSynchronize());
+	TG_CUDA(cudaMemcpy(c, dc.p, size_t(M) * N * 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_argmax_logits(const float *logits, int n, int *tok) {
+	if (!logits || !tok || n < 4 || n % 4) return fail(TG_EINVAL, "bad argument (n must be a multiple of 4)");
+	TG_TRY(ensure_device(0));
+	DevBuf dl, dt, dc;
+	TG_TRY(dl.alloc(size_t(n) * 4));
+	TG_TRY(dt.alloc(4));
+	TG_TRY(dc.alloc(4));
+	TG_CUDA(cudaMemcpy(dl.p, logits, size_t(n) * 4, cudaMemcpyHostToDevice));
+	SampleArgs a{};
+	a.logits = (float *)dl.p;
+	a.V = n;
+	a.tok_out = (int *)dt.p;
+	a.B = 1;
+	argmax_kernel<<<1, SM_THREADS>>>(a);
+	count_launch();
+	TG_TRY(check_launch("argmax"));
+	TG_CUDA(cudaMemcpy(tok, dt.p, 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_minp_logits(float *logits, int n, float minp, float temp, float randf, int *tok) {
+	if (!logits || !tok || n < MP_CHUNK || n % MP_CHUNK) return fail(TG_EINVAL, "bad argument (n must be a multiple of 8192)");
+	TG_TRY(ensure_device(0));
+	DevBuf dl, dt, dr, dc;
+	TG_TRY(dl.alloc(size_t(n) * 4));
+	TG_TRY(dt.alloc(4));
+	TG_TRY(dr.alloc(4));
+	TG_TRY(dc.alloc(4));
+	TG_CUDA(cudaMemcpy(dl.p, logits, size_t(n) * 4, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemcpy(dr.p, &randf, 4, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemset(dc.p, 0, 4));
+	SampleArgs a{};
+	a.logits = (float *)dl.p;
+	a.V = n;
+	a.tok_out = (int *)dt.p;
+	a.B = 1;
+	a.minp = minp;
+	a.temp = temp;
+	a.randf = (const float *)dr.p;
+	a.randf_count = (int *)dc.p;
+	a.randf_cap = 1;
+	minp_kernel<<<1, SM_THREADS>>>(a);
+	count_launch();
+	TG_TRY(check_launch("minp"));
+	TG_CUDA(cudaMemcpy(tok, dt.p, 4, cudaMemcpyDeviceToHost));
+	TG_CUDA(cudaMemcpy(logits, dl.p, size_t(n) * 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_rmsnorm(float *x, const float *w, int rows, int dim) {
+	if (!x || !w || rows < 1 || dim < 1) return fail(TG_EINVAL, "bad argument");
+	TG_TRY(ensure_device(0));
+	DevBuf dx, dw;
+	TG_TRY(dx.alloc(size_t(rows) * dim * 4));
+	TG_TRY(dw.alloc(size_t(dim) * 4));
+	TG_CUDA(cudaMemcpy(dx.p, x, size_t(rows) * dim * 4, cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMemcpy(dw.p, w, size_t(dim) * 4, cudaMemcpyHostToDevice));
+	rmsnorm_rows_kernel<<<rows, 256>>>((float *)dx.p, (const float *)dx.p, (const float *)dw.p, nullptr, dim);
+	count_launch();
+	TG_TRY(check_launch("rmsnorm"));
+	TG_CUDA(cudaMemcpy(x, dx.p, size_t(rows) * dim * 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_launch_count(int reset, long long *count) {
+	if (count) *count = g_launches.load();
+	if (reset) g_launches.store(0);
+	return TG_OK;
+}
+
+}  // extern "C"
