@@ -178,6 +178,10 @@ int tg_state_stream(tg_state *s, void **cuda_stream);
 int tg_generate_async(tg_state *s, int n_steps, float minp, float temp);
 /* upload uniforms [n, batch] used by min-p steps of tg_generate_async */
 int tg_state_set_randf(tg_state *s, const float *randf_host, int n);
+/* profiling aid for the persistent decode kernel: the first call arms a recorder;
+ * afterwards each launch stores SM-clock stamps taken by CTA 0 at the phase
+ * boundaries of its last token, and this call returns them (n = count). */
+int tg_state_phase_clocks(tg_state *s, long long *clocks_host, int cap, int *n);
 /* copy out the tokens the last tg_generate_async produced: [n_steps, batch] */
 int tg_state_tokens(tg_state *s, int n_steps, int *toks_host);
 

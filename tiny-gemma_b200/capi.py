@@ -69,6 +69,7 @@ SIGNATURES = {
     "tg_generate_async": (C.c_int, [_P, C.c_int, C.c_float, C.c_float]),
     "tg_state_set_randf": (C.c_int, [_P, _P, C.c_int]),
     "tg_state_tokens": (C.c_int, [_P, C.c_int, _P]),
+    "tg_state_phase_clocks": (C.c_int, [_P, _P, C.c_int, C.POINTER(C.c_int)]),
 }
 
 _lib = None
@@ -274,6 +275,12 @@ class State:
         out = np.empty((n_steps, self.B), np.int32)
         _ck(self.lib.tg_state_tokens(self.h, n_steps, _ptr(out)))
         return out
+
+    def phase_clocks(self) -> np.ndarray:
+        out = np.zeros(4096, np.int64)
+        n = C.c_int(0)
+        _ck(self.lib.tg_state_phase_clocks(self.h, _ptr(out), out.size, C.byref(n)))
+        return out[:n.value]
 
     def stream(self) -> int:
         p = C.c_void_p()

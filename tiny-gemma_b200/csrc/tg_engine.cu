@@ -15,6 +15,7 @@
 
 #include "../../include/tiny_gemma_b200.h"
 #include "kernels_decode.cuh"
+#include "kernels_mega.cuh"
 #include "kernels_prefill.cuh"
 #include "kernels_sampler.cuh"
 
@@ -286,6 +287,17 @@ struct tg_state {
 	bool use_graph = true;
 	bool warmed = false;
 	std::vector<int> host_pos;  // mirror of next_pos for call-order checks
+	// persistent decode kernel (batch 1)
+	bool mega_ok = false;
+	MgArgs mega{};
+	CUtensorMap *d_tmaps = nullptr;
+	MgLayer *d_layers = nullptr;
+	float *mg_part_A = nullptr, *mg_part_C = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr;
+	int *mg_samp_i = nullptr;
+	unsigned *mg_bar = nullptr;
+	int mega_grid = 0;
+	long long *mg_dbg = nullptr;
+	size_t mega_smem = 0;
 };
 
 namespace {
@@ -579,6 +591,256 @@ int enqueue_decode_step(tg_state *s) {
 	return TG_OK;
 }
 
+// ------------------------------------------------------------- persistent kernel set-up
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+PFN_encodeTiled get_encode_fn() {
+	static PFN_encodeTiled fn = nullptr;
+	if (!fn) {
+		void *p = nullptr;
+		cudaDriverEntryPointQueryResult q;
+		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+		    q == cudaDriverEntryPointSuccess)
+			fn = reinterpret_cast<PFN_encodeTiled>(p);
+	}
+	return fn;
+}
+
+// 2-D uint8 map over a row-major [K, N] int8 matrix; box = TN bytes x box_rows rows, no swizzle
+int make_tmap(CUtensorMap *out, const int8_t *base, int K, int N, int TN, int box_rows) {
+	PFN_encodeTiled enc = get_encode_fn();
+	if (!enc) return fail(TG_ECUDA, "cuTensorMapEncodeTiled entry point not available");
+	cuuint64_t gdim[2] = {cuuint64_t(N), cuuint64_t(K)};
+	cuuint64_t gstride[1] = {cuuint64_t(N)};
+	cuuint32_t box[2] = {cuuint32_t(TN), cuuint32_t(box_rows)};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(base), gdim, gstride, box, estr,
+	                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+	                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) return fail(TG_ECUDA, "cuTensorMapEncodeTiled failed: " + std::to_string(int(r)));
+	return TG_OK;
+}
+
+int largest_box_rows(int kc) {
+	for (int r = std::min(kc, 256); r >= 1; r--)
+		if (kc % r == 0) return r;
+	return 1;
+}
+
+// Choose the tile width and K-split of one phase so that as many of the G CTAs
+// as possible get exactly one unit. n_cols lists the matrices that share the
+// phase's column tiling (Q,K,V) — a tile never straddles two of them.
+bool plan_phase(MgPhase *out, int K, const std::vector<int> &n_cols, int nmat, bool allow_split, int G, int max_bytes) {
+	const int tns[] = {128, 96, 64, 48, 32, 16};
+	long best_score = -1;
+	for (int TN : tns) {
+		const int segs = TN / 16;
+		if (MG_THREADS % segs) continue;
+		bool ok = true;
+		int ntiles = 0;
+		for (int n : n_cols) {
+			if (n % TN) ok = false;
+			ntiles += n / TN;
+		}
+		if (!ok || ntiles > G) continue;
+		for (int ns = 1; ns <= (allow_split ? 64 : 1); ns++) {
+			if (K % ns) continue;
+			const int kc = K / ns;
+			if (kc % 8) continue;
+			const int units = ntiles * ns;
+			if (units > G) break;
+			const long bytes = long(nmat) * TN * kc;
+			if (bytes > max_bytes) continue;
+			long score = long(units) * 1000 - ns * 10 - (TN < 64 ? 100 : 0);
+			if (score > best_score) {
+				best_score = score;
+				const int br = largest_box_rows(kc);
+				*out = MgPhase{TN, segs, ns, kc, br, kc / br, ntiles, units, int(bytes)};
+			}
+		}
+	}
+	return best_score >= 0;
+}
+
+int mega_setup(tg_state *s) {
+	tg_model *m = s->m;
+	const tg_config &c = m->cfg;
+	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab, L = c.n_layers;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	int dev = m->device, coop = 0, smem_max = 0;
+	TG_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+	TG_CUDA(cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+	if (!coop) return fail(TG_ECUDA, "device lacks cooperative launch");
+	const int G = env_int("TG_MEGA_GRID", g_num_sms);
+	MgArgs &a = s->mega;
+	a = MgArgs{};
+	a.att_local = std::min(std::min(env_int("TG_MEGA_ATT_LOCAL", 32), MG_MAX_ATT), G);
+	a.att_global = std::min(std::min(env_int("TG_MEGA_ATT_GLOBAL", 32), MG_MAX_ATT), G);
+	const int budget = smem_max - 40 * 1024;  // room for h, xs, reduction scratch, attention scratch, static shared
+	if (!plan_phase(&a.A, D, {qd, kd, kd}, 1, true, G, budget / 8) || !plan_phase(&a.C, qd, {D}, 1, true, G, budget / 8) ||
+	    !plan_phase(&a.Dp, D, {I}, 2, false, G, budget) || !plan_phase(&a.E, I, {D}, 1, true, G, budget / 2))
+		return fail(TG_ESHAPE, "no phase plan fits");
+	a.LM = MgPhase{MG_LM_TN, MG_LM_TN / 16, 1, D, largest_box_rows(D), D / largest_box_rows(D), V / MG_LM_TN, V / MG_LM_TN, 0};
+	const int ring = MG_LM_STAGES * a.LM.TN * a.LM.box_rows;
+	auto up = [](int v) { return (v + 1023) & ~1023; };
+	int off = 0;
+	a.off_A = off;
+	off = up(off + a.A.bytes);
+	a.off_C = off;
+	off = up(off + a.C.bytes);
+	a.off_D = off;
+	a.off_E = off + a.Dp.bytes;  // contiguous with D: the lm_head ring overlays both
+	off = up(off + std::max(a.Dp.bytes + a.E.bytes, std::max(ring, 8192 * 4)));
+	a.off_h = off;
+	off = up(off + D * 4);
+	a.off_xs = off;
+	off = up(off + std::max(std::max(D, a.E.kc), std::max(a.A.kc, a.C.kc)) * 4);
+	a.off_red = off;
+	off = up(off + std::max(MG_NWARPS * AT_HD * 4, std::max((qd + 2 * kd) * 4, MG_NWARPS * 128 * 4)));
+	a.off_att = off;
+	off = up(off + (AT_NH + 2) * AT_HD * 4);
+	a.smem_total = off + 1024;
+	if (a.smem_total + 8 * 1024 > smem_max) return fail(TG_ESHAPE, "persistent kernel does not fit in shared memory");
+	if (L > MG_MAX_LAYERS || D > 3 * MG_THREADS || a.A.nsplit > 8 || std::max(a.att_local, a.att_global) * 8 * 4 > (AT_NH + 2) * AT_HD * 4)
+		return fail(TG_ESHAPE, "persistent kernel limits exceeded");
+	if ((a.Dp.bytes % 16) || (a.off_E % 128)) return fail(TG_ESHAPE, "region alignment");
+
+	// tensor maps: 7 per layer + lm_head
+	std::vector<CUtensorMap> maps(size_t(7) * L + 1);
+	std::vector<MgLayer> lys(L);
+	for (int l = 0; l < L; l++) {
+		const LayerW &w = m->layers[l];
+		MgLayer &ly = lys[l];
+		const int b = 7 * l;
+		TG_TRY(make_tmap(&maps[b + 0], w.Q.q, D, qd, a.A.TN, a.A.box_rows));
+		TG_TRY(make_tmap(&maps[b + 1], w.K.q, D, kd, a.A.TN, a.A.box_rows));
+		TG_TRY(make_tmap(&maps[b + 2], w.V.q, D, kd, a.A.TN, a.A.box_rows));
+		TG_TRY(make_tmap(&maps[b + 3], w.O.q, qd, D, a.C.TN, a.C.box_rows));
+		TG_TRY(make_tmap(&maps[b + 4], w.U.q, D, I, a.Dp.TN, a.Dp.box_rows));
+		TG_TRY(make_tmap(&maps[b + 5], w.G.q, D, I, a.Dp.TN, a.Dp.box_rows));
+		TG_TRY(make_tmap(&maps[b + 6], w.Dn.q, I, D, a.E.TN, a.E.box_rows));
+		ly.tm_q = b + 0;
+		ly.tm_k = b + 1;
+		ly.tm_v = b + 2;
+		ly.tm_o = b + 3;
+		ly.tm_u = b + 4;
+		ly.tm_g = b + 5;
+		ly.tm_d = b + 6;
+		ly.sq = w.Q.s;
+		ly.sk = w.K.s;
+		ly.sv = w.V.s;
+		ly.so = w.O.s;
+		ly.su = w.U.s;
+		ly.sg = w.G.s;
+		ly.sd = w.Dn.s;
+		ly.rmsq = w.rmsq;
+		ly.rmsk = w.rmsk;
+		ly.attn_pre = w.attn_pre;
+		ly.attn_post = w.attn_post;
+		ly.mlp_pre = w.mlp_pre;
+		ly.mlp_post = w.mlp_post;
+		ly.kcache = s->kcache[l];
+		ly.vcache = s->vcache[l];
+		ly.slots = s->slots[l];
+		ly.is_local = w.is_local ? 1 : 0;
+	}
+	TG_TRY(make_tmap(&maps[size_t(7) * L], m->lm_head.q, D, V, a.LM.TN, a.LM.box_rows));
+	a.tm_lm = 7 * L;
+	TG_CUDA(cudaMalloc(&s->d_tmaps, maps.size() * sizeof(CUtensorMap)));
+	TG_CUDA(cudaMemcpy(s->d_tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+	TG_CUDA(cudaMalloc(&s->d_layers, lys.size() * sizeof(MgLayer)));
+	TG_CUDA(cudaMemcpy(s->d_layers, lys.data(), lys.size() * sizeof(MgLayer), cudaMemcpyHostToDevice));
+	auto allocz = [&](void **p, size_t bytes) -> int {
+		TG_CUDA(cudaMalloc(p, bytes));
+		TG_CUDA(cudaMemset(*p, 0, bytes));
+		return TG_OK;
+	};
+	TG_TRY(allocz((void **)&s->mg_part_A, size_t(a.A.nsplit) * (qd + 2 * kd) * 4));
+	TG_TRY(allocz((void **)&s->mg_part_C, size_t(a.C.nsplit) * D * 4));
+	TG_TRY(allocz((void **)&s->mg_part_E, size_t(a.E.nsplit) * D * 4));
+	TG_TRY(allocz((void **)&s->mg_samp_f, size_t(3) * G * 4));
+	TG_TRY(allocz((void **)&s->mg_samp_i, size_t(G + 8) * 4));
+	TG_TRY(allocz((void **)&s->mg_bar, 64));
+	// attention partials: reuse the state's buffer if it is large enough
+	if (std::max(a.att_local, a.att_global) > std::max(s->attn_nsplit_local, s->attn_nsplit_global)) {
+		cudaFree(s->attn_part);
+		s->attn_part = nullptr;
+		TG_TRY(allocz((void **)&s->attn_part, size_t(s->B) * MG_MAX_ATT * (AT_NH * AT_HD + 8) * 4));
+	}
+	a.tmaps = s->d_tmaps;
+	a.layers = s->d_layers;
+	a.L = L;
+	a.D = D;
+	a.I = I;
+	a.V = V;
+	a.QD = qd;
+	a.KD = kd;
+	a.lm_scale = m->lm_head.s;
+	a.final_norm = m->final_norm;
+	a.wte = m->wte;
+	a.wte_s = m->wte_s;
+	a.sqrtD = float(std::sqrt(double(D)));
+	a.part_A = s->mg_part_A;
+	a.part_C = s->mg_part_C;
+	a.part_E = s->mg_part_E;
+	a.attn_part = s->attn_part;
+	a.act = s->act;
+	a.logits = s->logits;
+	a.samp_f = s->mg_samp_f;
+	a.samp_i = s->mg_samp_i;
+	a.xnorm_out = s->xnorm;
+	a.bar = s->mg_bar;
+	a.err = s->err_flag;
+	a.tok = s->tok;
+	a.next_pos = s->next_pos;
+	a.ring_base = s->ring_base;
+	a.log_count = s->log_count;
+	a.randf_count = s->randf_count;
+	TG_CUDA(cudaFuncSetAttribute(mega_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, a.smem_total));
+	int per_sm = 0;
+	TG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_decode_kernel, MG_THREADS, a.smem_total));
+	if (per_sm < 1 || G > per_sm * g_num_sms) return fail(TG_ESHAPE, "persistent kernel cannot be co-resident");
+	s->mega_grid = G;
+	s->mega_smem = a.smem_total;
+	s->mega_ok = true;
+	if (env_int("TG_MEGA_VERBOSE", 0))
+		fprintf(stderr,
+		        "[tg] mega plan: A TN%d x%d kc%d (%d units)  C TN%d x%d kc%d (%d)  D TN%d (%d)  E TN%d x%d kc%d (%d)  "
+		        "LM box %d  smem %d B  grid %d\n",
+		        a.A.TN, a.A.nsplit, a.A.kc, a.A.units, a.C.TN, a.C.nsplit, a.C.kc, a.C.units, a.Dp.TN, a.Dp.units, a.E.TN,
+		        a.E.nsplit, a.E.kc, a.E.units, a.LM.box_rows, a.smem_total, G);
+	return TG_OK;
+}
+
+// one cooperative launch: n_steps tokens; sampler 0 none / 1 argmax / 2 min-p
+int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, bool log_tokens) {
+	tg_model *m = s->m;
+	MgArgs a = s->mega;
+	a.rope[0][0] = m->rope[0][0];
+	a.rope[0][1] = m->rope[0][1];
+	a.rope[1][0] = m->rope[1][0];
+	a.rope[1][1] = m->rope[1][1];
+	a.lut = make_lut(m);
+	a.n_steps = n_steps;
+	a.sampler = sampler;
+	a.minp = minp;
+	a.temp = temp;
+	a.randf = s->randf;
+	a.randf_cap = s->randf_cap;
+	a.tok_log = log_tokens ? s->tok_log : nullptr;
+	a.log_cap = s->log_cap;
+	a.dbg = s->mg_dbg;
+	a.dbg_cap = s->mg_dbg ? 4096 : 0;
+	TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
+	void *params[] = {&a};
+	TG_CUDA(cudaLaunchCooperativeKernel((void *)mega_decode_kernel, dim3(s->mega_grid), dim3(MG_THREADS), params,
+	                                    s->mega_smem, s->stream));
+	count_launch();
+	return check_launch("mega_decode");
+}
+
 SampleArgs sample_args(tg_state *s, float minp, float temp, bool log_tokens) {
 	SampleArgs a{};
 	a.logits = s->logits;
@@ -615,7 +877,9 @@ int check_err_flag(tg_state *s) {
 	flag = s->host_pin[8192];
 	if (flag) {
 		cudaMemsetAsync(s->err_flag, 0, 4, s->stream);
-		return fail(TG_EINVAL, flag == 1 ? "token id out of range" : "global KV cache full (max_pos_global reached)");
+		if (flag == 1) return fail(TG_EINVAL, "token id out of range");
+		if (flag == 2) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
+		return fail(TG_ECUDA, flag == 3 ? "persistent kernel: a TMA wait ran out" : "persistent kernel: a grid barrier wait ran out");
 	}
 	return TG_OK;
 }
@@ -942,6 +1206,13 @@ int tg_state_create(tg_model *m, int batch, int max_pos_global, tg_state **out) 
 	s->B = batch;
 	s->max_pos_global = max_pos_global;
 	int rc = state_alloc(s);
+	if (rc == TG_OK && batch == 1 && env_int("TG_MEGA", 1)) {
+		int mrc = mega_setup(s);
+		if (mrc != TG_OK) {
+			if (env_int("TG_MEGA", 1) == 2) rc = mrc;  // 2 = required
+			s->mega_ok = false;
+		}
+	}
 	if (rc != TG_OK) {
 		std::string keep = g_err;
 		tg_state_free(s);
@@ -982,6 +1253,15 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->err_flag);
 	cudaFree(s->pf);
 	cudaFree(s->pf_ids);
+	cudaFree(s->d_tmaps);
+	cudaFree(s->d_layers);
+	cudaFree(s->mg_part_A);
+	cudaFree(s->mg_part_C);
+	cudaFree(s->mg_part_E);
+	cudaFree(s->mg_samp_f);
+	cudaFree(s->mg_samp_i);
+	cudaFree(s->mg_bar);
+	cudaFree(s->mg_dbg);
 	if (s->host_pin) cudaFreeHost(s->host_pin);
 	if (s->stream) cudaStreamDestroy(s->stream);
 	delete s;
@@ -1078,7 +1358,10 @@ int tg_decode(tg_state *s, const int *ids, float *logits_host) {
 		std::memcpy(s->host_pin, ids, 4 * s->B);
 		TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
 	}
-	TG_TRY(enqueue_decode_step(s));
+	if (s->mega_ok)
+		TG_TRY(mega_launch(s, 1, 0, 2.0f, 1.0f, false));
+	else
+		TG_TRY(enqueue_decode_step(s));
 	if (logits_host)
 		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, s->stream));
 	TG_TRY(check_err_flag(s));
@@ -1139,9 +1422,13 @@ int tg_generate_async(tg_state *s, int n_steps, float minp, float temp) {
 	if (minp < 1.0f && s->randf_cap < n_steps) return fail(TG_ESTATE, "upload uniforms first (tg_state_set_randf)");
 	TG_TRY(ensure_log(s, n_steps));
 	TG_CUDA(cudaMemsetAsync(s->log_count, 0, 4 * s->B, s->stream));
-	for (int i = 0; i < n_steps; i++) {
-		TG_TRY(enqueue_decode_step(s));
-		TG_TRY(enqueue_sampler(s, minp, temp, true));
+	if (s->mega_ok) {
+		TG_TRY(mega_launch(s, n_steps, minp < 1.0f ? 2 : 1, minp, temp, true));
+	} else {
+		for (int i = 0; i < n_steps; i++) {
+			TG_TRY(enqueue_decode_step(s));
+			TG_TRY(enqueue_sampler(s, minp, temp, true));
+		}
 	}
 	for (int b = 0; b < s->B; b++) s->host_pos[b] += n_steps;
 	return TG_OK;
@@ -1366,6 +1653,26 @@ int tg_rmsnorm(float *x, const float *w, int rows, int dim) {
 	count_launch();
 	TG_TRY(check_launch("rmsnorm"));
 	TG_CUDA(cudaMemcpy(x, dx.p, size_t(rows) * dim * 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_state_phase_clocks(tg_state *s, long long *clocks_host, int cap, int *n) {
+	if (!s || !n) return fail(TG_EINVAL, "null argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	if (!s->mg_dbg) {  // first call arms the recorder; later launches fill it
+		TG_CUDA(cudaMalloc(&s->mg_dbg, 4096 * sizeof(long long)));
+		TG_CUDA(cudaMemset(s->mg_dbg, 0, 4096 * sizeof(long long)));
+		*n = 0;
+		return TG_OK;
+	}
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	std::vector<long long> tmp(4096);
+	TG_CUDA(cudaMemcpy(tmp.data(), s->mg_dbg, 4096 * sizeof(long long), cudaMemcpyDeviceToHost));
+	int k = 0;
+	while (k < 4096 && tmp[k] != 0) k++;
+	*n = k;
+	if (clocks_host) std::memcpy(clocks_host, tmp.data(), sizeof(long long) * std::min(k, cap));
+	TG_CUDA(cudaMemset(s->mg_dbg, 0, 4096 * sizeof(long long)));
 	return TG_OK;
 }
 
