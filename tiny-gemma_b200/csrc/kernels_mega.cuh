@@ -83,7 +83,8 @@ struct MgArgs {
 	// L2-resident exchange buffers
 	float *part_A, *part_C, *part_E;  // [nsplit][N] partial sums
 	float *attn_part;                 // [MG_MAX_ATT][4*256 + 8]
-	float *act;                       // [I]
+	uint2 *act;                       // [I] {value bits, sequence tag}: flag-carrying hand-off D -> E
+	unsigned seq0;                    // sequence tags used by this launch start above seq0
 	float *logits;                    // [V]
 	float *samp_f;                    // [3][grid] sampler partials
 	int *samp_i;                      // [grid]
@@ -151,6 +152,18 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
 	unsigned v;
 	asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
 	return v;
+}
+
+// Flag-carrying hand-off: the producer stores {value, tag} as one 8-byte word; the
+// consumer polls the word itself until the tag is the one it expects. No fence,
+// no counter: the data is its own ready flag (8-byte stores are single-copy atomic).
+__device__ __forceinline__ void st_flagged(uint2 *p, float v, unsigned tag) {
+	asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_flagged(const uint2 *p) {
+	uint2 r;
+	asm volatile("ld.relaxed.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+	return r;
 }
 
 struct MgCtx {
@@ -905,6 +918,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				MG_STAMP();
 			}
 			// ============================================================ D: up & gate + GeGLU
+			const unsigned tag = a.seq0 + unsigned(step) * unsigned(L) + unsigned(l) + 1u;
 			{
 				const bool active = cta < a.Dp.units;
 				mg_resnorm(a, h, xs, bred, true, a.part_C, a.C.nsplit, vD, nullptr);
@@ -915,14 +929,13 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					const float up = mg_tile_colsum(R_D, D, a.Dp.segs, xs, red);
 					MG_STAMP();
 					const float gate = mg_tile_colsum(R_D + a.Dp.TN * D, D, a.Dp.segs, xs, red);
-					if (tid < a.Dp.TN) __stcg(a.act + cta * a.Dp.TN + tid, a.lut(gate * sg_r) * (up * su_r));
+					if (tid < a.Dp.TN) st_flagged(a.act + cta * a.Dp.TN + tid, a.lut(gate * sg_r) * (up * su_r), tag);
 				}
 				pD ^= 1;
 				MG_STAMP();
-				MgBar gb;
-				mg_arrive(ctx, gb);
+				// no grid barrier here: phase E polls the tagged activations it needs
+				__syncthreads();
 				if (warp == 1 && l + 1 < L) mg_issue_D(a, s_ly, l + 1, cta, R_D, &bar_D, pol);
-				mg_wait(ctx, gb);
 				MG_STAMP();
 			}
 			// ============================================================ E: down projection
@@ -932,7 +945,20 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				const int k0 = split * a.E.kc;
 				if (active) {
 #pragma unroll 1
-					for (int r = tid; r < a.E.kc; r += MG_THREADS) xs[r] = __ldcg(a.act + k0 + r);
+#pragma unroll 1
+					for (int r = tid; r < a.E.kc; r += MG_THREADS) {
+						uint2 w = ld_flagged(a.act + k0 + r);
+						int spins = 0;
+						while (w.y != tag && !*(volatile int *)&s_abort) {
+							if (++spins > MG_SPIN_CAP) {
+								s_abort = 1;
+								atomicExch(a.err, 5);
+								break;
+							}
+							w = ld_flagged(a.act + k0 + r);
+						}
+						xs[r] = __uint_as_float(w.x);
+					}
 					__syncthreads();
 					mg_wait_tma(ctx, &bar_E, pE);
 					MG_STAMP();

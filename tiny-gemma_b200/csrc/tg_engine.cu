@@ -295,6 +295,8 @@ struct tg_state {
 	float *mg_part_A = nullptr, *mg_part_C = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr;
 	int *mg_samp_i = nullptr;
 	unsigned *mg_bar = nullptr;
+	uint2 *mg_act = nullptr;
+	unsigned mg_seq = 0;  // sequence tags consumed so far by flag-carrying hand-offs
 	int mega_grid = 0;
 	long long *mg_dbg = nullptr;
 	size_t mega_smem = 0;
@@ -763,6 +765,7 @@ int mega_setup(tg_state *s) {
 	TG_TRY(allocz((void **)&s->mg_samp_f, size_t(3) * G * 4));
 	TG_TRY(allocz((void **)&s->mg_samp_i, size_t(G + 8) * 4));
 	TG_TRY(allocz((void **)&s->mg_bar, 64));
+	TG_TRY(allocz((void **)&s->mg_act, size_t(I) * sizeof(uint2)));
 	// attention partials: reuse the state's buffer if it is large enough
 	if (std::max(a.att_local, a.att_global) > std::max(s->attn_nsplit_local, s->attn_nsplit_global)) {
 		cudaFree(s->attn_part);
@@ -786,7 +789,7 @@ int mega_setup(tg_state *s) {
 	a.part_C = s->mg_part_C;
 	a.part_E = s->mg_part_E;
 	a.attn_part = s->attn_part;
-	a.act = s->act;
+	a.act = s->mg_act;
 	a.logits = s->logits;
 	a.samp_f = s->mg_samp_f;
 	a.samp_i = s->mg_samp_i;
@@ -831,6 +834,8 @@ int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, b
 	a.randf_cap = s->randf_cap;
 	a.tok_log = log_tokens ? s->tok_log : nullptr;
 	a.log_cap = s->log_cap;
+	a.seq0 = s->mg_seq;
+	s->mg_seq += unsigned(n_steps) * unsigned(m->cfg.n_layers) + 1u;
 	a.dbg = s->mg_dbg;
 	a.dbg_cap = s->mg_dbg ? 4096 : 0;
 	TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
@@ -1261,6 +1266,7 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->mg_samp_f);
 	cudaFree(s->mg_samp_i);
 	cudaFree(s->mg_bar);
+	cudaFree(s->mg_act);
 	cudaFree(s->mg_dbg);
 	if (s->host_pin) cudaFreeHost(s->host_pin);
 	if (s->stream) cudaStreamDestroy(s->stream);
