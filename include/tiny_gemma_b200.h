@@ -164,6 +164,19 @@ int tg_rmsnorm(float *x_host, const float *w_host, int rows, int dim);
 /* ---- device-pointer variants (data already in HBM; used for kernel timing) */
 int tg_dev_qmatvec(float *y_dev, const float *x_dev, const int8_t *w_dev, const float *scales_dev, int K, int N,
                    void *cuda_stream);
+/* Same operator as tg_dev_qmatvec for callers that must not allocate device memory when they
+ * call it: processes that hand all of HBM to their own pools, latency-critical loops that cannot
+ * afford the allocator's implicit synchronisation, code running under stream capture. It has no
+ * counterpart in the reference. The split-K partial sums and tile tickets live in a fixed
+ * 264 KiB array inside the library (held by every GPU that loads it until exit) instead of
+ * buffers grown with cudaMalloc; the call makes no cudaMalloc / cudaFree. Limits: N <= 262144
+ * and nsplit * N <= 65536 partial sums (the split is chosen to fit); larger sizes are rejected
+ * with TG_EINVAL. The first call on a device looks up the array's device address (with that
+ * device current) and should therefore be made before any stream capture. All calls share the
+ * array — it is cleared where it must start at zero — so two calls that overlap on the GPU
+ * (different streams) race; serialise them. */
+int tg_dev_qmatvec_static(float *y_dev, const float *x_dev, const int8_t *w_dev, const float *scales_dev, int K, int N,
+                          void *cuda_stream);
 int tg_dev_qgemm(float *c_dev, const float *a_dev, const int8_t *w_dev, const float *scales_dev, int M, int K, int N,
                  void *cuda_stream);
 

@@ -63,6 +63,7 @@ SIGNATURES = {
     "tg_minp_logits": (C.c_int, [_P, C.c_int, C.c_float, C.c_float, C.c_float, C.POINTER(C.c_int)]),
     "tg_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int]),
     "tg_dev_qmatvec": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
+    "tg_dev_qmatvec_static": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "tg_dev_qgemm": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "tg_launch_count": (C.c_int, [C.c_int, C.POINTER(C.c_longlong)]),
     "tg_state_stream": (C.c_int, [_P, C.POINTER(_P)]),

@@ -172,12 +172,12 @@ struct MvPlan {
 
 // Pick the K-split so that the launch fills the GPU in whole waves. kc must be a
 // multiple of 32 rows and divide K.
-MvPlan plan_matvec(int K, int ntiles, int target_ctas) {
+MvPlan plan_matvec(int K, int ntiles, int target_ctas, int max_split = 1 << 30) {
 	MvPlan best{1, K, ntiles};
 	if (ntiles >= target_ctas) return best;
 	double best_score = -1e9;
 	const int units = K / 32;
-	for (int ns = 1; ns <= units; ns++) {
+	for (int ns = 1; ns <= units && ns <= max_split; ns++) {
 		if (units % ns) continue;
 		int ctas = ntiles * ns;
 		int waves = (ctas + g_num_sms - 1) / g_num_sms;
@@ -1523,6 +1523,73 @@ int tg_dev_qmatvec(float *y, const float *x, const int8_t *w, const float *scale
 	a.x = x;
 	a.partial = partial[dev];
 	a.tickets = tickets[dev];
+	a.out = y;
+	return launch_mv(a, PRO_PLAIN, EPI_SCALE, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------- matvec that allocates nothing
+// Some hosts of this library must not call cudaMalloc on the request path: a
+// serving process that pre-reserves all of HBM for its own pools, a real-time
+// loop that cannot take the allocator's implicit device synchronisation, or code
+// that runs while a stream is being captured into a CUDA graph, where cudaMalloc
+// is illegal. tg_dev_qmatvec grows two device buffers on demand (split-K partial
+// sums and column-tile tickets); this variant keeps them in the fixed array
+// below instead. The array is part of the library image: every GPU that loads
+// the library holds these 264 KiB until the process exits.
+constexpr int STATIC_MAX_TILES = 2048;                 // N <= 262144 columns
+constexpr size_t STATIC_PARTIAL_FLOATS = 64 * 1024;    // nsplit * N <= 65536 partial sums
+constexpr size_t STATIC_TICKET_BYTES = STATIC_MAX_TILES * sizeof(unsigned);
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_TICKET_BYTES + STATIC_PARTIAL_FLOATS * sizeof(float)];
+
+int tg_dev_qmatvec_static(float *y, const float *x, const int8_t *w, const float *scales, int K, int N, void *stream) {
+	if (!y || !x || !w || !scales) return fail(TG_EINVAL, "null argument");
+	if (N > STATIC_MAX_TILES * MV_TN)
+		return fail(TG_EINVAL, "N = " + std::to_string(N) + " is beyond the static scratch maximum of " +
+		                           std::to_string(STATIC_MAX_TILES * MV_TN) + " columns");
+	if (!supported_k(K)) return fail(TG_ESHAPE, "Unsupported ROW dimension: " + std::to_string(K));
+	if (!supported_n(N)) return fail(TG_ESHAPE, "Unsupported COL dimension: " + std::to_string(N));
+	// Set-up, once per device and with that device current: in host code the array's name is only
+	// a stand-in for the device symbol, so its device address is asked for here and that pointer
+	// is what the kernel gets. This first call per device should come before any stream capture.
+	static unsigned char *scratch_dev[64] = {nullptr};
+	static int sms_dev[64] = {0};
+	int dev = 0;
+	TG_CUDA(cudaGetDevice(&dev));
+	if (dev < 0 || dev >= 64) return fail(TG_EINVAL, "device index out of range");
+	if (!scratch_dev[dev]) {
+		unsigned char *ptr = nullptr;
+		cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_static_scratch);
+		if (e != cudaSuccess || !ptr) return fail(TG_ECUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+		int sms = 0;
+		TG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+		sms_dev[dev] = sms > 0 ? sms : 148;
+		scratch_dev[dev] = ptr;
+	}
+	g_num_sms = sms_dev[dev];
+	// the K-split is capped so that the partial sums fit the fixed array
+	const int max_split = int(STATIC_PARTIAL_FLOATS / size_t(N)) > 0 ? int(STATIC_PARTIAL_FLOATS / size_t(N)) : 1;
+	MvPlan p = plan_matvec(K, N / MV_TN, 2 * g_num_sms, max_split);
+	if (p.nsplit > 1 && size_t(p.nsplit) * N > STATIC_PARTIAL_FLOATS)
+		return fail(TG_EINVAL, "split-K partial sums exceed the static scratch maximum of " +
+		                           std::to_string(STATIC_PARTIAL_FLOATS) + " floats");
+	unsigned *tickets = reinterpret_cast<unsigned *>(scratch_dev[dev]);
+	float *partial = reinterpret_cast<float *>(scratch_dev[dev] + STATIC_TICKET_BYTES);
+	// every call shares the array and finds the previous call's contents in it: the tickets must
+	// start at zero (the partial sums are fully overwritten before they are read)
+	TG_CUDA(cudaMemsetAsync(tickets, 0, sizeof(unsigned) * size_t(N / MV_TN), (cudaStream_t)stream));
+	MvArgs a{};
+	a.seg[0] = MvSeg{w, scales, N, 0, 0};
+	a.nseg = 1;
+	a.ntiles = N / MV_TN;
+	a.K = K;
+	a.kc = p.kc;
+	a.nsplit = p.nsplit;
+	a.B = 1;
+	a.part_stride = N;
+	a.out_stride = N;
+	a.x = x;
+	a.partial = partial;
+	a.tickets = tickets;
 	a.out = y;
 	return launch_mv(a, PRO_PLAIN, EPI_SCALE, (cudaStream_t)stream);
 }
