@@ -47,6 +47,9 @@ MINP, TEMP, SAMPLER_SEED = 0.1, 0.7, 1234
 WEIGHT_SEED, PROMPT_SEED = 0, 77
 CACHE = os.environ.get("TG_CACHE_DIR", "/tmp")
 PUBLISHED_DECODE_TOK_S = 16.45  # reference README.md:69, Ryzen 5 5500, 1 thread, real weights
+# dram__bytes_read.sum + dram__bytes_write.sum per decoded token from one ncu capture of the decode kernel
+# (profiles/mega_decode_kernel_1B_dram_traffic.md, profiles/mega_decode_kernel_270m_ncu_full.md)
+DRAM_TRAFFIC_PER_STEP = {"1B": 1005218304, "270m": 273278037}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -171,7 +174,7 @@ def run_reference(args):
         "impl": "reference", "metric": "decode_tok_s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": K, "warmup": W, "ms_per_step": 1e3 * dt / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": v / PUBLISHED_DECODE_TOK_S, "dtype": "int8w/f32", "data": "synthetic",
-        "config": {"workload": "gemma3-1B int8 weight-only, batch 1, 178-token random prompt, min-p 0.1 temp 0.7 decode",
+        "config": {"workload": "gemma3-%s int8 weight-only, batch 1, 178-token random prompt, min-p 0.1 temp 0.7 decode" % MODEL,
                    "model_size": MODEL, "prompt_len": PROMPT_LEN, "batch": 1},
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": 1, "kind": kind,
                          "sample": "%d decode steps after a %d-token prefill, single thread (the reference is "
@@ -361,8 +364,8 @@ def run_ours(args):
         "metric": "decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": dev_ms_max / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": value / PUBLISHED_DECODE_TOK_S, "dtype": "int8w/f32", "data": "synthetic",
-        "config": {"workload": "gemma3-1B int8 weight-only, batch 1 per GPU, 178-token random prompt, min-p 0.1 "
-                               "temp 0.7 decode", "model_size": MODEL, "prompt_len": PROMPT_LEN, "batch_per_gpu": 1,
+        "config": {"workload": "gemma3-%s int8 weight-only, batch 1 per GPU, 178-token random prompt, min-p 0.1 "
+                               "temp 0.7 decode" % MODEL, "model_size": MODEL, "prompt_len": PROMPT_LEN, "batch_per_gpu": 1,
                    "parallelism": "replica-dp%d (independent sequences, no collective)" % world,
                    "l2": "inputs larger than L2: every step streams 1.0 GB of weights through a 126 MB L2",
                    "timing": "CUDA events on the launching stream, max over ranks"},
@@ -371,8 +374,8 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "clocks": clk,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
-                     "what": "one decode step (CUDA graph of the per-token kernels + sampler)",
+                     "frac": achieved / hbm_peak, "traffic": DRAM_TRAFFIC_PER_STEP.get(MODEL), "peak_kind": peak_kind,
+                     "what": "one decode step of the persistent decode kernel (forward + sampler)",
                      "algorithmic_bytes_per_token": alg, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS},
         "prefill_tok_s": world * PROMPT_LEN / (prefill_ms_max / 1e3),
         "prefill_ms": prefill_ms_max,
@@ -403,7 +406,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the matvec sweep and the CPU baseline sample")
+    ap.add_argument("--model", default=MODEL, choices=["270m", "1B"],
+                    help="architecture; 1B is the benchmark configuration, 270m is the small case used for profiling")
     args = ap.parse_args()
+    globals()["MODEL"] = args.model
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
