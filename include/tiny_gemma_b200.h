@@ -180,6 +180,22 @@ int tg_dev_qmatvec_static(float *y_dev, const float *x_dev, const int8_t *w_dev,
 int tg_dev_qgemm(float *c_dev, const float *a_dev, const int8_t *w_dev, const float *scales_dev, int M, int K, int N,
                  void *cuda_stream);
 
+/* ---- vocab-sharded lm_head (multi-GPU variant) --------------------------- */
+/* The reference scores the whole vocabulary in modules::lm_head (modules.hpp:223-247) and takes
+ * the argmax (ops.hpp:744). With the [D, V] lm_head split by columns over several GPUs, each GPU
+ * (1) runs the layers for its own sequences and stops before the lm_head (tg_decode_hidden; the
+ * final-normed hidden states stay in HBM, tg_dev_hidden_copy copies them out [batch, D]),
+ * (2) after the hidden states of all GPUs have been gathered, scores M of them against its own
+ * column slice [col0, col0 + ncols) and returns per row the maximum logit and its global index,
+ * lowest index on ties (tg_dev_lm_head_top1), and (3) after the per-slice candidates have been
+ * gathered and resolved, takes the tokens of its own sequences back (tg_dev_set_tokens). The two
+ * gathers are the caller's (NCCL). col0 and ncols must be multiples of 128. */
+int tg_decode_hidden(tg_state *s, const int *ids_host);
+int tg_dev_hidden_copy(tg_state *s, float *dst_dev);
+int tg_dev_lm_head_top1(tg_model *m, const float *hidden_dev, int M, int col0, int ncols, float *max_dev, int *idx_dev,
+                        void *cuda_stream);
+int tg_dev_set_tokens(tg_state *s, const int *toks_dev);
+
 /* ---- introspection for benchmarks --------------------------------------- */
 /* number of kernels this library launched since the last call with reset != 0 */
 int tg_launch_count(int reset, long long *count);

@@ -65,6 +65,10 @@ SIGNATURES = {
     "tg_dev_qmatvec": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "tg_dev_qmatvec_static": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "tg_dev_qgemm": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "tg_decode_hidden": (C.c_int, [_P, _P]),
+    "tg_dev_hidden_copy": (C.c_int, [_P, _P]),
+    "tg_dev_lm_head_top1": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),
+    "tg_dev_set_tokens": (C.c_int, [_P, _P]),
     "tg_launch_count": (C.c_int, [C.c_int, C.POINTER(C.c_longlong)]),
     "tg_state_stream": (C.c_int, [_P, C.POINTER(_P)]),
     "tg_generate_async": (C.c_int, [_P, C.c_int, C.c_float, C.c_float]),
@@ -201,6 +205,10 @@ class Model:
         _ck(self.lib.tg_model_build_tables(self.h, gelu_size))
         return self
 
+    def lm_head_top1_dev(self, hidden_ptr: int, M: int, col0: int, ncols: int, max_ptr: int, idx_ptr: int, stream: int = 0):
+        _ck(self.lib.tg_dev_lm_head_top1(self.h, C.c_void_p(hidden_ptr), M, col0, ncols, C.c_void_p(max_ptr),
+                                         C.c_void_p(idx_ptr), C.c_void_p(stream)))
+
     def state(self, batch: int = 1, max_pos_global: int = 0) -> "State":
         return State(self, batch, max_pos_global)
 
@@ -282,6 +290,17 @@ class State:
         n = C.c_int(0)
         _ck(self.lib.tg_state_phase_clocks(self.h, _ptr(out), out.size, C.byref(n)))
         return out[:n.value]
+
+    def decode_hidden(self, ids=None):
+        if ids is not None:
+            ids = np.ascontiguousarray(ids, np.int32).reshape(self.B)
+        _ck(self.lib.tg_decode_hidden(self.h, _ptr(ids)))
+
+    def hidden_copy_dev(self, dst_ptr: int):
+        _ck(self.lib.tg_dev_hidden_copy(self.h, C.c_void_p(dst_ptr)))
+
+    def set_tokens_dev(self, toks_ptr: int):
+        _ck(self.lib.tg_dev_set_tokens(self.h, C.c_void_p(toks_ptr)))
 
     def stream(self) -> int:
         p = C.c_void_p()

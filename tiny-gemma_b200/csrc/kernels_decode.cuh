@@ -350,6 +350,33 @@ __global__ void __launch_bounds__(MV_THREADS) qmatvec_kernel(MvArgs a) {
 	}
 }
 
+// =========================================================== final hidden state
+// x = rmsnorm(h + rmsnorm(t; w_post); w_final) per sequence — the prologue of
+// the lm_head (reference modules.hpp:242-246) as a kernel of its own, for callers
+// that score the vocabulary elsewhere (vocab-sharded lm_head). One CTA per sequence.
+__global__ void __launch_bounds__(256) final_hidden_kernel(float *x_out, const float *h, const float *t, const float *w_post,
+                                                           const float *w_final, int D) {
+	__shared__ float bred[8];
+	extern __shared__ float hs[];
+	const int b = blockIdx.x, tid = threadIdx.x;
+	float ss = 0.0f;
+	for (int d = tid; d < D; d += 256) {
+		float v = t[size_t(b) * D + d];
+		ss = fmaf(v, v, ss);
+	}
+	ss = block_sum<8>(ss, bred);
+	const float r1 = inv_rms(ss, D);
+	float ss2 = 0.0f;
+	for (int d = tid; d < D; d += 256) {
+		float v = h[size_t(b) * D + d] + (t[size_t(b) * D + d] * r1) * (w_post[d] + 1.0f);
+		hs[d] = v;
+		ss2 = fmaf(v, v, ss2);
+	}
+	ss2 = block_sum<8>(ss2, bred);
+	const float r2 = inv_rms(ss2, D);
+	for (int d = tid; d < D; d += 256) x_out[size_t(b) * D + d] = (hs[d] * r2) * (w_final[d] + 1.0f);
+}
+
 // =========================================================== attention (decode)
 // Per sequence and layer: q/k RMSNorm (per head), RoPE at the token's position,
 // KV append into the (ring) cache, then one query against every valid cache

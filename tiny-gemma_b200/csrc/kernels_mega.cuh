@@ -131,7 +131,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 	    : "memory");
 	return ok != 0;
 }
-// 2-D tiled TMA load, no multicast: box at (x = byte column, y = row) -> dst, completes on bar.
+// 2-D tiled TMA load into this CTA only (never cluster-wide): box at (x = byte column, y = row) -> dst, completes on bar.
 // Weights are read once per token, so they carry an L2 evict-first policy and
 // leave the L2 to the KV cache and the small exchange vectors.
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {

@@ -390,7 +390,7 @@ int check_ready(const tg_model *m) {
 // layer: QKV matvec (norm prologue) -> attention -> O matvec -> gate/up matvec
 // (residual+norm prologue, GeGLU epilogue) -> down matvec; then the lm_head
 // matvec with the last residual+norm prologue.
-int enqueue_decode_chunk(tg_state *s, int b0, int nb) {
+int enqueue_decode_chunk(tg_state *s, int b0, int nb, bool with_lm_head = true) {
 	tg_model *m = s->m;
 	const tg_config &c = m->cfg;
 	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
@@ -529,6 +529,13 @@ int enqueue_decode_chunk(tg_state *s, int b0, int nb) {
 			a.out = s->t + size_t(b0) * D;
 			TG_TRY(launch_mv(a, PRO_PLAIN, EPI_SCALE, st));
 		}
+	}
+	if (!with_lm_head) {
+		final_hidden_kernel<<<nb, 256, size_t(D) * 4, st>>>(s->xnorm + size_t(b0) * D, s->h[cur] + size_t(b0) * D,
+		                                                    s->t + size_t(b0) * D, m->layers[c.n_layers - 1].mlp_post,
+		                                                    m->final_norm, D);
+		count_launch();
+		return check_launch("final_hidden");
 	}
 	// ---- lm_head (final residual add + final norm in the prologue)
 	{
@@ -1482,6 +1489,88 @@ int tg_hidden_read(tg_state *s, float *hidden_host) {
 	TG_CUDA(cudaSetDevice(s->m->device));
 	TG_CUDA(cudaMemcpyAsync(hidden_host, s->xnorm, size_t(s->B) * s->m->cfg.hidden_size * 4, cudaMemcpyDeviceToHost, s->stream));
 	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+// ---------------------------------------------------------------- vocab-sharded lm_head support
+int tg_decode_hidden(tg_state *s, const int *ids) {
+	if (!s) return fail(TG_EINVAL, "null state");
+	tg_model *m = s->m;
+	TG_TRY(check_ready(m));
+	TG_CUDA(cudaSetDevice(m->device));
+	for (int b = 0; b < s->B; b++)
+		if (s->host_pos[b] >= s->max_pos_global) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
+	if (ids) {
+		std::memcpy(s->host_pin, ids, 4 * s->B);
+		TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
+	}
+	for (int b0 = 0; b0 < s->B; b0 += MV_MAX_B) TG_TRY(enqueue_decode_chunk(s, b0, std::min(MV_MAX_B, s->B - b0), false));
+	TG_TRY(check_err_flag(s));
+	for (int b = 0; b < s->B; b++) s->host_pos[b] += 1;
+	return TG_OK;
+}
+
+int tg_dev_hidden_copy(tg_state *s, float *dst_dev) {
+	if (!s || !dst_dev) return fail(TG_EINVAL, "null argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	TG_CUDA(cudaMemcpyAsync(dst_dev, s->xnorm, size_t(s->B) * s->m->cfg.hidden_size * 4, cudaMemcpyDeviceToDevice, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+int tg_dev_set_tokens(tg_state *s, const int *toks_dev) {
+	if (!s || !toks_dev) return fail(TG_EINVAL, "null argument");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	TG_CUDA(cudaMemcpyAsync(s->tok, toks_dev, size_t(s->B) * 4, cudaMemcpyDeviceToDevice, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	return TG_OK;
+}
+
+int tg_dev_lm_head_top1(tg_model *m, const float *hidden_dev, int M, int col0, int ncols, float *max_dev, int *idx_dev,
+                        void *stream) {
+	if (!m || !hidden_dev || !max_dev || !idx_dev || M < 1) return fail(TG_EINVAL, "bad argument");
+	const int V = m->cfg.n_vocab, D = m->cfg.hidden_size;
+	if (col0 < 0 || ncols < MV_TN || col0 % MV_TN || ncols % MV_TN || col0 + ncols > V)
+		return fail(TG_EINVAL, "vocabulary slice must be a multiple of 128 columns inside [0, n_vocab)");
+	TG_CUDA(cudaSetDevice(m->device));
+	cudaStream_t st = (cudaStream_t)stream;
+	// logits of up to MV_MAX_B rows at a time over the slice, then their row maxima
+	static float *scratch[64] = {nullptr};
+	static size_t scratch_floats[64] = {0};
+	static unsigned *tickets[64] = {nullptr};
+	const int dev = m->device;
+	const size_t need = size_t(MV_MAX_B) * ncols;
+	if (need > scratch_floats[dev]) {
+		if (scratch[dev]) cudaFree(scratch[dev]);
+		scratch[dev] = nullptr;
+		TG_CUDA(cudaMalloc(&scratch[dev], need * 4));
+		scratch_floats[dev] = need;
+	}
+	if (!tickets[dev]) {
+		TG_CUDA(cudaMalloc(&tickets[dev], sizeof(unsigned) * 2048));
+		TG_CUDA(cudaMemset(tickets[dev], 0, sizeof(unsigned) * 2048));
+	}
+	for (int r0 = 0; r0 < M; r0 += MV_MAX_B) {
+		const int nb = std::min(MV_MAX_B, M - r0);
+		MvArgs a{};
+		a.seg[0] = MvSeg{m->lm_head.q + col0, m->lm_head.s + col0, V, 0, 0};
+		a.nseg = 1;
+		a.ntiles = ncols / MV_TN;
+		a.K = D;
+		a.kc = D;
+		a.nsplit = 1;
+		a.B = nb;
+		a.part_stride = ncols;
+		a.out_stride = ncols;
+		a.x = hidden_dev + size_t(r0) * D;
+		a.partial = nullptr;
+		a.tickets = tickets[dev];
+		a.out = scratch[dev];
+		TG_TRY(launch_mv(a, PRO_PLAIN, EPI_SCALE, st));
+		top1_rows_kernel<<<nb, SM_THREADS, 0, st>>>(scratch[dev], ncols, col0, max_dev + r0, idx_dev + r0);
+		count_launch();
+		TG_TRY(check_launch("top1_rows"));
+	}
 	return TG_OK;
 }
 
