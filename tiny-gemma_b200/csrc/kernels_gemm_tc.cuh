@@ -1,0 +1,330 @@
+// Prefill GEMM on the 5th-generation tensor cores (tcgen05 + TMEM):
+//   C[M,N] = scale[n] * sum_k A[m,k] * W[k,n],  A fp32, W int8 [K,N] row-major
+// (gemm::qgemmnn, reference linalg.hpp:210-308, which runs a full-K fp32 FMA
+// chain per output).
+//
+// fp32 accuracy on bf16 tensor cores: int8 weights are exact in bf16; an fp32
+// activation is split into three bf16 terms x = hi + mid + lo (8 + 8 + 8
+// mantissa bits, each residual computed exactly in fp32), and the three
+// products are accumulated into the same fp32 TMEM accumulator. Every product
+// is exact; only the fp32 accumulation rounds.
+//
+//   split_pack_kernel   A fp32 [M,K] -> three bf16 operands, already in the
+//                       tensor core's shared-memory layout, tile by tile, so
+//                       that a GEMM CTA fetches an operand tile with ONE bulk
+//                       copy.
+//   qgemm_tc_kernel     one CTA = one 128-column tile of W x two 128-row tiles
+//                       of A (M <= 256 per CTA; more rows -> grid.y). Warp
+//                       roles: warp 0 producer (bulk copies of A tiles, TMA of
+//                       the int8 W tile), warp 1 MMA issuer, warps 2-5 convert
+//                       W int8 -> bf16 into the operand layout and run the
+//                       epilogue (TMEM -> registers -> x scale -> C).
+//                       3-stage ring over K in blocks of 32. K may be split over
+//                       gridDim.z CTAs (raw partial sums, added in split order
+//                       and scaled by qgemm_splitk_reduce_kernel): it fills the
+//                       GPU when N/128 is small and keeps the accumulation
+//                       chains short — the tensor core truncates when it adds
+//                       into the fp32 accumulator, so the error grows with the
+//                       chain length (2e-5 at K = 6912 unsplit).
+//
+// Shared-memory operand layout (K-major, no swizzle): 8 x 8 bf16 "core
+// matrices" of 128 contiguous bytes (8 rows of 16 bytes); byte offset of
+// element (r, k) in a [128][32] tile = (r/8)*512 + (k/8)*128 + (r%8)*16 + (k%8)*2,
+// i.e. leading (K) offset 128 B, stride (row-group) offset 512 B.
+//
+// All waits are bounded; a wait that runs out sets *err and the CTA drains and
+// frees its TMEM before returning.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "kernels_mega.cuh"  // mbarrier / TMA helpers
+#include "tg_common.cuh"
+
+namespace tg {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 32;
+constexpr int TC_STAGES = 3;
+constexpr int TC_MT = 2;                       // 128-row tiles of A per CTA
+constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 8 KiB: one [128][32] bf16 operand tile
+constexpr int TC_W_BYTES = TC_BK * TC_BN;         // 4 KiB: int8 W tile
+constexpr int TC_STAGE_BYTES = 3 * TC_MT * TC_TILE_BYTES + TC_W_BYTES + TC_TILE_BYTES;  // A terms + W int8 + B bf16
+constexpr int TC_THREADS = 192;
+constexpr int TC_SPIN_CAP = 1 << 24;
+
+// ------------------------------------------------------------------ split + pack
+// out: [3 terms][m_tiles][k_blocks][TC_TILE_BYTES]; rows >= M are zero.
+__global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bfloat16 *out, int M, int K, int m_tiles) {
+	const int k_blocks = K / TC_BK;
+	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);  // one thread per (row, 8 consecutive k)
+	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
+	for (size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += size_t(gridDim.x) * blockDim.x) {
+		const int row = int(c / (K / 8)), k8 = int(c % (K / 8));
+		float x[8];
+		if (row < M) {
+			const float4 a = *reinterpret_cast<const float4 *>(A + size_t(row) * K + 8 * k8);
+			const float4 b = *reinterpret_cast<const float4 *>(A + size_t(row) * K + 8 * k8 + 4);
+			x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+		} else {
+#pragma unroll
+			for (int i = 0; i < 8; i++) x[i] = 0.0f;
+		}
+		__align__(16) __nv_bfloat16 hi[8], mid[8], lo[8];
+#pragma unroll
+		for (int i = 0; i < 8; i++) {
+			hi[i] = __float2bfloat16_rn(x[i]);
+			const float r1 = x[i] - __bfloat162float(hi[i]);  // exact
+			mid[i] = __float2bfloat16_rn(r1);
+			const float r2 = r1 - __bfloat162float(mid[i]);   // exact
+			lo[i] = __float2bfloat16_rn(r2);
+		}
+		const int mt = row / TC_BM, r = row % TC_BM, kb = (8 * k8) / TC_BK, kc = ((8 * k8) % TC_BK) / 8;
+		const size_t off = (size_t(mt) * k_blocks + kb) * (TC_TILE_BYTES / 2) + (r / 8) * 256 + kc * 64 + (r % 8) * 8;
+		*reinterpret_cast<uint4 *>(out + off) = *reinterpret_cast<const uint4 *>(hi);
+		*reinterpret_cast<uint4 *>(out + term_stride + off) = *reinterpret_cast<const uint4 *>(mid);
+		*reinterpret_cast<uint4 *>(out + 2 * term_stride + off) = *reinterpret_cast<const uint4 *>(lo);
+	}
+}
+
+// ------------------------------------------------------------------ tcgen05 helpers
+// shared-memory matrix descriptor: K-major, no swizzle, LBO 128 B, SBO 512 B
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
+	uint64_t d = 0;
+	d |= uint64_t((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+	d |= uint64_t(128 >> 4) << 16;               // leading-dimension byte offset (next 8 k)
+	d |= uint64_t(512 >> 4) << 32;               // stride-dimension byte offset (next 8 rows)
+	d |= uint64_t(1) << 46;                      // descriptor version of this architecture
+	return d;                                    // base offset 0, layout type 0 = no swizzle
+}
+// instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = 128
+__device__ __forceinline__ uint32_t tc_idesc() {
+	return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TC_BN >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+	asm volatile(
+	    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+	    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+	    "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+	    : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+	             "l"(src), "r"(bytes), "r"(smem_u32(bar))
+	             : "memory");
+}
+__device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int *err) {
+	int spins = 0;
+	while (!mbar_try_wait(bar, parity)) {
+		if (++spins > TC_SPIN_CAP) {
+			atomicExch(err, 6);
+			return false;
+		}
+	}
+	return true;
+}
+
+struct GemmTcArgs {
+	const __nv_bfloat16 *apack;  // [3][m_tiles][k_blocks][8 KiB]
+	const float *scales;         // [N]
+	float *C;                    // [M][N]                      (nsplit == 1: scaled result)
+	float *partial;              // [nsplit][M][N] raw sums      (nsplit > 1: summed and scaled by a second kernel)
+	int M, N, K, m_tiles;
+	int nsplit;                  // K-splits = gridDim.z; K / 32 must be a multiple of it
+	int *err;
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, GemmTcArgs a) {
+	extern __shared__ uint8_t tc_smem_raw[];
+	uint8_t *smem = reinterpret_cast<uint8_t *>((uintptr_t(tc_smem_raw) + 1023) & ~uintptr_t(1023));
+	__shared__ uint64_t full_bar[TC_STAGES];   // A tiles + W tile landed (transaction bytes)
+	__shared__ uint64_t conv_bar[TC_STAGES];   // W converted to bf16 (4 converter warps arrive)
+	__shared__ uint64_t free_bar[TC_STAGES];   // MMAs that read the stage have completed (tcgen05.commit)
+	__shared__ uint64_t acc_bar;               // all MMAs done: accumulators ready
+	__shared__ uint32_t tmem_base_s;
+	__shared__ int s_fail;
+	__shared__ int s_issued;  // k-blocks whose loads have been issued
+
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	const int n0 = blockIdx.x * TC_BN;
+	const int mt0 = blockIdx.y * TC_MT;
+	const int k_blocks_all = a.K / TC_BK;
+	const int k_blocks = k_blocks_all / a.nsplit;   // this CTA's share of K
+	const int kb_first = blockIdx.z * k_blocks;
+	const size_t term_stride = size_t(a.m_tiles) * k_blocks_all * TC_TILE_BYTES;  // bytes
+
+	if (tid == 0) {
+		for (int s = 0; s < TC_STAGES; s++) {
+			mbar_init(&full_bar[s], 1);
+			mbar_init(&conv_bar[s], 4);
+			mbar_init(&free_bar[s], 1);
+		}
+		mbar_init(&acc_bar, 1);
+		s_fail = 0;
+		s_issued = 0;
+		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+	}
+	if (warp == 1) {  // TMEM: 2 accumulators x 128 fp32 columns
+		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(256)
+		             : "memory");
+		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_base_s;
+
+	auto stage_a = [&](int s, int term, int mt) { return smem + size_t(s) * TC_STAGE_BYTES + (term * TC_MT + mt) * TC_TILE_BYTES; };
+	auto stage_w = [&](int s) { return smem + size_t(s) * TC_STAGE_BYTES + 3 * TC_MT * TC_TILE_BYTES; };
+	auto stage_b = [&](int s) { return smem + size_t(s) * TC_STAGE_BYTES + 3 * TC_MT * TC_TILE_BYTES + TC_W_BYTES; };
+
+	if (warp == 0) {
+		// ------------------------------------------------------------ producer
+		if (lane == 0) {
+			const uint64_t pol = l2_evict_first_policy();
+			for (int kb = 0; kb < k_blocks; kb++) {
+				const int s = kb % TC_STAGES, use = kb / TC_STAGES;
+				if (use > 0 && !tc_wait(&free_bar[s], (use - 1) & 1, a.err)) { s_fail = 1; break; }
+				fence_proxy_async();
+				mbar_expect_tx(&full_bar[s], uint32_t(3 * TC_MT * TC_TILE_BYTES + TC_W_BYTES));
+				for (int term = 0; term < 3; term++)
+					for (int mt = 0; mt < TC_MT; mt++) {
+						const int mtg = min(mt0 + mt, a.m_tiles - 1);  // a missing second tile re-reads the first (results unused)
+						const uint8_t *src = reinterpret_cast<const uint8_t *>(a.apack) + term * term_stride +
+						                     (size_t(mtg) * k_blocks_all + kb_first + kb) * TC_TILE_BYTES;
+						bulk_load(stage_a(s, term, mt), src, TC_TILE_BYTES, &full_bar[s]);
+					}
+				tma_load_2d(stage_w(s), &wmap, n0, (kb_first + kb) * TC_BK, &full_bar[s], pol);
+				s_issued = kb + 1;
+			}
+		}
+	} else if (warp == 1) {
+		// ------------------------------------------------------------ MMA issuer
+		if (lane == 0) {
+			const uint32_t idesc = tc_idesc();
+			for (int kb = 0; kb < k_blocks; kb++) {
+				const int s = kb % TC_STAGES, use = kb / TC_STAGES;
+				if (!tc_wait(&full_bar[s], use & 1, a.err) || !tc_wait(&conv_bar[s], use & 1, a.err)) { s_fail = 1; break; }
+				tc_fence_after();
+				const uint32_t b_addr = smem_u32(stage_b(s));
+#pragma unroll
+				for (int mt = 0; mt < TC_MT; mt++) {
+					const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN);
+#pragma unroll
+					for (int term = 0; term < 3; term++) {
+						const uint32_t a_addr = smem_u32(stage_a(s, term, mt));
+#pragma unroll
+						for (int j = 0; j < TC_BK / 16; j++) {
+							const uint32_t acc = (kb > 0 || term > 0 || j > 0) ? 1u : 0u;
+							tc_mma(d_tmem, tc_smem_desc(a_addr + j * 256), tc_smem_desc(b_addr + j * 256), idesc, acc);
+						}
+					}
+				}
+				tc_commit(&free_bar[s]);  // arrives when the MMAs above have read the stage
+			}
+			tc_commit(&acc_bar);
+		}
+	} else {
+		// ------------------------------------------------------------ converters (warps 2..5, 128 threads)
+		const int ct = tid - 64;  // 0..127 = column n of the W tile
+		for (int kb = 0; kb < k_blocks; kb++) {
+			const int s = kb % TC_STAGES, use = kb / TC_STAGES;
+			bool ok = tc_wait(&full_bar[s], use & 1, a.err);
+			// the bf16 tile of this stage was last read by the MMAs of use-1, which free_bar covers;
+			// the producer waited for it before refilling the stage, so full_bar implies it
+			if (!ok) { s_fail = 1; break; }
+			const uint8_t *w = stage_w(s);
+			uint8_t *b = stage_b(s);
+#pragma unroll
+			for (int kc = 0; kc < TC_BK / 8; kc++) {
+				__align__(16) __nv_bfloat162 v[4];
+#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					const uint32_t u0 = w[(kc * 8 + 2 * i) * TC_BN + ct], u1 = w[(kc * 8 + 2 * i + 1) * TC_BN + ct];
+					const float f0 = __uint_as_float(0x4B000000u | (u0 ^ 0x80u)) - 8388736.0f;
+					const float f1 = __uint_as_float(0x4B000000u | (u1 ^ 0x80u)) - 8388736.0f;
+					v[i] = __floats2bfloat162_rn(f0, f1);  // |int8| <= 128: exact in bf16
+				}
+				*reinterpret_cast<uint4 *>(b + (ct / 8) * 512 + kc * 128 + (ct % 8) * 16) = *reinterpret_cast<const uint4 *>(v);
+			}
+			fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+			__syncwarp();
+			if (lane == 0) mbar_arrive(&conv_bar[s]);
+		}
+		// ------------------------------------------------------------ epilogue
+		if (!*(volatile int *)&s_fail && tc_wait(&acc_bar, 0, a.err)) {
+			tc_fence_after();
+			const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+#pragma unroll 1
+			for (int mt = 0; mt < TC_MT; mt++) {
+				const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
+#pragma unroll 1
+				for (int c = 0; c < TC_BN / 32; c++) {
+					uint32_t r[32];
+					const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(mt * TC_BN + c * 32);
+					asm volatile(
+					    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+					    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+					    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+					      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+					      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+					      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+					    : "r"(taddr)
+					    : "memory");
+					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					if ((mt0 + mt) < a.m_tiles && row < a.M) {
+						if (a.nsplit == 1) {
+							float *dst = a.C + size_t(row) * a.N + n0 + c * 32;
+							const float *sc = a.scales + n0 + c * 32;
+#pragma unroll
+							for (int i = 0; i < 32; i += 4) {
+								float4 o;
+								o.x = __uint_as_float(r[i]) * sc[i];
+								o.y = __uint_as_float(r[i + 1]) * sc[i + 1];
+								o.z = __uint_as_float(r[i + 2]) * sc[i + 2];
+								o.w = __uint_as_float(r[i + 3]) * sc[i + 3];
+								*reinterpret_cast<float4 *>(dst + i) = o;
+							}
+						} else {
+							float *dst = a.partial + (size_t(blockIdx.z) * a.M + row) * a.N + n0 + c * 32;
+#pragma unroll
+							for (int i = 0; i < 32; i += 4)
+								*reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+								                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+						}
+					}
+				}
+			}
+		}
+	}
+	// ---------------------------------------------------------------- teardown
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 0 && lane == 0) {
+		// every load that was issued must have landed before the shared memory is given up
+		// (already true on the normal path; matters only after a wait ran out)
+		const int issued = *(volatile int *)&s_issued;
+		for (int kb = max(0, issued - TC_STAGES); kb < issued; kb++) {
+			int spins = 0;
+			while (!mbar_try_wait(&full_bar[kb % TC_STAGES], (kb / TC_STAGES) & 1) && ++spins < TC_SPIN_CAP) {
+			}
+		}
+	}
+	if (warp == 1) {
+		if (*(volatile int *)&s_fail && lane == 0) {
+			// a wait ran out: let the MMAs in flight finish before the TMEM goes away
+			int spins = 0;
+			while (!mbar_try_wait(&acc_bar, 0) && ++spins < TC_SPIN_CAP) {
+			}
+		}
+		__syncwarp();
+		tc_fence_after();
+		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+	}
+}
+
+}  // namespace tg

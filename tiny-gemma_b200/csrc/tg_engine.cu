@@ -16,6 +16,7 @@
 #include "../../include/tiny_gemma_b200.h"
 #include "kernels_decode.cuh"
 #include "kernels_mega.cuh"
+#include "kernels_gemm_tc.cuh"
 #include "kernels_prefill.cuh"
 #include "kernels_sampler.cuh"
 
@@ -891,6 +892,8 @@ int check_err_flag(tg_state *s) {
 		cudaMemsetAsync(s->err_flag, 0, 4, s->stream);
 		if (flag == 1) return fail(TG_EINVAL, "token id out of range");
 		if (flag == 2) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
+		if (flag == 6) return fail(TG_ECUDA, "tensor-core GEMM: a pipeline wait ran out");
+		if (flag == 5) return fail(TG_ECUDA, "persistent kernel: a hand-off flag wait ran out");
 		return fail(TG_ECUDA, flag == 3 ? "persistent kernel: a TMA wait ran out" : "persistent kernel: a grid barrier wait ran out");
 	}
 	return TG_OK;
@@ -906,6 +909,81 @@ int ensure_log(tg_state *s, int steps) {
 }
 
 // ------------------------------------------------------------- prefill
+// Tensor-core GEMM (kernels_gemm_tc.cuh): activations are split into three bf16 terms and packed
+// tile by tile once per distinct A (pack_activations), then any number of weight matrices with
+// the same K can be multiplied against that packing (launch_gemm_tc).
+struct TcScratch {
+	__nv_bfloat16 *apack = nullptr;
+	size_t apack_bytes = 0;
+	float *partial = nullptr;  // split-K partial sums
+	size_t partial_floats = 0;
+	int *err = nullptr;
+};
+
+// K-split of the tensor-core GEMM: enough CTAs to fill the GPU, accumulation chains of at most 24
+// K-blocks (768 rows) for accuracy, as far as the partial-sum buffer allows.
+int tc_pick_split(int M, int K, int N, size_t partial_floats) {
+	const int k_blocks = K / TC_BK;
+	const int ctas = (N / TC_BN) * (((M + TC_BM - 1) / TC_BM + TC_MT - 1) / TC_MT);
+	const int want = std::max((g_num_sms + ctas - 1) / ctas, (k_blocks + 23) / 24);
+	int best = 1;
+	for (int ns = 1; ns <= k_blocks; ns++) {
+		if (k_blocks % ns) continue;
+		if (ns > 1 && size_t(ns) * M * N > partial_floats) break;
+		best = ns;
+		if (ns >= want) break;
+	}
+	return best;
+}
+
+size_t tc_pack_bytes(int M, int K) {
+	const size_t m_tiles = (size_t(M) + TC_BM - 1) / TC_BM;
+	return 3 * m_tiles * size_t(K / TC_BK) * TC_TILE_BYTES;
+}
+
+int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStream_t st) {
+	if (tc_pack_bytes(M, K) > sc.apack_bytes) return fail(TG_ENOMEM, "tensor-core GEMM scratch too small");
+	const int m_tiles = (M + TC_BM - 1) / TC_BM;
+	const size_t chunks = size_t(m_tiles) * TC_BM * (K / 8);
+	const unsigned grid = unsigned(std::min<size_t>((chunks + 255) / 256, size_t(g_num_sms) * 16));
+	split_pack_kernel<<<grid, 256, 0, st>>>(A, sc.apack, M, K, m_tiles);
+	count_launch();
+	return check_launch("split_pack");
+}
+
+int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream_t st) {
+	static bool configured = false;
+	const size_t smem = size_t(TC_STAGES) * TC_STAGE_BYTES + 1024;
+	if (!configured) {
+		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+		configured = true;
+	}
+	CUtensorMap wmap;
+	TG_TRY(make_tmap(&wmap, w.q, w.K, w.N, TC_BN, TC_BK));
+	GemmTcArgs a{};
+	a.apack = sc.apack;
+	a.scales = w.s;
+	a.C = C;
+	a.M = M;
+	a.N = w.N;
+	a.K = w.K;
+	a.m_tiles = (M + TC_BM - 1) / TC_BM;
+	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats);
+	a.partial = sc.partial;
+	a.err = sc.err;
+	dim3 grid(w.N / TC_BN, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
+	qgemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(wmap, a);
+	count_launch();
+	TG_TRY(check_launch("qgemm_tc"));
+	if (a.nsplit > 1) {
+		const size_t n = size_t(M) * w.N;
+		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, sc.partial, w.s, M, w.N, a.nsplit);
+		count_launch();
+		TG_TRY(check_launch("qgemm_reduce"));
+	}
+	return TG_OK;
+}
+
 int launch_gemm(float *C, const float *A, const QW &w, int M, float *partial, size_t partial_floats, cudaStream_t st) {
 	const int K = w.K, N = w.N;
 	dim3 grid(N / GM_BN, (M + GM_BM - 1) / GM_BM, 1);
@@ -952,8 +1030,24 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 	float *tt = p;       p += size_t(S) * D;
 	float *up = p;       p += size_t(S) * I;
 	float *gate = p;     p += size_t(S) * I;
+	const bool use_tc = env_int("TG_GEMM_TC", 1) != 0;
+	TcScratch tc;
+	if (use_tc) {
+		tc.apack = reinterpret_cast<__nv_bfloat16 *>(p);
+		tc.apack_bytes = tc_pack_bytes(S, std::max(I, std::max(D, qd)));
+		tc.err = s->err_flag;
+		p += (tc.apack_bytes + 3) / 4;
+	}
 	float *part = p;
 	size_t part_floats = s->pf_floats - size_t(part - s->pf);
+	tc.partial = part;
+	tc.partial_floats = part_floats;
+	// C = A . W for one weight; `fresh` = A differs from the previous call and must be packed again
+	auto gemm = [&](float *C, const float *A, const QW &w, bool fresh) -> int {
+		if (!use_tc) return launch_gemm(C, A, w, S, part, part_floats, st);
+		if (fresh) TG_TRY(pack_activations(A, S, w.K, tc, st));
+		return launch_gemm_tc(C, w, S, tc, st);
+	};
 
 	embed_prefill_kernel<<<S, 256, 0, st>>>(m->wte, m->wte_s, s->pf_ids + size_t(b) * S, h, S, D, V,
 	                                        float(std::sqrt(double(D))), s->err_flag);
@@ -963,9 +1057,9 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		const LayerW &w = m->layers[l];
 		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.attn_pre, nullptr, D);
 		count_launch();
-		TG_TRY(launch_gemm(q, xn, w.Q, S, part, part_floats, st));
-		TG_TRY(launch_gemm(k, xn, w.K, S, part, part_floats, st));
-		TG_TRY(launch_gemm(v, xn, w.V, S, part, part_floats, st));
+		TG_TRY(gemm(q, xn, w.Q, true));
+		TG_TRY(gemm(k, xn, w.K, false));
+		TG_TRY(gemm(v, xn, w.V, false));
 		const int slots = s->slots[l];
 		qk_norm_rope_prefill_kernel<<<S, 192, 0, st>>>(q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
 		                                               m->rope[w.is_local ? 1 : 0][1],
@@ -975,17 +1069,17 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
 		TG_TRY(check_launch("attn_prefill"));
-		TG_TRY(launch_gemm(tt, ao, w.O, S, part, part_floats, st));
+		TG_TRY(gemm(tt, ao, w.O, true));
 		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.attn_post, h, D);
 		count_launch();
 		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.mlp_pre, nullptr, D);
 		count_launch();
-		TG_TRY(launch_gemm(up, xn, w.U, S, part, part_floats, st));
-		TG_TRY(launch_gemm(gate, xn, w.G, S, part, part_floats, st));
+		TG_TRY(gemm(up, xn, w.U, true));
+		TG_TRY(gemm(gate, xn, w.G, false));
 		size_t n = size_t(S) * I;
 		geglu_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(gate, up, n, lut);
 		count_launch();
-		TG_TRY(launch_gemm(tt, gate, w.Dn, S, part, part_floats, st));
+		TG_TRY(gemm(tt, gate, w.Dn, true));
 		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.mlp_post, h, D);
 		count_launch();
 		TG_TRY(check_launch("prefill layer"));
@@ -1329,7 +1423,9 @@ int tg_prefill(tg_state *s, const int *ids, int S, float *logits_host) {
 	}
 	size_t need = size_t(S) * (3 * size_t(D) + 2 * qd + 2 * kd + 2 * size_t(I));
 	size_t part = std::max(size_t(4) * S * D, size_t(1) << 22);  // split-K scratch
+	part = std::max(part, std::min(size_t(24) * S * std::max(I, qd), size_t(1) << 28));  // tensor-core GEMM partial sums (<= 1 GiB)
 	need += part;
+	need += (tc_pack_bytes(S, std::max(I, std::max(D, qd))) + 3) / 4 + 64;
 	if (need > s->pf_floats) {
 		if (s->pf) cudaFree(s->pf);
 		s->pf = nullptr;
@@ -1687,10 +1783,45 @@ int tg_dev_qgemm(float *c, const float *a, const int8_t *w, const float *scales,
 	if (!c || !a || !w || !scales || M < 1) return fail(TG_EINVAL, "bad argument");
 	if (!supported_k(K)) return fail(TG_ESHAPE, "Unsupported ROW dimension: " + std::to_string(K));
 	if (!supported_n(N)) return fail(TG_ESHAPE, "Unsupported COL dimension: " + std::to_string(N));
-	static float *partial[64] = {nullptr};
-	static size_t partial_floats[64] = {0};
 	int dev = 0;
 	TG_CUDA(cudaGetDevice(&dev));
+	QW q{w, scales, K, N};
+	if (env_int("TG_GEMM_TC", 1)) {
+		// tensor-core path: packed bf16 activations + an error word, per device, grown on demand
+		static TcScratch tc[64];
+		const size_t need = tc_pack_bytes(M, K);
+		if (need > tc[dev].apack_bytes) {
+			if (tc[dev].apack) cudaFree(tc[dev].apack);
+			tc[dev].apack = nullptr;
+			tc[dev].apack_bytes = 0;
+			TG_CUDA(cudaMalloc(&tc[dev].apack, need));
+			tc[dev].apack_bytes = need;
+		}
+		const size_t pneed = std::min(size_t(24) * M * N, size_t(1) << 28);
+		if (pneed > tc[dev].partial_floats) {
+			if (tc[dev].partial) cudaFree(tc[dev].partial);
+			tc[dev].partial = nullptr;
+			tc[dev].partial_floats = 0;
+			TG_CUDA(cudaMalloc(&tc[dev].partial, pneed * 4));
+			tc[dev].partial_floats = pneed;
+		}
+		if (!tc[dev].err) {
+			TG_CUDA(cudaMalloc(&tc[dev].err, 4));
+			TG_CUDA(cudaMemset(tc[dev].err, 0, 4));
+		}
+		TG_TRY(pack_activations(a, M, K, tc[dev], (cudaStream_t)stream));
+		TG_TRY(launch_gemm_tc(c, q, M, tc[dev], (cudaStream_t)stream));
+		int flag = 0;
+		TG_CUDA(cudaMemcpyAsync(&flag, tc[dev].err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+		TG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+		if (flag) {
+			cudaMemset(tc[dev].err, 0, 4);
+			return fail(TG_ECUDA, "tensor-core GEMM: a pipeline wait ran out");
+		}
+		return TG_OK;
+	}
+	static float *partial[64] = {nullptr};
+	static size_t partial_floats[64] = {0};
 	size_t need = std::max(size_t(4) * M * N, size_t(1) << 20);
 	if ((N / GM_BN) * ((M + GM_BM - 1) / GM_BM) >= g_num_sms) need = 0;
 	if (need > partial_floats[dev]) {
@@ -1699,7 +1830,6 @@ int tg_dev_qgemm(float *c, const float *a, const int8_t *w, const float *scales,
 		TG_CUDA(cudaMalloc(&partial[dev], need * 4));
 		partial_floats[dev] = need;
 	}
-	QW q{w, scales, K, N};
 	return launch_gemm(c, a, q, M, partial[dev], partial_floats[dev], (cudaStream_t)stream);
 }
 
