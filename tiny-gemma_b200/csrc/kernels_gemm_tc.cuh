@@ -131,7 +131,8 @@ __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int *err
 struct GemmTcArgs {
 	const __nv_bfloat16 *apack;  // [3][m_tiles][k_blocks][8 KiB]
 	const float *scales;         // [N]
-	float *C;                    // [M][N]                      (nsplit == 1: scaled result)
+	float *C;                    // [M] rows of ldc floats       (nsplit == 1: scaled result)
+	int ldc;                     // row stride of C (>= N; lets a GEMM write a column block of a wider row)
 	float *partial;              // [nsplit][M][N] raw sums      (nsplit > 1: summed and scaled by a second kernel)
 	int M, N, K, m_tiles;
 	int nsplit;                  // K-splits = gridDim.z; K / 32 must be a multiple of it
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 					if ((mt0 + mt) < a.m_tiles && row < a.M) {
 						if (a.nsplit == 1) {
-							float *dst = a.C + size_t(row) * a.N + n0 + c * 32;
+							float *dst = a.C + size_t(row) * a.ldc + n0 + c * 32;
 							const float *sc = a.scales + n0 + c * 32;
 #pragma unroll
 							for (int i = 0; i < 32; i += 4) {

@@ -40,7 +40,7 @@ namespace tg {
 constexpr int MG_THREADS = 384;
 constexpr int MG_NWARPS = MG_THREADS / 32;
 constexpr int MG_SPIN_CAP = 1 << 22;
-constexpr int MG_LM_STAGES = 6;
+constexpr int MG_LM_STAGES = 3;
 constexpr int MG_LM_TN = 128;
 constexpr int MG_MAX_ATT = 64;  // most CTAs that take part in attention
 
@@ -72,6 +72,7 @@ struct MgArgs {
 	int L, D, I, V, QD, KD;
 	MgPhase A, C, Dp, E, LM;
 	int tm_lm;
+	int lm_bps;  // TMA boxes per lm_head ring stage
 	const float *lm_scale, *final_norm;
 	const int8_t *wte;
 	const float *wte_s;
@@ -104,7 +105,8 @@ struct MgArgs {
 	int *randf_count;
 	int randf_cap;
 	int att_local, att_global;  // CTAs taking part in attention
-	long long *dbg;  // optional: SM-clock stamps of CTA 0 along the last step (profiling aid)
+	long long *dbg;  // optional: SM-clock stamps of one CTA along the last step (profiling aid)
+	int dbg_cta;     // which CTA records
 	int dbg_cap;
 };
 
@@ -631,7 +633,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 #pragma unroll 1
 	for (int step = 0; step < a.n_steps; step++) {
 		const bool more = (step + 1 < a.n_steps);
-		const bool dbg_on = (a.dbg != nullptr) && cta == 0 && tid == 0 && !more;
+		const bool dbg_on = (a.dbg != nullptr) && cta == a.dbg_cta && tid == 0 && !more;
 		MG_STAMP();
 		// ---------------------------------------------------------------- embedding
 		if (tok < 0 || tok >= a.V) {
@@ -992,25 +994,32 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 			// 12 warps arrives on empty[stage] when it has read the stage; one lane then refills
 			// it. No block-wide barrier per chunk — only the tile-end reduction synchronises.
 			const MgPhase &ph = a.LM;
+			const int bps = a.lm_bps;                 // boxes per stage
+			const int spt = ph.nboxes / bps;          // stages per column tile
+			const int stage_rows = ph.box_rows * bps;
 			const int my_tiles = (ph.ntiles - cta + G - 1) / G;
-			const int total = my_tiles * ph.nboxes;  // chunks this CTA consumes
-			const int stage_bytes = ph.TN * ph.box_rows;
+			const int total = my_tiles * spt;  // stages this CTA consumes
+			const int box_bytes = ph.TN * ph.box_rows;
+			const int stage_bytes = box_bytes * bps;
 			uint8_t *ring = R_D;
+			auto issue_stage = [&](int q, int stg) {  // by one lane
+				const int t = cta + (q / spt) * G, c = q % spt;
+				mbar_expect_tx(&bar_lm[stg], uint32_t(stage_bytes));
+				for (int b = 0; b < bps; b++)
+					tma_load_2d(ring + stg * stage_bytes + b * box_bytes, a.tmaps + a.tm_lm, t * ph.TN,
+					            c * stage_rows + b * ph.box_rows, &bar_lm[stg], pol);
+			};
 			if (warp == MG_NWARPS - 1) {
 				if (lane == 0) fence_proxy_async();
 				__syncwarp();
-				if (lane < MG_LM_STAGES && lane < total) {
-					const int t = cta + (lane / ph.nboxes) * G, c = lane % ph.nboxes;
-					mbar_expect_tx(&bar_lm[lane], uint32_t(stage_bytes));
-					tma_load_2d(ring + lane * stage_bytes, a.tmaps + a.tm_lm, t * ph.TN, c * ph.box_rows, &bar_lm[lane], pol);
-				}
+				if (lane < MG_LM_STAGES && lane < total) issue_stage(lane, lane);
 			}
 			float acc[16];
 			float sc_tile = 0.0f;
 			const int rstep = MG_THREADS / ph.segs;
 #pragma unroll 1
 			for (int q = 0; q < total; q++) {
-				const int stg = q % MG_LM_STAGES, c = q % ph.nboxes, tile = cta + (q / ph.nboxes) * G;
+				const int stg = q % MG_LM_STAGES, c = q % spt, tile = cta + (q / spt) * G;
 				if (c == 0) {
 #pragma unroll
 					for (int i = 0; i < 16; i++) acc[i] = 0.0f;
@@ -1020,18 +1029,23 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				plm ^= (1u << stg);
 				{
 					const uint8_t *tp = ring + stg * stage_bytes + 16 * tid;
-					const float *xc = xs + c * ph.box_rows;
+					const float *xc = xs + c * stage_rows;
 					int row = tid / ph.segs;
 #pragma unroll 1
-					for (; row + rstep < ph.box_rows; row += 2 * rstep) {
+					for (; row + 3 * rstep < stage_rows; row += 4 * rstep) {
 						int4 v0 = *reinterpret_cast<const int4 *>(tp);
 						int4 v1 = *reinterpret_cast<const int4 *>(tp + 16 * MG_THREADS);
-						tp += 32 * MG_THREADS;
-						mg_fma16(acc, v0, xc[row]);
-						mg_fma16(acc, v1, xc[row + rstep]);
+						int4 v2 = *reinterpret_cast<const int4 *>(tp + 32 * MG_THREADS);
+						int4 v3 = *reinterpret_cast<const int4 *>(tp + 48 * MG_THREADS);
+						const float x0 = xc[row], x1 = xc[row + rstep], x2 = xc[row + 2 * rstep], x3 = xc[row + 3 * rstep];
+						tp += 64 * MG_THREADS;
+						mg_fma16(acc, v0, x0);
+						mg_fma16(acc, v1, x1);
+						mg_fma16(acc, v2, x2);
+						mg_fma16(acc, v3, x3);
 					}
 #pragma unroll 1
-					for (; row < ph.box_rows; row += rstep) {
+					for (; row < stage_rows; row += rstep) {
 						int4 v = *reinterpret_cast<const int4 *>(tp);
 						tp += 16 * MG_THREADS;
 						mg_fma16(acc, v, xc[row]);
@@ -1043,15 +1057,13 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					const int nq = q + MG_LM_STAGES;
 					if (nq < total) {
 						mg_wait_tma(ctx, &emp_lm[stg], (pemp >> stg) & 1u);  // all 12 warps have left the stage
-						const int t2 = cta + (nq / ph.nboxes) * G, c2 = nq % ph.nboxes;
 						fence_proxy_async();
-						mbar_expect_tx(&bar_lm[stg], uint32_t(stage_bytes));
-						tma_load_2d(ring + stg * stage_bytes, a.tmaps + a.tm_lm, t2 * ph.TN, c2 * ph.box_rows, &bar_lm[stg], pol);
+						issue_stage(nq, stg);
 					}
 				}
 				pemp ^= (1u << stg);
 				__syncwarp();
-				if (c == ph.nboxes - 1) {
+				if (c == spt - 1) {
 					float s = mg_tile_reduce(acc, ph.segs, red);
 					if (tid < ph.TN) {
 						const int v = tile * ph.TN + tid;

@@ -115,13 +115,18 @@ __global__ void __launch_bounds__(256) qgemm_simt_kernel(float *C, const float *
 	}
 }
 
-__global__ void qgemm_splitk_reduce_kernel(float *C, const float *partial, const float *scales, int M, int N, int nsplit) {
+__global__ void qgemm_splitk_reduce_kernel(float *C, const float *partial, const float *scales, int M, int N, int nsplit,
+                                           int ldc) {
 	size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
 	if (i >= size_t(M) * N) return;
 	float s = 0.0f;
 	for (int sp = 0; sp < nsplit; sp++) s += partial[size_t(sp) * M * N + i];
-	C[i] = s * scales[i % N];
+	const size_t m = i / N, n = i % N;
+	C[m * ldc + n] = s * scales[n];
 }
+
+// out[b, :] = table lookup per element: gate = lut(gate) * up over [rows][n] with row strides
+// (the batched decode step keeps up and gate in separate buffers)
 
 // ops::gelu (LUT) + ops::mul, reference ops.hpp:62-123: gate = lut(gate) * up
 __global__ void geglu_kernel(float *gate, const float *up, size_t n, GeluLut lut) {
@@ -179,21 +184,39 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
 // ops::attention_prefill, reference ops.hpp:377-526: causal; on sliding-window
 // layers query s sees keys max(0, s - window) .. s (window + 1 keys, :437-443).
 // q,o [S][4][256], k,v [S][256] (the prompt's own activations, not the cache).
-// One warp per query position handles the 4 heads that share the KV head;
-// 8 warps per CTA take 8 consecutive queries so their key ranges overlap in L1/L2.
+// One CTA = 8 consecutive queries, one warp per query handling the 4 heads that
+// share the KV head. The CTA walks the union of its queries' key ranges in
+// tiles of 16 keys staged in shared memory (K and V, 32 KiB); the next tile is
+// fetched into registers while the current one is consumed, so the L2 latency of
+// a key row is paid once per tile instead of once per key.
+constexpr int AP_QPB = 8;     // queries per CTA
+constexpr int AP_TILE = 16;   // keys per shared-memory tile
+
 __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float *q, const float *k, const float *v, int S,
                                                            int is_local, int window) {
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int s = blockIdx.x * 8 + warp;
-	if (s >= S) return;
+	__shared__ __align__(16) float ks[AP_TILE][256];
+	__shared__ __align__(16) float vs[AP_TILE][256];
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	const int s0 = blockIdx.x * AP_QPB;
+	const int s = s0 + warp;              // this warp's query (may be >= S: then it only helps loading)
+	const int s_last = min(S - 1, s0 + AP_QPB - 1);
+	int cta_j0 = 0;
+	if (is_local) cta_j0 = (s0 >= window) ? s0 - window : 0;
+	int my_j0 = 0;
+	if (is_local) my_j0 = (s >= window) ? s - window : 0;
 	float4 q0[4], q1[4], o0[4], o1[4];
 	float m[4], l[4];
 #pragma unroll
 	for (int h = 0; h < 4; h++) {
-		const float *qr = q + size_t(s) * 1024 + h * 256;
-		q0[h] = *reinterpret_cast<const float4 *>(qr + 4 * lane);
-		q1[h] = *reinterpret_cast<const float4 *>(qr + 128 + 4 * lane);
-		// reference multiplies the score by 1/16 after the dot product (ops.hpp:463); scaling q
+		if (s < S) {
+			const float *qr = q + size_t(s) * 1024 + h * 256;
+			q0[h] = *reinterpret_cast<const float4 *>(qr + 4 * lane);
+			q1[h] = *reinterpret_cast<const float4 *>(qr + 128 + 4 * lane);
+		} else {
+			q0[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+			q1[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+		}
+		// the reference multiplies the score by 1/16 after the dot product (ops.hpp:463); scaling q
 		// by the same power of two first is exact
 		q0[h].x *= 0.0625f; q0[h].y *= 0.0625f; q0[h].z *= 0.0625f; q0[h].w *= 0.0625f;
 		q1[h].x *= 0.0625f; q1[h].y *= 0.0625f; q1[h].z *= 0.0625f; q1[h].w *= 0.0625f;
@@ -202,49 +225,79 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float
 		m[h] = -INFINITY;
 		l[h] = 0.0f;
 	}
-	int j0 = 0;
-	if (is_local) j0 = (s >= window) ? s - window : 0;
-	for (int j = j0; j <= s; j++) {
-		const float *kr = k + size_t(j) * 256, *vr = v + size_t(j) * 256;
-		float4 k0v = *reinterpret_cast<const float4 *>(kr + 4 * lane);
-		float4 k1v = *reinterpret_cast<const float4 *>(kr + 128 + 4 * lane);
-		float4 v0v = *reinterpret_cast<const float4 *>(vr + 4 * lane);
-		float4 v1v = *reinterpret_cast<const float4 *>(vr + 128 + 4 * lane);
-		float sc[4];
+	// tile loads: 16 rows x 256 floats x {K,V} = 2048 float4; thread t takes float4 slots t, t+256, ... (4 of K, 4 of V)
+	float4 pk[4], pv[4];
+	auto fetch = [&](int jt) {
 #pragma unroll
-		for (int h = 0; h < 4; h++) {
-			float t = q0[h].x * k0v.x;
-			t = fmaf(q0[h].y, k0v.y, t);
-			t = fmaf(q0[h].z, k0v.z, t);
-			t = fmaf(q0[h].w, k0v.w, t);
-			t = fmaf(q1[h].x, k1v.x, t);
-			t = fmaf(q1[h].y, k1v.y, t);
-			t = fmaf(q1[h].z, k1v.z, t);
-			t = fmaf(q1[h].w, k1v.w, t);
-			sc[h] = t;
+		for (int u = 0; u < 4; u++) {
+			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
+			const int j = jt + r;
+			if (j <= s_last) {
+				pk[u] = *reinterpret_cast<const float4 *>(k + size_t(j) * 256 + 4 * c4);
+				pv[u] = *reinterpret_cast<const float4 *>(v + size_t(j) * 256 + 4 * c4);
+			} else {
+				pk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+				pv[u] = pk[u];
+			}
 		}
+	};
+	fetch(cta_j0);
+	for (int jt = cta_j0; jt <= s_last; jt += AP_TILE) {
+		__syncthreads();  // previous tile fully consumed
 #pragma unroll
-		for (int of = 16; of > 0; of >>= 1) {
-#pragma unroll
-			for (int h = 0; h < 4; h++) sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], of);
+		for (int u = 0; u < 4; u++) {
+			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
+			*reinterpret_cast<float4 *>(&ks[r][4 * c4]) = pk[u];
+			*reinterpret_cast<float4 *>(&vs[r][4 * c4]) = pv[u];
 		}
+		__syncthreads();
+		if (jt + AP_TILE <= s_last) fetch(jt + AP_TILE);
+		if (s < S) {
+			const int ja = max(jt, my_j0), jb = min(jt + AP_TILE - 1, s);
+			for (int j = ja; j <= jb; j++) {
+				const int r = j - jt;
+				const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r][4 * lane]);
+				const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r][128 + 4 * lane]);
+				const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r][4 * lane]);
+				const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r][128 + 4 * lane]);
+				float sc[4];
 #pragma unroll
-		for (int h = 0; h < 4; h++) {
-			float mn = fmaxf(m[h], sc[h]);
-			float corr = expf(m[h] - mn);
-			float p = expf(sc[h] - mn);
-			l[h] = fmaf(l[h], corr, p);
-			o0[h].x = fmaf(p, v0v.x, o0[h].x * corr);
-			o0[h].y = fmaf(p, v0v.y, o0[h].y * corr);
-			o0[h].z = fmaf(p, v0v.z, o0[h].z * corr);
-			o0[h].w = fmaf(p, v0v.w, o0[h].w * corr);
-			o1[h].x = fmaf(p, v1v.x, o1[h].x * corr);
-			o1[h].y = fmaf(p, v1v.y, o1[h].y * corr);
-			o1[h].z = fmaf(p, v1v.z, o1[h].z * corr);
-			o1[h].w = fmaf(p, v1v.w, o1[h].w * corr);
-			m[h] = mn;
+				for (int h = 0; h < 4; h++) {
+					float t = q0[h].x * k0v.x;
+					t = fmaf(q0[h].y, k0v.y, t);
+					t = fmaf(q0[h].z, k0v.z, t);
+					t = fmaf(q0[h].w, k0v.w, t);
+					t = fmaf(q1[h].x, k1v.x, t);
+					t = fmaf(q1[h].y, k1v.y, t);
+					t = fmaf(q1[h].z, k1v.z, t);
+					t = fmaf(q1[h].w, k1v.w, t);
+					sc[h] = t;
+				}
+#pragma unroll
+				for (int of = 16; of > 0; of >>= 1) {
+#pragma unroll
+					for (int h = 0; h < 4; h++) sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], of);
+				}
+#pragma unroll
+				for (int h = 0; h < 4; h++) {
+					const float mn = fmaxf(m[h], sc[h]);
+					const float corr = expf(m[h] - mn);
+					const float p = expf(sc[h] - mn);
+					l[h] = fmaf(l[h], corr, p);
+					o0[h].x = fmaf(p, v0v.x, o0[h].x * corr);
+					o0[h].y = fmaf(p, v0v.y, o0[h].y * corr);
+					o0[h].z = fmaf(p, v0v.z, o0[h].z * corr);
+					o0[h].w = fmaf(p, v0v.w, o0[h].w * corr);
+					o1[h].x = fmaf(p, v1v.x, o1[h].x * corr);
+					o1[h].y = fmaf(p, v1v.y, o1[h].y * corr);
+					o1[h].z = fmaf(p, v1v.z, o1[h].z * corr);
+					o1[h].w = fmaf(p, v1v.w, o1[h].w * corr);
+					m[h] = mn;
+				}
+			}
 		}
 	}
+	if (s >= S) return;
 #pragma unroll
 	for (int h = 0; h < 4; h++) {
 		const float inv = 1.0f / l[h];

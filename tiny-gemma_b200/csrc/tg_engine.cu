@@ -243,6 +243,18 @@ constexpr int MV_MAX_B = 4;
 
 }  // namespace
 
+// ------------------------------------------------------------- prefill
+// Tensor-core GEMM (kernels_gemm_tc.cuh): activations are split into three bf16 terms and packed
+// tile by tile once per distinct A (pack_activations), then any number of weight matrices with
+// the same K can be multiplied against that packing (launch_gemm_tc).
+struct TcScratch {
+	__nv_bfloat16 *apack = nullptr;
+	size_t apack_bytes = 0;
+	float *partial = nullptr;  // split-K partial sums
+	size_t partial_floats = 0;
+	int *err = nullptr;
+};
+
 // ===================================================================== state
 struct tg_state {
 	tg_model *m = nullptr;
@@ -287,7 +299,12 @@ struct tg_state {
 	cudaGraphExec_t graph = nullptr;
 	bool use_graph = true;
 	bool warmed = false;
+	int graph_launches = 0;
 	std::vector<int> host_pos;  // mirror of next_pos for call-order checks
+	// batched decode step (tensor-core GEMMs with M = batch)
+	bool batched_ok = false;
+	float *bx = nullptr, *bup = nullptr;  // [B][D] normed input, [B][I] up projection
+	TcScratch btc;
 	// persistent decode kernel (batch 1)
 	bool mega_ok = false;
 	MgArgs mega{};
@@ -564,9 +581,13 @@ int enqueue_decode_chunk(tg_state *s, int b0, int nb, bool with_lm_head = true) 
 	return TG_OK;
 }
 
-int decode_launches_per_chunk(const tg_config &c) { return 1 + 5 * c.n_layers + 1; }
+
+int batched_setup(tg_state *s);
+int enqueue_decode_batched(tg_state *s, bool with_lm_head);
+
 
 int enqueue_decode_all(tg_state *s) {
+	if (s->batched_ok) return enqueue_decode_batched(s, true);
 	for (int b0 = 0; b0 < s->B; b0 += MV_MAX_B) TG_TRY(enqueue_decode_chunk(s, b0, std::min(MV_MAX_B, s->B - b0)));
 	return TG_OK;
 }
@@ -585,6 +606,7 @@ int enqueue_decode_step(tg_state *s) {
 		TG_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
 		int rc = enqueue_decode_all(s);
 		cudaError_t e = cudaStreamEndCapture(s->stream, &g);
+		s->graph_launches = int(g_launches.load() - before);
 		g_launches.store(before);
 		if (rc != TG_OK) {
 			if (g) cudaGraphDestroy(g);
@@ -596,8 +618,7 @@ int enqueue_decode_step(tg_state *s) {
 		if (e != cudaSuccess) return fail(TG_ECUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
 	}
 	TG_CUDA(cudaGraphLaunch(s->graph, s->stream));
-	const int chunks = (s->B + MV_MAX_B - 1) / MV_MAX_B;
-	count_launch(chunks * decode_launches_per_chunk(s->m->cfg));
+	count_launch(s->graph_launches);
 	return TG_OK;
 }
 
@@ -663,7 +684,9 @@ bool plan_phase(MgPhase *out, int K, const std::vector<int> &n_cols, int nmat, b
 			if (units > G) break;
 			const long bytes = long(nmat) * TN * kc;
 			if (bytes > max_bytes) continue;
-			long score = long(units) * 1000 - ns * 10 - (TN < 64 ? 100 : 0);
+			// as many busy SMs as possible; then few K-splits (every CTA re-reads all split partial sums in
+			// its norm prologue); rows narrower than a 32-byte DRAM sector are avoided
+			long score = long(units) * 1000 - ns * env_int("TG_MEGA_SPLIT_COST", 40) - (TN < 32 ? 2000 : 0);
 			if (score > best_score) {
 				best_score = score;
 				const int br = largest_box_rows(kc);
@@ -693,7 +716,8 @@ int mega_setup(tg_state *s) {
 	    !plan_phase(&a.Dp, D, {I}, 2, false, G, budget) || !plan_phase(&a.E, I, {D}, 1, true, G, budget / 2))
 		return fail(TG_ESHAPE, "no phase plan fits");
 	a.LM = MgPhase{MG_LM_TN, MG_LM_TN / 16, 1, D, largest_box_rows(D), D / largest_box_rows(D), V / MG_LM_TN, V / MG_LM_TN, 0};
-	const int ring = MG_LM_STAGES * a.LM.TN * a.LM.box_rows;
+	a.lm_bps = (a.LM.nboxes % 2 == 0) ? 2 : 1;  // TMA boxes per ring stage
+	const int ring = MG_LM_STAGES * a.LM.TN * a.LM.box_rows * a.lm_bps;
 	auto up = [](int v) { return (v + 1023) & ~1023; };
 	int off = 0;
 	a.off_A = off;
@@ -846,6 +870,7 @@ int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, b
 	s->mg_seq += unsigned(n_steps) * unsigned(m->cfg.n_layers) + 1u;
 	a.dbg = s->mg_dbg;
 	a.dbg_cap = s->mg_dbg ? 4096 : 0;
+	a.dbg_cta = std::min(std::max(env_int("TG_MEGA_DBG_CTA", 0), 0), s->mega_grid - 1);
 	TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
 	void *params[] = {&a};
 	TG_CUDA(cudaLaunchCooperativeKernel((void *)mega_decode_kernel, dim3(s->mega_grid), dim3(MG_THREADS), params,
@@ -908,17 +933,6 @@ int ensure_log(tg_state *s, int steps) {
 	return TG_OK;
 }
 
-// ------------------------------------------------------------- prefill
-// Tensor-core GEMM (kernels_gemm_tc.cuh): activations are split into three bf16 terms and packed
-// tile by tile once per distinct A (pack_activations), then any number of weight matrices with
-// the same K can be multiplied against that packing (launch_gemm_tc).
-struct TcScratch {
-	__nv_bfloat16 *apack = nullptr;
-	size_t apack_bytes = 0;
-	float *partial = nullptr;  // split-K partial sums
-	size_t partial_floats = 0;
-	int *err = nullptr;
-};
 
 // K-split of the tensor-core GEMM: enough CTAs to fill the GPU, accumulation chains of at most 24
 // K-blocks (768 rows) for accuracy, as far as the partial-sum buffer allows.
@@ -951,7 +965,8 @@ int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStre
 	return check_launch("split_pack");
 }
 
-int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream_t st) {
+int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream_t st, int ldc = 0, int max_split = 1 << 30) {
+	if (ldc <= 0) ldc = w.N;
 	static bool configured = false;
 	const size_t smem = size_t(TC_STAGES) * TC_STAGE_BYTES + 1024;
 	if (!configured) {
@@ -969,6 +984,8 @@ int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream
 	a.K = w.K;
 	a.m_tiles = (M + TC_BM - 1) / TC_BM;
 	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats);
+	while (a.nsplit > max_split) a.nsplit = 1;
+	a.ldc = ldc;
 	a.partial = sc.partial;
 	a.err = sc.err;
 	dim3 grid(w.N / TC_BN, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
@@ -977,11 +994,108 @@ int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream
 	TG_TRY(check_launch("qgemm_tc"));
 	if (a.nsplit > 1) {
 		const size_t n = size_t(M) * w.N;
-		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, sc.partial, w.s, M, w.N, a.nsplit);
+		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, sc.partial, w.s, M, w.N, a.nsplit, ldc);
 		count_launch();
 		TG_TRY(check_launch("qgemm_reduce"));
 	}
 	return TG_OK;
+}
+
+// ------------------------------------------------------------- batched decode step
+// For larger batches the per-token work is the prefill's: every weight matrix is read once per
+// step for all sequences by the tensor-core GEMM (M = batch), the norms run row-wise, and only
+// the attention is per sequence (each against its own cache, positions read on the device).
+int batched_setup(tg_state *s) {
+	const tg_config &c = s->m->cfg;
+	const int B = s->B, D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab, qd = c.n_head * c.head_dim;
+	TG_CUDA(cudaMalloc(&s->bx, size_t(B) * D * 4));
+	TG_CUDA(cudaMalloc(&s->bup, size_t(B) * I * 4));
+	s->btc.apack_bytes = tc_pack_bytes(B, std::max(I, std::max(D, qd)));
+	TG_CUDA(cudaMalloc(&s->btc.apack, s->btc.apack_bytes));
+	s->btc.partial_floats = std::min(size_t(24) * B * std::max(I, qd), size_t(1) << 28);
+	TG_CUDA(cudaMalloc(&s->btc.partial, s->btc.partial_floats * 4));
+	s->btc.err = s->err_flag;
+	(void)V;
+	s->batched_ok = true;
+	return TG_OK;
+}
+
+int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
+	tg_model *m = s->m;
+	const tg_config &c = m->cfg;
+	const int B = s->B, D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim, NQ = qd + 2 * kd;
+	cudaStream_t st = s->stream;
+	const GeluLut lut = make_lut(m);
+	float *h = s->h[0];
+	EmbedArgs ea;
+	ea.wte = m->wte;
+	ea.scales = m->wte_s;
+	ea.tok = s->tok;
+	ea.h = h;
+	ea.step_pos = s->step_pos;
+	ea.next_pos = s->next_pos;
+	ea.err_flag = s->err_flag;
+	ea.D = D;
+	ea.V = V;
+	ea.sqrtD = float(std::sqrt(double(D)));
+	embed_decode_kernel<<<B, 256, 0, st>>>(ea);
+	count_launch();
+	for (int l = 0; l < c.n_layers; l++) {
+		const LayerW &w = m->layers[l];
+		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->bx, h, w.attn_pre, nullptr, D);
+		count_launch();
+		TG_TRY(pack_activations(s->bx, B, D, s->btc, st));
+		TG_TRY(launch_gemm_tc(s->qkv, w.Q, B, s->btc, st, NQ));
+		TG_TRY(launch_gemm_tc(s->qkv + qd, w.K, B, s->btc, st, NQ));
+		TG_TRY(launch_gemm_tc(s->qkv + qd + kd, w.V, B, s->btc, st, NQ));
+		{
+			AttnArgs a{};
+			a.qkv = s->qkv;
+			a.rmsq = w.rmsq;
+			a.rmsk = w.rmsk;
+			a.cosT = m->rope[w.is_local ? 1 : 0][0];
+			a.sinT = m->rope[w.is_local ? 1 : 0][1];
+			a.slots = s->slots[l];
+			a.kcache = s->kcache[l];
+			a.vcache = s->vcache[l];
+			a.is_local = w.is_local ? 1 : 0;
+			a.step_pos = s->step_pos;
+			a.ring_base = s->ring_base;
+			a.nsplit = w.is_local ? s->attn_nsplit_local : s->attn_nsplit_global;
+			a.part = s->attn_part;
+			a.tickets = s->attn_tickets;
+			a.out = s->attn_out;
+			a.err_flag = s->err_flag;
+			attn_decode_kernel<<<dim3(a.nsplit, B), AT_THREADS, 0, st>>>(a);
+			count_launch();
+			TG_TRY(check_launch("attn_decode"));
+		}
+		TG_TRY(pack_activations(s->attn_out, B, qd, s->btc, st));
+		TG_TRY(launch_gemm_tc(s->t, w.O, B, s->btc, st));
+		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(h, s->t, w.attn_post, h, D);
+		count_launch();
+		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->bx, h, w.mlp_pre, nullptr, D);
+		count_launch();
+		TG_TRY(pack_activations(s->bx, B, D, s->btc, st));
+		TG_TRY(launch_gemm_tc(s->bup, w.U, B, s->btc, st));
+		TG_TRY(launch_gemm_tc(s->act, w.G, B, s->btc, st));
+		const size_t n = size_t(B) * I;
+		geglu_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(s->act, s->bup, n, lut);
+		count_launch();
+		TG_TRY(pack_activations(s->act, B, I, s->btc, st));
+		TG_TRY(launch_gemm_tc(s->t, w.Dn, B, s->btc, st));
+		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(h, s->t, w.mlp_post, h, D);
+		count_launch();
+		TG_TRY(check_launch("batched layer"));
+	}
+	rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->xnorm, h, m->final_norm, nullptr, D);
+	count_launch();
+	if (with_lm_head) {
+		TG_TRY(pack_activations(s->xnorm, B, D, s->btc, st));
+		TG_TRY(launch_gemm_tc(s->logits, m->lm_head, B, s->btc, st, 0, 1));
+	}
+	return check_launch("batched decode");
 }
 
 int launch_gemm(float *C, const float *A, const QW &w, int M, float *partial, size_t partial_floats, cudaStream_t st) {
@@ -1004,7 +1118,7 @@ int launch_gemm(float *C, const float *A, const QW &w, int M, float *partial, si
 	TG_TRY(check_launch("qgemm_simt"));
 	if (nsplit > 1) {
 		size_t n = size_t(M) * N;
-		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, partial, w.s, M, N, nsplit);
+		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, partial, w.s, M, N, nsplit, N);
 		count_launch();
 		TG_TRY(check_launch("qgemm_reduce"));
 	}
@@ -1312,6 +1426,7 @@ int tg_state_create(tg_model *m, int batch, int max_pos_global, tg_state **out) 
 	s->B = batch;
 	s->max_pos_global = max_pos_global;
 	int rc = state_alloc(s);
+	if (rc == TG_OK && batch >= env_int("TG_BATCH_TC_MIN", 16)) rc = batched_setup(s);
 	if (rc == TG_OK && batch == 1 && env_int("TG_MEGA", 1)) {
 		int mrc = mega_setup(s);
 		if (mrc != TG_OK) {
@@ -1359,6 +1474,10 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->err_flag);
 	cudaFree(s->pf);
 	cudaFree(s->pf_ids);
+	cudaFree(s->bx);
+	cudaFree(s->bup);
+	cudaFree(s->btc.apack);
+	cudaFree(s->btc.partial);
 	cudaFree(s->d_tmaps);
 	cudaFree(s->d_layers);
 	cudaFree(s->mg_part_A);
@@ -1600,7 +1719,11 @@ int tg_decode_hidden(tg_state *s, const int *ids) {
 		std::memcpy(s->host_pin, ids, 4 * s->B);
 		TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
 	}
-	for (int b0 = 0; b0 < s->B; b0 += MV_MAX_B) TG_TRY(enqueue_decode_chunk(s, b0, std::min(MV_MAX_B, s->B - b0), false));
+	if (s->batched_ok) {
+		TG_TRY(enqueue_decode_batched(s, false));
+	} else {
+		for (int b0 = 0; b0 < s->B; b0 += MV_MAX_B) TG_TRY(enqueue_decode_chunk(s, b0, std::min(MV_MAX_B, s->B - b0), false));
+	}
 	TG_TRY(check_err_flag(s));
 	for (int b = 0; b < s->B; b++) s->host_pos[b] += 1;
 	return TG_OK;
