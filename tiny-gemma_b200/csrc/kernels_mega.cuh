@@ -61,13 +61,13 @@ struct MgLayer {
 	const float *rmsq, *rmsk, *attn_pre, *attn_post, *mlp_pre, *mlp_post;
 	float *kcache, *vcache;
 	int slots, is_local;
-	int tm_q, tm_k, tm_v, tm_o, tm_u, tm_g, tm_d;  // indices into the tensor-map array
-	int pad_;
 };
 constexpr int MG_MAX_LAYERS = 32;
 
 struct MgArgs {
-	const CUtensorMap *tmaps;
+	const CUtensorMap *tmaps;  // [0] = lm_head
+	const int8_t *tiled;       // re-tiled layer weights: per layer [A units | C units | D units (up, gate) | E units]
+	size_t tl_layer, tl_A, tl_C, tl_D, tl_E;  // layer stride and byte offsets of the phases inside a layer
 	const MgLayer *layers;
 	int L, D, I, V, QD, KD;
 	MgPhase A, C, Dp, E, LM;
@@ -82,10 +82,15 @@ struct MgArgs {
 	// shared-memory carve-up (byte offsets from a 1024-aligned base)
 	int off_A, off_C, off_D, off_E, off_h, off_xs, off_red, off_att, smem_total;
 	// L2-resident exchange buffers
-	float *part_A, *part_C, *part_E;  // [nsplit][N] partial sums
-	float *attn_part;                 // [MG_MAX_ATT][4*256 + 8]
-	uint2 *act;                       // [I] {value bits, sequence tag}: flag-carrying hand-off D -> E
-	unsigned seq0;                    // sequence tags used by this launch start above seq0
+	// Self-validating hand-off arena, two copies used by alternate layers: every float is
+	// either the sentinel MG_LL_EMPTY or a value. ll + parity * ll_stride + one of the offsets:
+	//   ll_pA  [A.nsplit][NQ]  K-split partial sums of q|k|v        (A -> B)
+	//   ll_att [MG_MAX_ATT][4*256 + 8] attention partials (o, m, l) (B -> C)
+	//   ll_pC  [C.nsplit][D]   K-split partial sums of the O projection (C -> D)
+	//   ll_act [I]             GeGLU activations                    (D -> E)
+	float *ll;
+	int ll_stride, ll_pA, ll_att, ll_pC, ll_act;
+	float *part_E;  // [2][E.nsplit][D] partial sums of the down projection (E -> A, behind the grid barrier)
 	float *logits;                    // [V]
 	float *samp_f;                    // [3][grid] sampler partials
 	int *samp_i;                      // [grid]
@@ -107,6 +112,9 @@ struct MgArgs {
 	int att_local, att_global;  // CTAs taking part in attention
 	long long *dbg;  // optional: SM-clock stamps of one CTA along the last step (profiling aid)
 	int dbg_cta;     // which CTA records
+	int sched;       // when the next layer's large tiles are requested. Bit 0: up/gate after the down projection's poll (else
+	                 // right after the gate product); bit 1: down tiles after phase A's prologue (else after the down
+	                 // product). A burst of bulk copies delays the small hand-off loads issued while it lands.
 	int dbg_cap;
 };
 
@@ -156,16 +164,23 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
 	return v;
 }
 
-// Flag-carrying hand-off: the producer stores {value, tag} as one 8-byte word; the
-// consumer polls the word itself until the tag is the one it expects. No fence,
-// no counter: the data is its own ready flag (8-byte stores are single-copy atomic).
-__device__ __forceinline__ void st_flagged(uint2 *p, float v, unsigned tag) {
-	asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+// Self-validating hand-off ("LL" style): the consumer's buffer is filled with a sentinel that no
+// computation produces (all ones, a NaN the hardware never generates); the producer stores plain
+// values; the consumer loads the data itself and repeats a load until none of its words is the
+// sentinel. 4-byte accesses are single-copy atomic, so a word is either old (sentinel) or new.
+// One L2 round trip hands the data over; no flag, no fence, no counter.
+constexpr unsigned MG_LL_EMPTY = 0xFFFFFFFFu;
+__device__ __forceinline__ void ll_store(float *p, float v) {
+	asm volatile("st.relaxed.gpu.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
-__device__ __forceinline__ uint2 ld_flagged(const uint2 *p) {
-	uint2 r;
-	asm volatile("ld.relaxed.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+__device__ __forceinline__ float4 ll_load4_once(const float *p) {
+	float4 r;
+	asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p) : "memory");
 	return r;
+}
+__device__ __forceinline__ bool ll_valid(const float4 &v) {
+	return __float_as_uint(v.x) != MG_LL_EMPTY && __float_as_uint(v.y) != MG_LL_EMPTY &&
+	       __float_as_uint(v.z) != MG_LL_EMPTY && __float_as_uint(v.w) != MG_LL_EMPTY;
 }
 
 struct MgCtx {
@@ -187,6 +202,20 @@ __device__ __forceinline__ void mg_wait_tma(MgCtx &c, uint64_t *bar, uint32_t pa
 			return;
 		}
 	}
+}
+
+// Polling discipline of the self-validating hand-off: a batch of loads is issued, and if any
+// word is still empty the WHOLE batch is reloaded after a short pause (compact code; the retry is
+// the rare path). ll_retry() counts the rounds and gives up after MG_SPIN_CAP of them.
+__device__ __noinline__ bool ll_retry(MgCtx &c, int &spins) {
+	if (*(volatile int *)c.s_abort) return false;
+	if (++spins > MG_SPIN_CAP) {
+		*c.s_abort = 1;
+		atomicExch(c.err, 5);
+		return false;
+	}
+	__nanosleep(20);
+	return true;
 }
 
 // grid-wide barrier, split so that work which does not depend on other CTAs
@@ -415,154 +444,260 @@ __device__ __noinline__ float mg_tile_colsum(const uint8_t *tile, int rows, int 
 
 // TMA issue for one phase region: `nmat` matrices (1, or 2 for up+gate), each
 // nboxes boxes of box_rows rows at byte column x, rows from y0.
-__device__ __noinline__ void mg_issue(const MgPhase &ph, uint8_t *dst, uint64_t *bar, const CUtensorMap *m0,
-                                         const CUtensorMap *m1, int x, int y0, uint64_t pol) {
-	// called by every lane of one warp: lane 0 arms the barrier, then lane b issues box b
-	// (a TMA issue costs the issuing thread ~0.1 us, so the boxes go out side by side)
-	const int box_bytes = ph.TN * ph.box_rows;
-	const int nmat = m1 ? 2 : 1;
+// Untiled bulk copy global -> this CTA's shared memory, completing on an mbarrier. Both addresses
+// 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar, uint64_t pol) {
+	asm volatile(
+	    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
+	    "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+	    : "memory");
+}
+// A CTA's unit of a weight matrix is one contiguous block of the re-tiled weight copy (see
+// retile_kernel): the whole region is fetched with a few large sequential copies. Called by every
+// lane of one warp: lane 0 arms the barrier, then lane i issues piece i.
+constexpr uint32_t MG_BULK_PIECE = 16384;
+__device__ __noinline__ void mg_issue(uint8_t *dst, const int8_t *src, uint32_t bytes, uint64_t *bar, uint64_t pol) {
 	const int lane = threadIdx.x & 31;
 	if (lane == 0) {
 		fence_proxy_async();
-		mbar_expect_tx(bar, uint32_t(box_bytes * ph.nboxes * nmat));
+		mbar_expect_tx(bar, bytes);
 	}
 	__syncwarp();
-	for (int b = lane; b < ph.nboxes * nmat; b += 32) {
-		const int bb = b % ph.nboxes;
-		tma_load_2d(dst + b * box_bytes, (b < ph.nboxes) ? m0 : m1, x, y0 + bb * ph.box_rows, bar, pol);
-	}
+	for (uint32_t off = lane * MG_BULK_PIECE; off < bytes; off += 32 * MG_BULK_PIECE)
+		bulk_load(dst + off, src + off, min(MG_BULK_PIECE, bytes - off), bar, pol);
 }
-
-// which matrix / column a phase-A unit covers: tiles run over Q | K | V
-struct MgQkvTile {
-	int which;  // 0 q, 1 k, 2 v
-	int x;      // byte column inside that matrix
-	int col;    // column inside the concatenated [QD + 2*KD] vector
-};
-__device__ __forceinline__ MgQkvTile mg_qkv_tile(const MgArgs &a, int tile) {
-	const int tq = a.QD / a.A.TN, tk = a.KD / a.A.TN;
-	MgQkvTile r;
-	if (tile < tq) {
-		r.which = 0;
-		r.x = tile * a.A.TN;
-		r.col = r.x;
-	} else if (tile < tq + tk) {
-		r.which = 1;
-		r.x = (tile - tq) * a.A.TN;
-		r.col = a.QD + r.x;
-	} else {
-		r.which = 2;
-		r.x = (tile - tq - tk) * a.A.TN;
-		r.col = a.QD + a.KD + r.x;
-	}
-	return r;
-}
-
-__device__ __forceinline__ void mg_issue_A(const MgArgs &a, const MgLayer *lys, int l, int cta, uint8_t *dst,
-                                           uint64_t *bar, uint64_t pol) {
+__device__ __forceinline__ void mg_issue_A(const MgArgs &a, const MgLayer *, int l, int cta, uint8_t *dst, uint64_t *bar,
+                                           uint64_t pol) {
 	if (cta >= a.A.units) return;
-	const MgLayer &ly = lys[l];
-	const int tile = cta % a.A.ntiles, split = cta / a.A.ntiles;
-	MgQkvTile t = mg_qkv_tile(a, tile);
-	const int tm = t.which == 0 ? ly.tm_q : (t.which == 1 ? ly.tm_k : ly.tm_v);
-	mg_issue(a.A, dst, bar, a.tmaps + tm, nullptr, t.x, split * a.A.kc, pol);
+	mg_issue(dst, a.tiled + size_t(l) * a.tl_layer + a.tl_A + size_t(cta) * a.A.bytes, a.A.bytes, bar, pol);
 }
-__device__ __forceinline__ void mg_issue_C(const MgArgs &a, const MgLayer *lys, int l, int cta, uint8_t *dst,
-                                           uint64_t *bar, uint64_t pol) {
+__device__ __forceinline__ void mg_issue_C(const MgArgs &a, const MgLayer *, int l, int cta, uint8_t *dst, uint64_t *bar,
+                                           uint64_t pol) {
 	if (cta >= a.C.units) return;
-	const int tile = cta % a.C.ntiles, split = cta / a.C.ntiles;
-	mg_issue(a.C, dst, bar, a.tmaps + lys[l].tm_o, nullptr, tile * a.C.TN, split * a.C.kc, pol);
+	mg_issue(dst, a.tiled + size_t(l) * a.tl_layer + a.tl_C + size_t(cta) * a.C.bytes, a.C.bytes, bar, pol);
 }
-__device__ __forceinline__ void mg_issue_D(const MgArgs &a, const MgLayer *lys, int l, int cta, uint8_t *dst,
-                                           uint64_t *bar, uint64_t pol) {
+__device__ __forceinline__ void mg_issue_D(const MgArgs &a, const MgLayer *, int l, int cta, uint8_t *dst, uint64_t *bar,
+                                           uint64_t pol) {
 	if (cta >= a.Dp.units) return;
-	mg_issue(a.Dp, dst, bar, a.tmaps + lys[l].tm_u, a.tmaps + lys[l].tm_g, cta * a.Dp.TN, 0, pol);
+	mg_issue(dst, a.tiled + size_t(l) * a.tl_layer + a.tl_D + size_t(cta) * a.Dp.bytes, a.Dp.bytes, bar, pol);
 }
-__device__ __forceinline__ void mg_issue_E(const MgArgs &a, const MgLayer *lys, int l, int cta, uint8_t *dst,
-                                           uint64_t *bar, uint64_t pol) {
+__device__ __forceinline__ void mg_issue_E(const MgArgs &a, const MgLayer *, int l, int cta, uint8_t *dst, uint64_t *bar,
+                                           uint64_t pol) {
 	if (cta >= a.E.units) return;
-	const int tile = cta % a.E.ntiles, split = cta / a.E.ntiles;
-	mg_issue(a.E, dst, bar, a.tmaps + lys[l].tm_d, nullptr, tile * a.E.TN, split * a.E.kc, pol);
+	mg_issue(dst, a.tiled + size_t(l) * a.tl_layer + a.tl_E + size_t(cta) * a.E.bytes, a.E.bytes, bar, pol);
 }
+
+// Copy `ntiles_mat` column tiles x `nsplit` K-splits of a row-major int8 matrix [K][N] into unit
+// order: unit (split, tile0 + t) becomes a contiguous [kc][TN] block at
+// dst + (split * ntiles_total + tile0 + t) * unit_stride + dst_off. One thread per 16 bytes.
+__global__ void retile_kernel(int8_t *dst, const int8_t *src, int N, int TN, int kc, int nsplit, int ntiles_total, int tile0,
+                              int ntiles_mat, size_t unit_stride, size_t dst_off) {
+	const int segs = TN / 16;
+	const size_t total = size_t(nsplit) * ntiles_mat * kc * segs;
+	for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+		const int seg = int(i % segs);
+		const int r = int((i / segs) % kc);
+		const int t = int((i / (size_t(segs) * kc)) % ntiles_mat);
+		const int split = int(i / (size_t(segs) * kc * ntiles_mat));
+		const int4 v = *reinterpret_cast<const int4 *>(src + size_t(split * kc + r) * N + t * TN + seg * 16);
+		*reinterpret_cast<int4 *>(dst + size_t(split * ntiles_total + tile0 + t) * unit_stride + dst_off + (size_t(r) * segs + seg) * 16) = v;
+	}
+}
+
 
 
 // Per-thread slices (d = tid, tid+384, tid+768) of the three D-long vectors a
 // residual+norm prologue needs. They are cold in DRAM (read once per token),
 // so they are loaded into registers BEFORE the grid barrier that precedes the
 // prologue and are there when the barrier opens.
+// Norm weights and column scales of a residual+norm prologue, held in registers:
+// thread t < D/4 owns elements 4t..4t+3 of every D-vector.
 struct MgVec3 {
-	float s[3], wpost[3], wpre[3];
+	float4 s, wpost, wpre;
 };
 __device__ __forceinline__ void mg_load_vec3(MgVec3 &v, const float *scale, const float *w_post, const float *w_pre, int D) {
-#pragma unroll
-	for (int j = 0; j < 3; j++) {
-		const int d = threadIdx.x + j * MG_THREADS;
-		const bool in = d < D;
-		v.s[j] = (in && scale) ? __ldg(scale + d) : 0.0f;
-		v.wpost[j] = (in && w_post) ? __ldg(w_post + d) : 0.0f;
-		v.wpre[j] = (in && w_pre) ? __ldg(w_pre + d) : 0.0f;
-	}
+	const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+	const int t = threadIdx.x;
+	const bool in = 4 * t < D;
+	v.s = (in && scale) ? __ldg(reinterpret_cast<const float4 *>(scale) + t) : z;
+	v.wpost = (in && w_post) ? __ldg(reinterpret_cast<const float4 *>(w_post) + t) : z;
+	v.wpre = (in && w_pre) ? __ldg(reinterpret_cast<const float4 *>(w_pre) + t) : z;
 }
 
 // If has_t: t[d] = scale[d] * sum_s part[s][d];  h += rmsnorm(t; w_post).
 // Then xs[0..D) = rmsnorm(h; w_pre). Every CTA computes the same bits.
-// D <= 3 * MG_THREADS. The partial sums are fetched eight at a time so that
-// the L2 round trips overlap.
-__device__ __noinline__ void mg_resnorm(const MgArgs &a, float *h, float *xs, float *bred, bool has_t, const float *part,
-                                        int nsplit, const MgVec3 v, float *x_out) {
+// D <= 4 * MG_THREADS, D % 4 == 0. The partial sums of all splits are requested
+// at once so that the L2 round trips overlap; with `ll` they are polled until
+// complete (self-validating hand-off), otherwise they are plain loads behind a
+// grid barrier. Splits are added in ascending order.
+__device__ __noinline__ void mg_resnorm(const MgArgs &a, MgCtx &c, float *h, float *xs, float *bred, bool has_t,
+                                        const float *part, int nsplit, bool ll, const MgVec3 v, float *x_out) {
 	const int D = a.D, tid = threadIdx.x;
+	const bool in = 4 * tid < D;
+	float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
+	if (in) hv = *reinterpret_cast<const float4 *>(h + 4 * tid);  // own elements: written by this thread
 	if (has_t) {
-		float tv[3] = {0.0f, 0.0f, 0.0f};
+		float4 tv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
 		for (int s0 = 0; s0 < nsplit; s0 += 8) {
-			float pv[3][8];
+			float4 pv[8];
+			int spins = 0;
+			bool ok;
+			do {
+				ok = true;
 #pragma unroll
-			for (int j = 0; j < 3; j++) {
-				const int d = tid + j * MG_THREADS;
+				for (int q = 0; q < 8; q++) {
+					pv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+					if (in && s0 + q < nsplit) {
+						const float *src = part + size_t(s0 + q) * D + 4 * tid;
+						pv[q] = ll ? ll_load4_once(src) : __ldcg(reinterpret_cast<const float4 *>(src));
+					}
+				}
 #pragma unroll
-				for (int q = 0; q < 8; q++)
-					pv[j][q] = (d < D && s0 + q < nsplit) ? __ldcg(part + size_t(s0 + q) * D + d) : 0.0f;
+				for (int q = 0; q < 8; q++) ok = ok && ll_valid(pv[q]);
+			} while (ll && !ok && ll_retry(c, spins));
+#pragma unroll
+			for (int q = 0; q < 8; q++) {
+				tv.x += pv[q].x;
+				tv.y += pv[q].y;
+				tv.z += pv[q].z;
+				tv.w += pv[q].w;
 			}
-#pragma unroll
-			for (int j = 0; j < 3; j++)
-#pragma unroll
-				for (int q = 0; q < 8; q++) tv[j] += pv[j][q];
 		}
-		float ss = 0.0f;
-#pragma unroll
-		for (int j = 0; j < 3; j++) {
-			tv[j] *= v.s[j];
-			ss = fmaf(tv[j], tv[j], ss);
-		}
+		tv.x *= v.s.x;
+		tv.y *= v.s.y;
+		tv.z *= v.s.z;
+		tv.w *= v.s.w;
+		float ss = fmaf(tv.x, tv.x, fmaf(tv.y, tv.y, fmaf(tv.z, tv.z, tv.w * tv.w)));
 		ss = mg_block_sum<MG_NWARPS>(ss, bred);
 		const float r1 = inv_rms(ss, D);
-#pragma unroll
-		for (int j = 0; j < 3; j++) {
-			const int d = tid + j * MG_THREADS;
-			if (d < D) h[d] = h[d] + (tv[j] * r1) * (v.wpost[j] + 1.0f);
-		}
+		hv.x = hv.x + (tv.x * r1) * (v.wpost.x + 1.0f);
+		hv.y = hv.y + (tv.y * r1) * (v.wpost.y + 1.0f);
+		hv.z = hv.z + (tv.z * r1) * (v.wpost.z + 1.0f);
+		hv.w = hv.w + (tv.w * r1) * (v.wpost.w + 1.0f);
+		if (in) *reinterpret_cast<float4 *>(h + 4 * tid) = hv;
 	}
-	float hv[3];
-	float ss2 = 0.0f;
-#pragma unroll
-	for (int j = 0; j < 3; j++) {
-		const int d = tid + j * MG_THREADS;
-		hv[j] = d < D ? h[d] : 0.0f;  // own element: written by this thread
-		ss2 = fmaf(hv[j], hv[j], ss2);
-	}
+	float ss2 = fmaf(hv.x, hv.x, fmaf(hv.y, hv.y, fmaf(hv.z, hv.z, hv.w * hv.w)));
 	ss2 = mg_block_sum<MG_NWARPS>(ss2, bred);
 	const float r2 = inv_rms(ss2, D);
-#pragma unroll
-	for (int j = 0; j < 3; j++) {
-		const int d = tid + j * MG_THREADS;
-		if (d < D) {
-			const float y = (hv[j] * r2) * (v.wpre[j] + 1.0f);
-			xs[d] = y;
-			if (x_out) x_out[d] = y;
-		}
+	if (in) {
+		float4 y;
+		y.x = (hv.x * r2) * (v.wpre.x + 1.0f);
+		y.y = (hv.y * r2) * (v.wpre.y + 1.0f);
+		y.z = (hv.z * r2) * (v.wpre.z + 1.0f);
+		y.w = (hv.w * r2) * (v.wpre.w + 1.0f);
+		*reinterpret_cast<float4 *>(xs + 4 * tid) = y;
+		if (x_out) *reinterpret_cast<float4 *>(x_out + 4 * tid) = y;
 	}
 	__syncthreads();
 }
 
+// Phase C prologue: merge the attention partials for rows k0..k0+kc of the head-major output
+// into xs[0..kc). Kept out of line so that its registers do not add to the layer loop's.
+__device__ __noinline__ void mg_attn_merge(const MgArgs &a, MgCtx &ctx, const float *attn_part, int nsA, int k0, float *att,
+                                           float *red, float *xs) {
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	// Merge the attention partials for rows k0..k0+kc of the head-major output:
+	// o = sum_s w[s][h] * o_s with w = exp(m_s - M) / sum_s l_s exp(m_s - M).
+	// Thread -> (16-byte piece of the row range, group of partials); every load is in
+	// flight before the first wait, and the partials are polled until complete.
+	float *sml = att;                   // [nsA][8]: m[4], l[4] of every partial
+	float *wgt = att + 8 * MG_MAX_ATT;  // [nsA][4]
+	const int kc4 = a.C.kc / 4;
+	const int ngrp = max(1, MG_THREADS / kc4);
+	const int per = (nsA + ngrp - 1) / ngrp;  // partials per group
+	const int grp = tid / kc4, c4 = tid - grp * kc4;
+	const bool worker = grp < ngrp;
+	const int sp0 = grp * per, sp1 = min(nsA, sp0 + per);
+	// stage 1: the (m, l) words of every partial. They are small, so CTAs that idle through the
+	// attention phase poll these and leave the L2 to the attention CTAs.
+	{
+		float4 mlv = make_float4(0.f, 0.f, 0.f, 0.f);
+		const float *mlp = attn_part + size_t(tid >> 1) * (AT_NH * AT_HD + 8) + AT_NH * AT_HD + 4 * (tid & 1);
+		int spins = 0;
+		if (tid < 2 * nsA) {
+			do {
+				mlv = ll_load4_once(mlp);
+			} while (!ll_valid(mlv) && ll_retry(ctx, spins));
+			*reinterpret_cast<float4 *>(sml + (tid >> 1) * 8 + 4 * (tid & 1)) = mlv;
+		}
+	}
+	__syncthreads();
+	if (warp < AT_NH) {  // warp = head; lanes stride over the partials
+		float M = -INFINITY;
+#pragma unroll 1
+		for (int sp = lane; sp < nsA; sp += 32) M = fmaxf(M, sml[sp * 8 + warp]);
+		M = warp_max(M);
+		float Ls = 0.0f;
+#pragma unroll 1
+		for (int sp = lane; sp < nsA; sp += 32) {
+			const float ms = sml[sp * 8 + warp];
+			const float ee = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+			wgt[sp * 4 + warp] = ee;
+			Ls = fmaf(sml[sp * 8 + 4 + warp], ee, Ls);
+		}
+		Ls = warp_sum(Ls);
+		const float inv = 1.0f / Ls;
+#pragma unroll 1
+		for (int sp = lane; sp < nsA; sp += 32) wgt[sp * 4 + warp] *= inv;
+	}
+	// stage 2: the partial outputs, eight 16-byte pieces in flight per thread
+	float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+	const int eh = (k0 + 4 * c4) / AT_HD;
+	float4 ov[8];
+	auto load_batch = [&](int s0) {
+		int spins = 0;
+		bool ok;
+		do {
+			ok = true;
+#pragma unroll
+			for (int q = 0; q < 8; q++) {
+				ov[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+				if (worker && s0 + q < sp1) ov[q] = ll_load4_once(attn_part + size_t(s0 + q) * (AT_NH * AT_HD + 8) + k0 + 4 * c4);
+			}
+#pragma unroll
+			for (int q = 0; q < 8; q++) ok = ok && ll_valid(ov[q]);
+		} while (!ok && ll_retry(ctx, spins));
+	};
+	load_batch(sp0);
+	__syncthreads();  // the weights are ready
+#pragma unroll 1
+	for (int s0 = sp0; s0 < sp1; s0 += 8) {
+		if (s0 > sp0) load_batch(s0);
+#pragma unroll
+		for (int q = 0; q < 8; q++) {
+			if (worker && s0 + q < sp1) {
+				const float w = wgt[(s0 + q) * 4 + eh];
+				acc.x = fmaf(ov[q].x, w, acc.x);
+				acc.y = fmaf(ov[q].y, w, acc.y);
+				acc.z = fmaf(ov[q].z, w, acc.z);
+				acc.w = fmaf(ov[q].w, w, acc.w);
+			}
+		}
+	}
+	if (worker) *reinterpret_cast<float4 *>(red + grp * a.C.kc + 4 * c4) = acc;
+	__syncthreads();
+	if (tid < a.C.kc) {
+		float O = 0.0f;
+#pragma unroll 1
+		for (int g = 0; g < ngrp; g++) O += red[g * a.C.kc + tid];
+		xs[tid] = O;
+	}
+	__syncthreads();
+
+}
+
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+	uint32_t ok;
+	asm volatile(
+	    "{\n\t.reg .pred p;\n\t"
+	    "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+	    "selp.u32 %0, 1, 0, p;\n\t}"
+	    : "=r"(ok)
+	    : "r"(smem_u32(bar)), "r"(parity)
+	    : "memory");
+	return ok != 0;
+}
 #define MG_STAMP()                                                   \
 	do {                                                             \
 		if (dbg_on && dbg_n < a.dbg_cap) a.dbg[dbg_n++] = clock64(); \
@@ -663,38 +798,55 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 			}
 			const int chunk = (valid + nsA - 1) / nsA;
 			const int j0 = cta * chunk, j1 = min(valid, j0 + chunk);
+			// Hand-off buffers of this layer (one of two copies; the other copy is wiped below for
+			// the next layer — its readers all passed the grid barrier that ended the previous layer).
+			const int lc = step * L + l;
+			float *const llb = a.ll + size_t(lc & 1) * a.ll_stride;
+#define part_A (llb + a.ll_pA)
+#define attn_part (llb + a.ll_att)
+#define part_C (llb + a.ll_pC)
+#define act (llb + a.ll_act)
+#define part_E_cur (a.part_E + size_t(lc & 1) * a.E.nsplit * D)
+#define part_E_prev (a.part_E + size_t((lc & 1) ^ 1) * a.E.nsplit * D)
 			// ============================================================ A: QKV
-			float qsc[4];  // scales of this thread's q|k|v columns (attention CTAs)
+			float4 qsc = make_float4(0.f, 0.f, 0.f, 0.f);  // scales of this thread's 4 q|k|v columns (attention CTAs)
 			{
 				const bool active = cta < a.A.units;
 				const int tile = active ? cta % a.A.ntiles : 0, split = active ? cta / a.A.ntiles : 0;
 				const int k0 = split * a.A.kc;
-				mg_resnorm(a, h, xs, bred, l > 0, a.part_E, a.E.nsplit, vA, nullptr);
+				mg_resnorm(a, ctx, h, xs, bred, l > 0, part_E_prev, a.E.nsplit, false, vA, nullptr);
+				if (warp == 1 && l > 0 && (a.sched & 2)) mg_issue_E(a, s_ly, l, cta, R_E, &bar_E, pol);
+				MG_STAMP();
+				if (active) mg_wait_tma(ctx, &bar_A, pA);
 				MG_STAMP();
 				if (active) {
-					mg_wait_tma(ctx, &bar_A, pA);
-					MG_STAMP();
 					const float s = mg_tile_colsum(R_A, a.A.kc, a.A.segs, xs + k0, red);
-					MgQkvTile t = mg_qkv_tile(a, tile);
-					if (tid < a.A.TN) __stcg(a.part_A + size_t(split) * NQ + t.col + tid, s);
+					// q, k, v tiles are consecutive and equally wide: tile -> column of the q|k|v vector
+					if (tid < a.A.TN) ll_store(part_A + size_t(split) * NQ + tile * a.A.TN + tid, s);
 				}
 				pA ^= 1;
 				MG_STAMP();
-				MgBar gb;
-				mg_arrive(ctx, gb);
+				__syncthreads();  // R_A is free again
 				if (warp == 1) {
 					if (l + 1 < L)
 						mg_issue_A(a, s_ly, l + 1, cta, R_A, &bar_A, pol);
 					else if (more)
 						mg_issue_A(a, s_ly, 0, cta, R_A, &bar_A, pol);
 				}
-				// cold data of phase B, requested before the barrier
+				{  // wipe this CTA's share of the other copy of the hand-off arena
+					float4 *other = reinterpret_cast<float4 *>(a.ll + size_t((lc & 1) ^ 1) * a.ll_stride);
+					const int n4 = a.ll_stride / 4, per = (n4 + G - 1) / G;
+					const float e = __uint_as_float(MG_LL_EMPTY);
+#pragma unroll 1
+					for (int i = cta * per + tid; i < min(n4, (cta + 1) * per); i += MG_THREADS)
+						__stcg(other + i, make_float4(e, e, e, e));
+				}
+				// cold data of phase B
 				if (cta < nsA) {
-#pragma unroll
-					for (int j = 0; j < 4; j++) {
-						const int n = tid + j * MG_THREADS;
-						qsc[j] = 0.0f;
-						if (n < NQ) qsc[j] = n < a.QD ? __ldg(ly.sq + n) : (n < a.QD + a.KD ? __ldg(ly.sk + n - a.QD) : __ldg(ly.sv + n - a.QD - a.KD));
+					if (4 * tid < NQ) {
+						const int n = 4 * tid;
+						const float *sp = n < a.QD ? ly.sq + n : (n < a.QD + a.KD ? ly.sk + (n - a.QD) : ly.sv + (n - a.QD - a.KD));
+						qsc = __ldg(reinterpret_cast<const float4 *>(sp));
 					}
 					const float *cosr = a.rope[ly.is_local][0] + size_t(p) * AT_HD;
 					const float *sinr = a.rope[ly.is_local][1] + size_t(p) * AT_HD;
@@ -712,33 +864,39 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					}
 				}
 				MG_STAMP();
-				mg_wait(ctx, gb);
-				MG_STAMP();
 			}
 			// ============================================================ B: attention
 			{
 				if (cta < nsA) {
-					// q|k|v = scale * sum of K-split partials
+					// q|k|v = scale * sum of K-split partials (polled: phase A's CTAs store them as they finish)
 					float *qkv = red;  // NQ floats; `red` is free here
-					{
-						float pv[4][8];
-#pragma unroll
-						for (int j = 0; j < 4; j++) {
-							const int n = tid + j * MG_THREADS;
-#pragma unroll
-							for (int q = 0; q < 8; q++)
-								pv[j][q] = (n < NQ && q < a.A.nsplit) ? __ldcg(a.part_A + size_t(q) * NQ + n) : 0.0f;
-						}
-#pragma unroll
-						for (int j = 0; j < 4; j++) {
-							const int n = tid + j * MG_THREADS;
-							float s = 0.0f;
-#pragma unroll
-							for (int q = 0; q < 8; q++) s += pv[j][q];
+					if (4 * tid < NQ) {
+						float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-							for (int q = 8; q < a.A.nsplit; q++) s += __ldcg(a.part_A + size_t(q) * NQ + n);
-							if (n < NQ) qkv[n] = s * qsc[j];
+						for (int s0 = 0; s0 < a.A.nsplit; s0 += 8) {
+							float4 pv[8];
+							int spins = 0;
+							bool ok;
+							do {
+								ok = true;
+#pragma unroll
+								for (int q = 0; q < 8; q++) {
+									pv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+									if (s0 + q < a.A.nsplit) pv[q] = ll_load4_once(part_A + size_t(s0 + q) * NQ + 4 * tid);
+								}
+#pragma unroll
+								for (int q = 0; q < 8; q++) ok = ok && ll_valid(pv[q]);
+							} while (!ok && ll_retry(ctx, spins));
+#pragma unroll
+							for (int q = 0; q < 8; q++) {
+								sum.x += pv[q].x;
+								sum.y += pv[q].y;
+								sum.z += pv[q].z;
+								sum.w += pv[q].w;
+							}
 						}
+						*reinterpret_cast<float4 *>(qkv + 4 * tid) =
+						    make_float4(sum.x * qsc.x, sum.y * qsc.y, sum.z * qsc.z, sum.w * qsc.w);
 					}
 					__syncthreads();
 					const float *cosr = a.rope[ly.is_local][0] + size_t(p) * AT_HD;
@@ -821,7 +979,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					*reinterpret_cast<float4 *>(red + (grp * AT_NH + hh) * AT_HD + 4 * lane) = o0;
 					*reinterpret_cast<float4 *>(red + (grp * AT_NH + hh) * AT_HD + 128 + 4 * lane) = o1;
 					__syncthreads();
-					float *prow = a.attn_part + size_t(cta) * (AT_NH * AT_HD + 8);
+					float *prow = attn_part + size_t(cta) * (AT_NH * AT_HD + 8);
 #pragma unroll 1
 					for (int e = tid; e < AT_NH * AT_HD; e += MG_THREADS) {
 						const int eh = e / AT_HD;
@@ -833,15 +991,14 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 							Ls = fmaf(wl[g][eh], ee, Ls);
 							O = fmaf(red[(g * AT_NH + eh) * AT_HD + (e % AT_HD)], ee, O);
 						}
-						__stcg(prow + e, O);
+						ll_store(prow + e, O);
 						if ((e % AT_HD) == 0) {
-							__stcg(prow + AT_NH * AT_HD + eh, M);
-							__stcg(prow + AT_NH * AT_HD + 4 + eh, Ls);
+							ll_store(prow + AT_NH * AT_HD + eh, M);
+							ll_store(prow + AT_NH * AT_HD + 4 + eh, Ls);
 						}
 					}
+					__syncthreads();  // `red`, `att` are reused by phase C
 				}
-				MG_STAMP();
-				mg_grid_sync(ctx);
 				MG_STAMP();
 			}
 			// ============================================================ C: O projection
@@ -852,59 +1009,17 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				const int tile = active ? cta % a.C.ntiles : 0, split = active ? cta / a.C.ntiles : 0;
 				const int k0 = split * a.C.kc;
 				if (active) {
-					// merge the attention partials for rows k0..k0+kc of the head-major output:
-					// o = sum_s w[s][h] * o_s with w = exp(m_s - M) / sum_s l_s exp(m_s - M)
-					float *sml = att;             // [nsA][8]: m[4], l[4] of every partial
-					float *wgt = att + 8 * MG_MAX_ATT;  // [nsA][4]
-#pragma unroll 1
-					for (int i = tid; i < nsA * 8; i += MG_THREADS)
-						sml[i] = __ldcg(a.attn_part + size_t(i >> 3) * (AT_NH * AT_HD + 8) + AT_NH * AT_HD + (i & 7));
-					__syncthreads();
-					if (warp < AT_NH) {  // warp = head; lanes stride over the partials
-						float M = -INFINITY;
-#pragma unroll 1
-						for (int sp = lane; sp < nsA; sp += 32) M = fmaxf(M, sml[sp * 8 + warp]);
-						M = warp_max(M);
-						float Ls = 0.0f;
-#pragma unroll 1
-						for (int sp = lane; sp < nsA; sp += 32) {
-							const float ms = sml[sp * 8 + warp];
-							const float ee = (ms == -INFINITY) ? 0.0f : expf(ms - M);
-							wgt[sp * 4 + warp] = ee;
-							Ls = fmaf(sml[sp * 8 + 4 + warp], ee, Ls);
-						}
-						Ls = warp_sum(Ls);
-						const float inv = 1.0f / Ls;
-#pragma unroll 1
-						for (int sp = lane; sp < nsA; sp += 32) wgt[sp * 4 + warp] *= inv;
-					}
-					__syncthreads();
-#pragma unroll 1
-					for (int r = tid; r < a.C.kc; r += MG_THREADS) {
-						const int e = k0 + r, eh = e / AT_HD;
-						float O = 0.0f;
-#pragma unroll 1
-						for (int s0 = 0; s0 < nsA; s0 += 16) {
-							float ov[16];
-#pragma unroll
-							for (int q = 0; q < 16; q++)
-								ov[q] = (s0 + q < nsA) ? __ldcg(a.attn_part + size_t(s0 + q) * (AT_NH * AT_HD + 8) + e) : 0.0f;
-#pragma unroll
-							for (int q = 0; q < 16; q++)
-								if (s0 + q < nsA) O = fmaf(ov[q], wgt[(s0 + q) * 4 + eh], O);
-						}
-						xs[r] = O;
-					}
-					__syncthreads();
-					MG_STAMP();
+					mg_attn_merge(a, ctx, attn_part, nsA, k0, att, red, xs);
+				}
+				MG_STAMP();
+				if (active) {
 					mg_wait_tma(ctx, &bar_C, pC);
 					const float s = mg_tile_colsum(R_C, a.C.kc, a.C.segs, xs, red);
-					if (tid < a.C.TN) __stcg(a.part_C + size_t(split) * D + tile * a.C.TN + tid, s);
+					if (tid < a.C.TN) ll_store(part_C + size_t(split) * D + tile * a.C.TN + tid, s);
 				}
 				pC ^= 1;
 				MG_STAMP();
-				MgBar gb;
-				mg_arrive(ctx, gb);
+				__syncthreads();  // R_C is free again
 				if (warp == 1) {
 					if (l + 1 < L)
 						mg_issue_C(a, s_ly, l + 1, cta, R_C, &bar_C, pol);
@@ -916,28 +1031,26 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					su_r = __ldg(ly.su + cta * a.Dp.TN + tid);
 					sg_r = __ldg(ly.sg + cta * a.Dp.TN + tid);
 				}
-				mg_wait(ctx, gb);
 				MG_STAMP();
 			}
 			// ============================================================ D: up & gate + GeGLU
-			const unsigned tag = a.seq0 + unsigned(step) * unsigned(L) + unsigned(l) + 1u;
 			{
 				const bool active = cta < a.Dp.units;
-				mg_resnorm(a, h, xs, bred, true, a.part_C, a.C.nsplit, vD, nullptr);
+				mg_resnorm(a, ctx, h, xs, bred, true, part_C, a.C.nsplit, true, vD, nullptr);
+				MG_STAMP();
+				if (active) mg_wait_tma(ctx, &bar_D, pD);
+				MG_STAMP();
+				float up = 0.0f;
+				if (active) up = mg_tile_colsum(R_D, D, a.Dp.segs, xs, red);
 				MG_STAMP();
 				if (active) {
-					mg_wait_tma(ctx, &bar_D, pD);
-					MG_STAMP();
-					const float up = mg_tile_colsum(R_D, D, a.Dp.segs, xs, red);
-					MG_STAMP();
 					const float gate = mg_tile_colsum(R_D + a.Dp.TN * D, D, a.Dp.segs, xs, red);
-					if (tid < a.Dp.TN) st_flagged(a.act + cta * a.Dp.TN + tid, a.lut(gate * sg_r) * (up * su_r), tag);
+					if (tid < a.Dp.TN) ll_store(act + cta * a.Dp.TN + tid, a.lut(gate * sg_r) * (up * su_r));
 				}
 				pD ^= 1;
 				MG_STAMP();
-				// no grid barrier here: phase E polls the tagged activations it needs
-				__syncthreads();
-				if (warp == 1 && l + 1 < L) mg_issue_D(a, s_ly, l + 1, cta, R_D, &bar_D, pol);
+				__syncthreads();  // R_D is free again
+				if (warp == 1 && l + 1 < L && !(a.sched & 1)) mg_issue_D(a, s_ly, l + 1, cta, R_D, &bar_D, pol);
 				MG_STAMP();
 			}
 			// ============================================================ E: down projection
@@ -946,32 +1059,44 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				const int tile = active ? cta % a.E.ntiles : 0, split = active ? cta / a.E.ntiles : 0;
 				const int k0 = split * a.E.kc;
 				if (active) {
+					// this CTA's rows of the activation vector, polled until complete
+					const int n4 = a.E.kc / 4;
 #pragma unroll 1
-#pragma unroll 1
-					for (int r = tid; r < a.E.kc; r += MG_THREADS) {
-						uint2 w = ld_flagged(a.act + k0 + r);
+					for (int i0 = 0; i0 < n4; i0 += 5 * MG_THREADS) {
+						float4 v[5];
 						int spins = 0;
-						while (w.y != tag && !*(volatile int *)&s_abort) {
-							if (++spins > MG_SPIN_CAP) {
-								s_abort = 1;
-								atomicExch(a.err, 5);
-								break;
+						bool ok;
+						do {
+							ok = true;
+#pragma unroll
+							for (int q = 0; q < 5; q++) {
+								const int i = i0 + q * MG_THREADS + tid;
+								v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+								if (i < n4) v[q] = ll_load4_once(act + k0 + 4 * i);
 							}
-							w = ld_flagged(a.act + k0 + r);
+#pragma unroll
+							for (int q = 0; q < 5; q++) ok = ok && ll_valid(v[q]);
+						} while (!ok && ll_retry(ctx, spins));
+#pragma unroll
+						for (int q = 0; q < 5; q++) {
+							const int i = i0 + q * MG_THREADS + tid;
+							if (i < n4) *reinterpret_cast<float4 *>(xs + 4 * i) = v[q];
 						}
-						xs[r] = __uint_as_float(w.x);
 					}
 					__syncthreads();
 					mg_wait_tma(ctx, &bar_E, pE);
-					MG_STAMP();
+				}
+				if (warp == 1 && l + 1 < L && (a.sched & 1)) mg_issue_D(a, s_ly, l + 1, cta, R_D, &bar_D, pol);
+				MG_STAMP();
+				if (active) {
 					const float s = mg_tile_colsum(R_E, a.E.kc, a.E.segs, xs, red);
-					if (tid < a.E.TN) __stcg(a.part_E + size_t(split) * D + tile * a.E.TN + tid, s);
+					if (tid < a.E.TN) __stcg(part_E_cur + size_t(split) * D + tile * a.E.TN + tid, s);
 				}
 				pE ^= 1;
 				MG_STAMP();
 				MgBar gb;
 				mg_arrive(ctx, gb);
-				if (warp == 1 && l + 1 < L) mg_issue_E(a, s_ly, l + 1, cta, R_E, &bar_E, pol);
+				if (warp == 1 && l + 1 < L && !(a.sched & 2)) mg_issue_E(a, s_ly, l + 1, cta, R_E, &bar_E, pol);
 				if (l + 1 < L)
 					mg_load_vec3(vA, ly.sd, ly.mlp_post, s_ly[l + 1].attn_pre, D);
 				else
@@ -979,13 +1104,20 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				mg_wait(ctx, gb);
 				MG_STAMP();
 			}
+#undef part_A
+#undef attn_part
+#undef part_C
+#undef act
+#undef part_E_cur
+#undef part_E_prev
 		}
 
 		// ================================================================ lm_head
 		// logits[v] = lm_scale[v] * sum_k x[k] W[k,v]; this CTA takes column tiles
 		// cta, cta+G, ...; a tile's K rows stream through a ring of MG_LM_STAGES
 		// stages of LM.box_rows rows laid over the (now idle) D and E regions.
-		mg_resnorm(a, h, xs, bred, true, a.part_E, a.E.nsplit, vA, cta == 0 ? a.xnorm_out : nullptr);
+		mg_resnorm(a, ctx, h, xs, bred, true, a.part_E + size_t((step * L + L - 1) & 1) * a.E.nsplit * D, a.E.nsplit, false, vA,
+		           cta == 0 ? a.xnorm_out : nullptr);
 		MG_STAMP();
 		float best = -INFINITY;  // running max of this CTA's (temperature-scaled) logits, threads < 128
 		int best_i = -1;

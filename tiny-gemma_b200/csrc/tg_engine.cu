@@ -80,6 +80,12 @@ struct LayerW {
 struct tg_model {
 	tg_config cfg;
 	int device = 0;
+	long weights_version = 0;  // bumped by every load
+	// layer weights re-ordered into the persistent decode kernel's per-CTA units (built on first use)
+	int8_t *dec_tiled = nullptr;
+	size_t dec_tiled_bytes = 0;
+	long dec_tiled_version = -1;
+	int dec_tiled_key[12] = {0};
 	uint8_t *blob = nullptr;
 	size_t nbytes = 0;
 	const int8_t *wte = nullptr;
@@ -310,11 +316,10 @@ struct tg_state {
 	MgArgs mega{};
 	CUtensorMap *d_tmaps = nullptr;
 	MgLayer *d_layers = nullptr;
-	float *mg_part_A = nullptr, *mg_part_C = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr;
+	float *mg_ll = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr;
+	size_t mg_ll_bytes = 0;
 	int *mg_samp_i = nullptr;
 	unsigned *mg_bar = nullptr;
-	uint2 *mg_act = nullptr;
-	unsigned mg_seq = 0;  // sequence tags consumed so far by flag-carrying hand-offs
 	int mega_grid = 0;
 	long long *mg_dbg = nullptr;
 	size_t mega_smem = 0;
@@ -741,27 +746,12 @@ int mega_setup(tg_state *s) {
 		return fail(TG_ESHAPE, "persistent kernel limits exceeded");
 	if ((a.Dp.bytes % 16) || (a.off_E % 128)) return fail(TG_ESHAPE, "region alignment");
 
-	// tensor maps: 7 per layer + lm_head
-	std::vector<CUtensorMap> maps(size_t(7) * L + 1);
+	// one tensor map (lm_head); the layer weights come from the re-tiled copy
+	std::vector<CUtensorMap> maps(1);
 	std::vector<MgLayer> lys(L);
 	for (int l = 0; l < L; l++) {
 		const LayerW &w = m->layers[l];
 		MgLayer &ly = lys[l];
-		const int b = 7 * l;
-		TG_TRY(make_tmap(&maps[b + 0], w.Q.q, D, qd, a.A.TN, a.A.box_rows));
-		TG_TRY(make_tmap(&maps[b + 1], w.K.q, D, kd, a.A.TN, a.A.box_rows));
-		TG_TRY(make_tmap(&maps[b + 2], w.V.q, D, kd, a.A.TN, a.A.box_rows));
-		TG_TRY(make_tmap(&maps[b + 3], w.O.q, qd, D, a.C.TN, a.C.box_rows));
-		TG_TRY(make_tmap(&maps[b + 4], w.U.q, D, I, a.Dp.TN, a.Dp.box_rows));
-		TG_TRY(make_tmap(&maps[b + 5], w.G.q, D, I, a.Dp.TN, a.Dp.box_rows));
-		TG_TRY(make_tmap(&maps[b + 6], w.Dn.q, I, D, a.E.TN, a.E.box_rows));
-		ly.tm_q = b + 0;
-		ly.tm_k = b + 1;
-		ly.tm_v = b + 2;
-		ly.tm_o = b + 3;
-		ly.tm_u = b + 4;
-		ly.tm_g = b + 5;
-		ly.tm_d = b + 6;
 		ly.sq = w.Q.s;
 		ly.sk = w.K.s;
 		ly.sv = w.V.s;
@@ -780,8 +770,13 @@ int mega_setup(tg_state *s) {
 		ly.slots = s->slots[l];
 		ly.is_local = w.is_local ? 1 : 0;
 	}
-	TG_TRY(make_tmap(&maps[size_t(7) * L], m->lm_head.q, D, V, a.LM.TN, a.LM.box_rows));
-	a.tm_lm = 7 * L;
+	TG_TRY(make_tmap(&maps[0], m->lm_head.q, D, V, a.LM.TN, a.LM.box_rows));
+	a.tm_lm = 0;
+	a.tl_A = 0;
+	a.tl_C = a.tl_A + size_t(a.A.units) * a.A.bytes;
+	a.tl_D = a.tl_C + size_t(a.C.units) * a.C.bytes;
+	a.tl_E = a.tl_D + size_t(a.Dp.units) * a.Dp.bytes;
+	a.tl_layer = a.tl_E + size_t(a.E.units) * a.E.bytes;
 	TG_CUDA(cudaMalloc(&s->d_tmaps, maps.size() * sizeof(CUtensorMap)));
 	TG_CUDA(cudaMemcpy(s->d_tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
 	TG_CUDA(cudaMalloc(&s->d_layers, lys.size() * sizeof(MgLayer)));
@@ -791,19 +786,20 @@ int mega_setup(tg_state *s) {
 		TG_CUDA(cudaMemset(*p, 0, bytes));
 		return TG_OK;
 	};
-	TG_TRY(allocz((void **)&s->mg_part_A, size_t(a.A.nsplit) * (qd + 2 * kd) * 4));
-	TG_TRY(allocz((void **)&s->mg_part_C, size_t(a.C.nsplit) * D * 4));
-	TG_TRY(allocz((void **)&s->mg_part_E, size_t(a.E.nsplit) * D * 4));
+	// hand-off arena (two copies) and the double-buffered down-projection partial sums
+	auto up4 = [](int n) { return (n + 3) & ~3; };
+	a.ll_pA = 0;
+	a.ll_att = a.ll_pA + up4(a.A.nsplit * (qd + 2 * kd));
+	a.ll_pC = a.ll_att + up4(MG_MAX_ATT * (AT_NH * AT_HD + 8));
+	a.ll_act = a.ll_pC + up4(a.C.nsplit * D);
+	a.ll_stride = a.ll_act + up4(I);
+	s->mg_ll_bytes = size_t(2) * a.ll_stride * 4;
+	TG_CUDA(cudaMalloc(&s->mg_ll, s->mg_ll_bytes));
+	TG_CUDA(cudaMemset(s->mg_ll, 0xFF, s->mg_ll_bytes));
+	TG_TRY(allocz((void **)&s->mg_part_E, size_t(2) * a.E.nsplit * D * 4));
 	TG_TRY(allocz((void **)&s->mg_samp_f, size_t(3) * G * 4));
 	TG_TRY(allocz((void **)&s->mg_samp_i, size_t(G + 8) * 4));
 	TG_TRY(allocz((void **)&s->mg_bar, 64));
-	TG_TRY(allocz((void **)&s->mg_act, size_t(I) * sizeof(uint2)));
-	// attention partials: reuse the state's buffer if it is large enough
-	if (std::max(a.att_local, a.att_global) > std::max(s->attn_nsplit_local, s->attn_nsplit_global)) {
-		cudaFree(s->attn_part);
-		s->attn_part = nullptr;
-		TG_TRY(allocz((void **)&s->attn_part, size_t(s->B) * MG_MAX_ATT * (AT_NH * AT_HD + 8) * 4));
-	}
 	a.tmaps = s->d_tmaps;
 	a.layers = s->d_layers;
 	a.L = L;
@@ -817,11 +813,8 @@ int mega_setup(tg_state *s) {
 	a.wte = m->wte;
 	a.wte_s = m->wte_s;
 	a.sqrtD = float(std::sqrt(double(D)));
-	a.part_A = s->mg_part_A;
-	a.part_C = s->mg_part_C;
+	a.ll = s->mg_ll;
 	a.part_E = s->mg_part_E;
-	a.attn_part = s->attn_part;
-	a.act = s->mg_act;
 	a.logits = s->logits;
 	a.samp_f = s->mg_samp_f;
 	a.samp_i = s->mg_samp_i;
@@ -849,10 +842,56 @@ int mega_setup(tg_state *s) {
 	return TG_OK;
 }
 
+// Build (or refresh after a reload of the weights) the model's copy of the layer weights in unit
+// order: for every layer the units of phase A (q|k|v column tiles x K-splits), C (O projection),
+// D (up tile followed by the gate tile of the same columns) and E (down projection), each unit a
+// contiguous [rows][TN] block, so that a CTA fetches its unit with sequential bulk copies.
+int ensure_decode_tiles(tg_state *s) {
+	tg_model *m = s->m;
+	const MgArgs &a = s->mega;
+	const tg_config &c = m->cfg;
+	const int L = c.n_layers, D = c.hidden_size, I = c.intermediate_size;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	const int key[12] = {a.A.TN, a.A.nsplit, a.C.TN, a.C.nsplit, a.Dp.TN, a.Dp.nsplit, a.E.TN, a.E.nsplit, s->mega_grid, L, D, I};
+	if (m->dec_tiled && m->dec_tiled_version == m->weights_version && std::memcmp(key, m->dec_tiled_key, sizeof key) == 0)
+		return TG_OK;
+	const size_t bytes = a.tl_layer * L;
+	if (m->dec_tiled_bytes != bytes) {
+		cudaFree(m->dec_tiled);
+		m->dec_tiled = nullptr;
+		TG_CUDA(cudaMalloc(&m->dec_tiled, bytes));
+		m->dec_tiled_bytes = bytes;
+	}
+	cudaStream_t st = s->stream;
+	auto run = [&](int8_t *dst, const QW &w, const MgPhase &ph, int ntiles_total, int tile0, size_t unit_stride, size_t dst_off) {
+		const int ntiles_mat = w.N / ph.TN;
+		retile_kernel<<<4 * g_num_sms, 256, 0, st>>>(dst, w.q, w.N, ph.TN, ph.kc, ph.nsplit, ntiles_total, tile0, ntiles_mat,
+		                                             unit_stride, dst_off);
+		count_launch();
+	};
+	for (int l = 0; l < L; l++) {
+		const LayerW &w = m->layers[l];
+		int8_t *base = m->dec_tiled + size_t(l) * a.tl_layer;
+		run(base + a.tl_A, w.Q, a.A, a.A.ntiles, 0, a.A.bytes, 0);
+		run(base + a.tl_A, w.K, a.A, a.A.ntiles, qd / a.A.TN, a.A.bytes, 0);
+		run(base + a.tl_A, w.V, a.A, a.A.ntiles, (qd + kd) / a.A.TN, a.A.bytes, 0);
+		run(base + a.tl_C, w.O, a.C, a.C.ntiles, 0, a.C.bytes, 0);
+		run(base + a.tl_D, w.U, a.Dp, a.Dp.ntiles, 0, a.Dp.bytes, 0);
+		run(base + a.tl_D, w.G, a.Dp, a.Dp.ntiles, 0, a.Dp.bytes, size_t(a.Dp.TN) * D);
+		run(base + a.tl_E, w.Dn, a.E, a.E.ntiles, 0, a.E.bytes, 0);
+	}
+	TG_TRY(check_launch("retile"));
+	std::memcpy(m->dec_tiled_key, key, sizeof key);
+	m->dec_tiled_version = m->weights_version;
+	return TG_OK;
+}
+
 // one cooperative launch: n_steps tokens; sampler 0 none / 1 argmax / 2 min-p
 int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, bool log_tokens) {
 	tg_model *m = s->m;
+	TG_TRY(ensure_decode_tiles(s));
 	MgArgs a = s->mega;
+	a.tiled = m->dec_tiled;
 	a.rope[0][0] = m->rope[0][0];
 	a.rope[0][1] = m->rope[0][1];
 	a.rope[1][0] = m->rope[1][0];
@@ -866,10 +905,11 @@ int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, b
 	a.randf_cap = s->randf_cap;
 	a.tok_log = log_tokens ? s->tok_log : nullptr;
 	a.log_cap = s->log_cap;
-	a.seq0 = s->mg_seq;
-	s->mg_seq += unsigned(n_steps) * unsigned(m->cfg.n_layers) + 1u;
+	// every word of the hand-off arena starts as "empty" (all ones)
+	TG_CUDA(cudaMemsetAsync(s->mg_ll, 0xFF, s->mg_ll_bytes, s->stream));
 	a.dbg = s->mg_dbg;
 	a.dbg_cap = s->mg_dbg ? 4096 : 0;
+	a.sched = env_int("TG_MEGA_SCHED", 1);
 	a.dbg_cta = std::min(std::max(env_int("TG_MEGA_DBG_CTA", 0), 0), s->mega_grid - 1);
 	TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
 	void *params[] = {&a};
@@ -1289,6 +1329,7 @@ int tg_model_free(tg_model *m) {
 	if (!m) return TG_OK;
 	cudaSetDevice(m->device);
 	cudaFree(m->blob);
+	cudaFree(m->dec_tiled);
 	for (int i = 0; i < 2; i++)
 		for (int j = 0; j < 2; j++) cudaFree(m->rope[i][j]);
 	cudaFree(m->gelu);
@@ -1302,6 +1343,7 @@ int tg_model_load_memory(tg_model *m, const void *bytes, size_t nbytes) {
 	TG_CUDA(cudaSetDevice(m->device));
 	TG_CUDA(cudaMemcpy(m->blob, bytes, m->nbytes, cudaMemcpyHostToDevice));
 	m->loaded = true;
+	m->weights_version++;
 	return TG_OK;
 }
 
@@ -1347,7 +1389,10 @@ int tg_model_load_file(tg_model *m, const char *path) {
 	cudaStreamDestroy(st);
 	cudaFreeHost(pin[0]);
 	cudaFreeHost(pin[1]);
-	if (rc == TG_OK) m->loaded = true;
+	if (rc == TG_OK) {
+		m->loaded = true;
+		m->weights_version++;
+	}
 	return rc;
 }
 
@@ -1480,13 +1525,11 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->btc.partial);
 	cudaFree(s->d_tmaps);
 	cudaFree(s->d_layers);
-	cudaFree(s->mg_part_A);
-	cudaFree(s->mg_part_C);
+	cudaFree(s->mg_ll);
 	cudaFree(s->mg_part_E);
 	cudaFree(s->mg_samp_f);
 	cudaFree(s->mg_samp_i);
 	cudaFree(s->mg_bar);
-	cudaFree(s->mg_act);
 	cudaFree(s->mg_dbg);
 	if (s->host_pin) cudaFreeHost(s->host_pin);
 	if (s->stream) cudaStreamDestroy(s->stream);
@@ -2086,7 +2129,7 @@ int tg_state_phase_clocks(tg_state *s, long long *clocks_host, int cap, int *n) 
 	int k = 0;
 	while (k < 4096 && tmp[k] != 0) k++;
 	*n = k;
-	if (clocks_host) std::memcpy(clocks_host, tmp.data(), sizeof(long long) * std::min(k, cap));
+	if (clocks_host) std::memcpy(clocks_host, tmp.data(), sizeof(long long) * std::min(cap >= 4096 ? 4096 : k, cap));
 	TG_CUDA(cudaMemset(s->mg_dbg, 0, 4096 * sizeof(long long)));
 	return TG_OK;
 }

@@ -30,8 +30,8 @@ for rep in range(2):
 L = m.cfg.n_layers
 print("stamps", len(c))
 d = np.diff(c)/1965.0  # us at 1965 MHz
-# layout: 1 (step start) + per layer: A: pro, wait, pre-bar, post-bar (4); B: pre,post (2); C: pro, pre, post (3); D: pro, wait, pre, post (4); E: wait, pre, post (3) = 16 per layer; then lm start, sampler start, end
-names = ["A.pro","A.wait","A.comp","A.arr+pf","A.bar","B.work","B.bar","C.pro","C.comp","C.bar","D.pro","D.wait","D.up","D.gate","D.issue","E.wait","E.comp","E.bar"]
+# layout: 1 (step start) + 16 stamps per layer (see names); then lm_head prologue, lm_head, sampler
+names = ["A.pro","A.wait","A.comp","A.post","B.work","C.pro","C.comp","C.post","D.pro","D.wait","D.up","D.gate","D.issue","E.wait","E.comp","E.bar"]
 NS=len(names)
 per = d[:NS*L].reshape(L,NS)
 for i,nm in enumerate(names):
