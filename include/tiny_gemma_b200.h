@@ -158,6 +158,12 @@ int tg_qgemm(float *c_host, const float *a_host, const int8_t *w_host, const flo
  * (n = 262144 in the reference); minp mutates logits_host like the reference */
 int tg_argmax_logits(const float *logits_host, int n, int *tok);
 int tg_minp_logits(float *logits_host, int n, float minp, float temp, float randf, int *tok);
+/* The last step of ops::minp_logits in isolation (ops.hpp:849-857, the inverse-CDF loop):
+ * *idx = first i with fl(cum0 + p[0] + ... + p[i]) >= randf, the sum taken sequentially in fp32,
+ * or -1 if it never gets there; *cum_out (may be null) = the running sum where the scan stopped.
+ * The GPU evaluates the sequential chain exactly with a parallel scan; this entry exists so that
+ * the exactness can be tested on arbitrary vectors. */
+int tg_inverse_cdf(const float *p_host, int n, float cum0, float randf, int *idx, float *cum_out);
 /* ops::rmsnorm, ops.hpp:182-222, rows x dim in place */
 int tg_rmsnorm(float *x_host, const float *w_host, int rows, int dim);
 

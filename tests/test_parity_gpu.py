@@ -226,6 +226,42 @@ def test_sliding_window_ring_270m(capi, model_270m, ref_or_none, golden, weights
     st.close()
 
 
+def _seq_cross(p, randf, cum0=0.0):
+    c = np.cumsum(np.concatenate([[np.float32(cum0)], p.astype(np.float32)]), dtype=np.float32)[1:]
+    hit = np.nonzero(c >= np.float32(randf))[0]
+    return (int(hit[0]), c[hit[0]]) if hit.size else (-1, c[-1])
+
+
+def test_inverse_cdf_is_the_sequential_fp32_chain(capi):
+    """The parallel scan must give the crossing index AND the running sum of the sequential fp32 chain, bit for
+    bit: random vectors, vectors quantised so that exact ties (round-half-even) are common, wide dynamic range,
+    zeros, a start inside a binade, and thresholds that are never reached."""
+    rng = np.random.default_rng(17)
+    cases = []
+    n = 40000
+    p = rng.random(n, dtype=np.float32)
+    p /= p.sum()
+    cases += [(p, r, 0.0) for r in (0.0, 1e-7, 0.013, 0.25, 0.5, 0.93, 0.99999, 2.0)]
+    # dyadic probabilities: multiples of 2^-26, sums in [0.25, 1): every addition of an odd multiple of a half ulp ties
+    q = rng.integers(0, 64, size=n).astype(np.float32) * np.float32(2.0 ** -26)
+    cases += [(q, r, c0) for r in (0.3, 0.6, 0.99, 5.0) for c0 in (0.0, 0.25, 0.5000001)]
+    # wide dynamic range with zeros and a few large jumps (binade changes in one step)
+    w = (10.0 ** rng.uniform(-12, -4, size=n)).astype(np.float32)
+    w[rng.integers(0, n, size=n // 7)] = 0.0
+    w[rng.integers(0, n, size=5)] = 0.07
+    cases += [(w, r, 0.0) for r in (1e-9, 0.01, 0.2, 0.36, 10.0)]
+    # softmax-like: the shape the sampler sees
+    z = rng.standard_normal(262144).astype(np.float32) * 1.7
+    s = np.exp(z - z.max()).astype(np.float32)
+    s = (s * np.float32(1.0 / s.sum(dtype=np.float32))).astype(np.float32)
+    cases += [(s, r, 0.0) for r in rng.random(12, dtype=np.float32)]
+    for p, r, c0 in cases:
+        want_i, want_c = _seq_cross(p, r, c0)
+        got_i, got_c = capi.inverse_cdf(p, float(np.float32(r)), float(np.float32(c0)))
+        assert got_i == want_i, (r, c0, got_i, want_i)
+        assert np.float32(got_c) == np.float32(want_c), (r, c0, got_c, want_c)
+
+
 def test_device_loop_equals_stepwise(capi, model_270m, golden):
     g = golden["ref_e2e_270m"]
     model_270m.build_tables(1024)

@@ -61,6 +61,7 @@ SIGNATURES = {
     "tg_qgemm": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int]),
     "tg_argmax_logits": (C.c_int, [_P, C.c_int, C.POINTER(C.c_int)]),
     "tg_minp_logits": (C.c_int, [_P, C.c_int, C.c_float, C.c_float, C.c_float, C.POINTER(C.c_int)]),
+    "tg_inverse_cdf": (C.c_int, [_P, C.c_int, C.c_float, C.c_float, C.POINTER(C.c_int), C.POINTER(C.c_float)]),
     "tg_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int]),
     "tg_dev_qmatvec": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "tg_dev_qmatvec_static": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
@@ -160,6 +161,15 @@ def minp_logits(logits, minp: float, temp: float, randf: float):
     t = C.c_int(0)
     _ck(load().tg_minp_logits(_ptr(p), p.size, minp, temp, randf, C.byref(t)))
     return t.value, p
+
+
+def inverse_cdf(p, randf: float, cum0: float = 0.0):
+    """First index whose sequential fp32 running sum reaches randf (-1 if none), and the sum there."""
+    p = _f32(p)
+    i = C.c_int(0)
+    c = C.c_float(0.0)
+    _ck(load().tg_inverse_cdf(_ptr(p), p.size, cum0, randf, C.byref(i), C.byref(c)))
+    return i.value, c.value
 
 
 def rmsnorm(x, w) -> np.ndarray:

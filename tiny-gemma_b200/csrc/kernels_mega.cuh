@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include "kernels_decode.cuh"
+#include "kernels_sampler.cuh"
 #include "tg_common.cuh"
 
 namespace tg {
@@ -92,6 +93,8 @@ struct MgArgs {
 	int ll_stride, ll_pA, ll_att, ll_pC, ll_act;
 	float *part_E;  // [2][E.nsplit][D] partial sums of the down projection (E -> A, behind the grid barrier)
 	float *logits;                    // [V]
+	float *probs;                     // [V] exp(z - max) of the min-p sampler (before normalisation)
+	int samp_ch;                      // probabilities staged per round of the inverse CDF (multiple of 4, fits the weight ring)
 	float *samp_f;                    // [3][grid] sampler partials
 	int *samp_i;                      // [grid]
 	float *xnorm_out;                 // [D] final-normed hidden state (parity read-back)
@@ -711,6 +714,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 	__shared__ int s_abort;
 	__shared__ float s_f[8];
 	__shared__ int s_i[4];
+	__shared__ int s_cdf[2 * MG_NWARPS + 8];
 	__shared__ float wm[3][AT_NH], wl[3][AT_NH];
 	__shared__ MgLayer s_ly[MG_MAX_LAYERS];
 
@@ -1309,6 +1313,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					for (int j = tid; j < my_tiles * MG_LM_TN; j += MG_THREADS) {
 						const int v = (cta + (j / MG_LM_TN) * G) * MG_LM_TN + (j % MG_LM_TN);
 						const float pv = expf(__ldcg(a.logits + v) / a.temp - gmax);
+						__stcg(a.probs + v, pv);
 						ds += (pv < cut) ? 0.0f : pv;
 					}
 				}
@@ -1329,78 +1334,36 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					if (rc < a.randf_cap) randf = __ldg(a.randf + rc);
 					__syncthreads();
 					const float inv = s_f[6];
-					// inverse-CDF: a sequential fp32 running sum in index order. fp32 addition
-					// is not associative and the crossing index depends on the rounding, so
-					// lane 0 of warp 0 replays the sum in order, 16 terms per step with the
-					// next 16 already in registers, while the other warps compute the next
-					// chunk of probabilities into the second buffer.
-					float *cbuf = reinterpret_cast<float *>(R_D);  // ring is idle now; 2 x CH floats
-					const int CH = 4096;
+					// inverse CDF: the first index whose sequential fp32 running sum reaches randf,
+					// evaluated exactly and in parallel (cdf_cross_block) over chunks of probabilities
+					// p = exp(z - max) * inv staged in the idle weight ring
+					float *cbuf = reinterpret_cast<float *>(R_D);
+					const int CH = a.samp_ch;
 					if (tid == 0) {
 						s_i[1] = -1;
 						s_f[5] = 0.0f;
 					}
-#pragma unroll 1
-					for (int i = tid; i < CH; i += MG_THREADS) cbuf[i] = expf(__ldcg(a.logits + i) / a.temp - gmax) * inv;
 					__syncthreads();
 #pragma unroll 1
 					for (int c0 = 0; c0 < a.V; c0 += CH) {
-						const float *cur = cbuf + ((c0 / CH) & 1) * CH;
-						float *nxt = cbuf + (((c0 / CH) & 1) ^ 1) * CH;
-						if (warp > 0) {
-							if (c0 + CH < a.V)
-#pragma unroll 1
-								for (int i = tid - 32; i < CH; i += MG_THREADS - 32)
-									nxt[i] = expf(__ldcg(a.logits + c0 + CH + i) / a.temp - gmax) * inv;
-						} else if (lane == 0) {
-							float cum = s_f[5];
-							int f = -1;
-							float4 n0 = *reinterpret_cast<const float4 *>(cur), n1 = *reinterpret_cast<const float4 *>(cur + 4);
-							float4 n2 = *reinterpret_cast<const float4 *>(cur + 8), n3 = *reinterpret_cast<const float4 *>(cur + 12);
-#pragma unroll 1
-							for (int i = 0; i < CH; i += 16) {
-								const float4 u0 = n0, u1 = n1, u2 = n2, u3 = n3;
-								if (i + 16 < CH) {
-									n0 = *reinterpret_cast<const float4 *>(cur + i + 16);
-									n1 = *reinterpret_cast<const float4 *>(cur + i + 20);
-									n2 = *reinterpret_cast<const float4 *>(cur + i + 24);
-									n3 = *reinterpret_cast<const float4 *>(cur + i + 28);
-								}
-								float cs[16];
-								cs[0] = cum + u0.x;
-								cs[1] = cs[0] + u0.y;
-								cs[2] = cs[1] + u0.z;
-								cs[3] = cs[2] + u0.w;
-								cs[4] = cs[3] + u1.x;
-								cs[5] = cs[4] + u1.y;
-								cs[6] = cs[5] + u1.z;
-								cs[7] = cs[6] + u1.w;
-								cs[8] = cs[7] + u2.x;
-								cs[9] = cs[8] + u2.y;
-								cs[10] = cs[9] + u2.z;
-								cs[11] = cs[10] + u2.w;
-								cs[12] = cs[11] + u3.x;
-								cs[13] = cs[12] + u3.y;
-								cs[14] = cs[13] + u3.z;
-								cs[15] = cs[14] + u3.w;
-								// p >= 0, so the running sum never decreases: the crossing is in this
-								// group iff its last partial sum has reached randf
-								if (cs[15] >= randf) {
-									int k = 0;
-#pragma unroll
-									for (int t = 15; t >= 0; t--)
-										if (cs[t] >= randf) k = t;
-									f = c0 + i + k;
-									break;
-								}
-								cum = cs[15];
-							}
-							s_f[5] = cum;
-							s_i[1] = f;
+						const int n = min(CH, a.V - c0);
+#pragma unroll 4
+						for (int i = tid * 4; i < n; i += MG_THREADS * 4) {
+							float4 v = __ldcg(reinterpret_cast<const float4 *>(a.probs + c0 + i));
+							v.x *= inv;
+							v.y *= inv;
+							v.z *= inv;
+							v.w *= inv;
+							*reinterpret_cast<float4 *>(cbuf + i) = v;
 						}
 						__syncthreads();
-						if (s_i[1] >= 0) break;
+						const int r = cdf_cross_block<MG_NWARPS>(cbuf, n, &s_f[5], randf, s_cdf);
+						if (r >= 0) {
+							if (tid == 0) s_i[1] = c0 + r;
+							break;
+						}
 					}
+					__syncthreads();
 					if (tid == 0) {
 						__stcg(a.samp_i + G, s_i[1] < 0 ? 0 : s_i[1]);
 						*a.randf_count = rc + 1;

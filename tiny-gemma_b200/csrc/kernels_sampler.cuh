@@ -108,6 +108,176 @@ __global__ void __launch_bounds__(SM_THREADS) top1_rows_kernel(const float *logi
 	}
 }
 
+
+// ------------------------------------------------------------------ exact parallel inverse CDF
+// Step (6) of min-p sampling is "the first index whose running fp32 sum reaches randf", where the
+// running sum is the sequential chain cum = fl(cum + p[i]). fp32 addition is not associative, so a
+// tree sum would move the crossing index. The chain can still be evaluated in parallel, exactly:
+// while cum stays in one binade [2^e, 2^(e+1)) it is an integer multiple S of u = 2^(e-23), and
+// adding p rounds S + p/u to the nearest integer, ties to even. So element i acts on S as
+//     S -> S + a0[i]  (S even),   S -> S + a1[i]  (S odd),
+// with a0 = a1 = round(p/u) except on an exact tie, where the pair encodes round-half-even. Such
+// maps compose into maps of the same form (the parity of the result follows from the parity of the
+// input), so a prefix scan of (a0, a1) pairs gives every partial sum of the chain, bit for bit.
+// When a sum would leave the binade, that one addition is done in fp32 and the scan restarts behind
+// it with the new u. Sums saturate far above every threshold, so they stay monotone.
+struct CdfFn {
+	int a0, a1;
+};
+constexpr int CDF_SAT = 1 << 27;
+constexpr int CDF_BIG = 1 << 25;
+__device__ __forceinline__ CdfFn cdf_compose(CdfFn f, CdfFn g) {  // first f, then g
+	CdfFn h;
+	h.a0 = min(CDF_SAT, f.a0 + ((f.a0 & 1) ? g.a1 : g.a0));
+	h.a1 = min(CDF_SAT, f.a1 + ((f.a1 & 1) ? g.a0 : g.a1));
+	return h;
+}
+__device__ __forceinline__ int cdf_apply(CdfFn f, int S) { return min(CDF_SAT, S + ((S & 1) ? f.a1 : f.a0)); }
+__device__ __forceinline__ CdfFn cdf_element(float p, float inv_u) {
+	const float x = p * inv_u;
+	CdfFn f;
+	if (!(x < 33554432.0f)) {  // also NaN / inf: forces the fp32 path for this element
+		f.a0 = f.a1 = CDF_BIG;
+		return f;
+	}
+	const float fl = floorf(x);
+	const float fr = x - fl;  // exact
+	const int q = int(fl);
+	if (fr == 0.5f) {
+		f.a0 = q + (q & 1);
+		f.a1 = q + 1 - (q & 1);
+	} else {
+		f.a0 = f.a1 = q + (fr > 0.5f ? 1 : 0);
+	}
+	return f;
+}
+
+constexpr int CDF_PER_LANE = 8;
+constexpr int CDF_PER_WARP = 32 * CDF_PER_LANE;
+
+// Block-cooperative (NW warps, all threads call it with the same arguments). p[0..n) lies in shared
+// memory; *cum_io (shared) holds the running sum before p[0] and receives the sum after the last
+// element consumed. Returns the first index i with fl(cum + p[0] + ... + p[i]) >= randf, or -1.
+// scratch: 2 * NW + 8 ints of shared memory.
+template <int NW>
+__device__ int cdf_cross_block(const float *p, int n, float *cum_io, float randf, int *scratch) {
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	CdfFn *wt = reinterpret_cast<CdfFn *>(scratch);  // per-warp composite
+	int *s_pos = scratch + 2 * NW, *s_res = scratch + 2 * NW + 1;
+	if (tid == 0) {
+		*s_pos = 0;
+		*s_res = -1;
+	}
+	__syncthreads();
+	for (int guard = 0; guard < n + 64; guard++) {  // every round consumes at least one element
+		const int pos = *s_pos;
+		if (*s_res >= 0 || pos >= n) break;
+		const float cum = *cum_io;
+		const unsigned bits = __float_as_uint(cum);
+		const int e = int((bits >> 23) & 0xffu) - 127;
+		if (!(cum >= 7.888609e-31f) || e > 120) {
+			// zero, tiny, inf or NaN: plain fp32 steps until the sum is an ordinary number
+			__syncthreads();
+			if (tid == 0) {
+				float c = cum;
+				int i = pos, r = -1;
+				for (; i < n && r < 0; i++) {
+					c += p[i];
+					if (c >= randf) r = i;
+					if (c >= 7.888609e-31f && c < 1e36f) {
+						i++;
+						break;
+					}
+				}
+				*cum_io = c;
+				*s_pos = i;
+				*s_res = r;
+			}
+			__syncthreads();
+			continue;
+		}
+		const float u = __uint_as_float(unsigned(e - 23 + 127) << 23);
+		const float inv_u = __uint_as_float(unsigned(23 - e + 127) << 23);
+		const int S0 = int(cum * inv_u);
+		const float y = randf * inv_u;
+		const int T = (y < 33554432.0f) ? int(ceilf(y)) : CDF_BIG;
+		const int Tmin = min(T, 1 << 24);
+		// this lane's elements
+		const int base = pos + warp * CDF_PER_WARP + lane * CDF_PER_LANE;
+		CdfFn el[CDF_PER_LANE];
+		CdfFn mine{0, 0};
+#pragma unroll
+		for (int k = 0; k < CDF_PER_LANE; k++) {
+			el[k] = CdfFn{0, 0};
+			if (base + k < n) el[k] = cdf_element(p[base + k], inv_u);
+			mine = cdf_compose(mine, el[k]);
+		}
+		// inclusive scan over the lanes
+		CdfFn inc = mine;
+#pragma unroll
+		for (int o = 1; o < 32; o <<= 1) {
+			CdfFn prev;
+			prev.a0 = __shfl_up_sync(0xffffffffu, inc.a0, o);
+			prev.a1 = __shfl_up_sync(0xffffffffu, inc.a1, o);
+			if (lane >= o) inc = cdf_compose(prev, inc);
+		}
+		if (lane == 31) wt[warp] = inc;
+		CdfFn exc;
+		exc.a0 = __shfl_up_sync(0xffffffffu, inc.a0, 1);
+		exc.a1 = __shfl_up_sync(0xffffffffu, inc.a1, 1);
+		if (lane == 0) exc = CdfFn{0, 0};
+		__syncthreads();
+		// state at the start of every warp; first warp in which the sum reaches the threshold
+		int Sw = S0, hit = -1, Shit = 0;
+#pragma unroll 1
+		for (int w = 0; w < NW; w++) {
+			const int nx = cdf_apply(wt[w], Sw);
+			if (hit < 0 && nx >= Tmin) {
+				hit = w;
+				Shit = Sw;
+			}
+			Sw = nx;
+		}
+		__syncthreads();  // wt is rewritten next round
+		if (hit < 0) {
+			if (tid == 0) {
+				*cum_io = float(Sw) * u;  // exact: Sw < 2^24
+				*s_pos = pos + NW * CDF_PER_WARP;
+			}
+		} else if (warp == hit) {
+			int S = cdf_apply(exc, Shit);
+			int jfirst = -1, Sbefore = 0, Safter = 0;
+#pragma unroll
+			for (int k = 0; k < CDF_PER_LANE; k++) {
+				const int nx = cdf_apply(el[k], S);
+				if (jfirst < 0 && nx >= Tmin) {
+					jfirst = base + k;
+					Sbefore = S;
+					Safter = nx;
+				}
+				S = nx;
+			}
+			const unsigned m = __ballot_sync(0xffffffffu, jfirst >= 0);
+			const int src = __ffs(m) - 1;  // m != 0: this warp's total reaches the threshold
+			if (lane == src) {
+				if (Safter < (1 << 24)) {
+					*s_res = jfirst;  // the sum reached randf inside the binade
+					*cum_io = float(Safter) * u;
+					*s_pos = jfirst + 1;
+				} else {
+					const float c = float(Sbefore) * u + p[jfirst];  // the one addition that leaves the binade
+					*cum_io = c;
+					*s_pos = jfirst + 1;
+					if (c >= randf) *s_res = jfirst;
+				}
+			}
+		}
+		__syncthreads();
+	}
+	__syncthreads();
+	return *s_res;
+}
+
 // ops::minp_logits, reference ops.hpp:762-859.
 //  (1) x /= temp  (2) rowmax  (3) p = exp(x - rowmax), maxp  (4) cut = minp*maxp,
 //  denom = sum of p >= cut  (5) every p *= 1/denom — tokens under the cut keep
@@ -115,14 +285,14 @@ __global__ void __launch_bounds__(SM_THREADS) top1_rows_kernel(const float *logi
 //  fp32 sum reaches randf, else 0.
 // Steps 1-5 are data-parallel. Step 6 must reproduce a *sequential* fp32 sum
 // (fp32 addition is not associative, and the crossing index depends on the
-// rounding), so one thread replays the sum in index order over chunks that
-// the whole CTA stages into shared memory, stopping at the crossing.
+// rounding): cdf_cross_block evaluates that chain exactly, in parallel, over
+// chunks that the whole CTA stages into shared memory.
 constexpr int MP_CHUNK = 8192;
 
 __global__ void __launch_bounds__(SM_THREADS) minp_kernel(SampleArgs a) {
 	__shared__ float red[SM_NWARPS];
 	__shared__ float chunk[MP_CHUNK];
-	__shared__ int s_found;
+	__shared__ int scratch[2 * SM_NWARPS + 8];
 	__shared__ float s_cum;
 	const int b = blockIdx.x, tid = threadIdx.x;
 	float *x = a.logits + size_t(b) * a.V;
@@ -175,36 +345,55 @@ __global__ void __launch_bounds__(SM_THREADS) minp_kernel(SampleArgs a) {
 	float denom = 0.0f;
 	for (int w = 0; w < SM_NWARPS; w++) denom += red[w];
 	const float inv = 1.0f / denom;
-	// (5)+(6)
-	if (tid == 0) { s_found = -1; s_cum = 0.0f; }
+	// (5)+(6): every chunk is scaled (the reference scales the whole row); the running sum is
+	// evaluated chunk by chunk until the crossing is known
+	if (tid == 0) s_cum = 0.0f;
 	__syncthreads();
 	int found = -1;
 	for (int c0 = 0; c0 < a.V; c0 += MP_CHUNK) {
-		for (int i = tid * 4; i < MP_CHUNK; i += SM_THREADS * 4) {
+		const int n = min(MP_CHUNK, a.V - c0);
+		for (int i = tid * 4; i < n; i += SM_THREADS * 4) {
 			float4 v = __ldcg(reinterpret_cast<const float4 *>(x + c0 + i));
 			v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
 			__stcg(reinterpret_cast<float4 *>(x + c0 + i), v);
 			*reinterpret_cast<float4 *>(&chunk[i]) = v;
 		}
 		__syncthreads();
-		if (tid == 0 && s_found < 0) {
-			float cum = s_cum;
-			int f = -1;
-			for (int i = 0; i < MP_CHUNK; i++) {
-				cum += chunk[i];
-				if (cum >= randf) { f = c0 + i; break; }
-			}
-			s_cum = cum;
-			s_found = f;
+		if (found < 0) {
+			const int r = cdf_cross_block<SM_NWARPS>(chunk, n, &s_cum, randf, scratch);
+			if (r >= 0) found = c0 + r;
 		}
 		__syncthreads();
-		found = s_found;
-		// keep scaling the remaining chunks (the reference scales the whole row)
-		// but stop replaying once the crossing is known
 	}
 	if (tid == 0) {
 		emit_token(a, b, found < 0 ? 0 : found);
 		a.randf_count[b] += 1;
+	}
+}
+
+// The inverse-CDF step in isolation over an explicit vector p[0..n) in global memory, starting
+// from the running sum cum0: *idx = first i with fl(cum0 + p[0] + ... + p[i]) >= randf, else -1.
+// One CTA; *cum_out receives the sum after the last element consumed.
+__global__ void __launch_bounds__(SM_THREADS) inverse_cdf_kernel(const float *p, int n, float cum0, float randf, int *idx,
+                                                                 float *cum_out) {
+	__shared__ float chunk[MP_CHUNK];
+	__shared__ int scratch[2 * SM_NWARPS + 8];
+	__shared__ float s_cum;
+	const int tid = threadIdx.x;
+	if (tid == 0) s_cum = cum0;
+	__syncthreads();
+	int found = -1;
+	for (int c0 = 0; c0 < n && found < 0; c0 += MP_CHUNK) {
+		const int m = min(MP_CHUNK, n - c0);
+		for (int i = tid; i < m; i += SM_THREADS) chunk[i] = p[c0 + i];
+		__syncthreads();
+		const int r = cdf_cross_block<SM_NWARPS>(chunk, m, &s_cum, randf, scratch);
+		if (r >= 0) found = c0 + r;
+		__syncthreads();
+	}
+	if (tid == 0) {
+		*idx = found;
+		*cum_out = s_cum;
 	}
 }
 

@@ -316,7 +316,7 @@ struct tg_state {
 	MgArgs mega{};
 	CUtensorMap *d_tmaps = nullptr;
 	MgLayer *d_layers = nullptr;
-	float *mg_ll = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr;
+	float *mg_ll = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr, *mg_probs = nullptr;
 	size_t mg_ll_bytes = 0;
 	int *mg_samp_i = nullptr;
 	unsigned *mg_bar = nullptr;
@@ -816,6 +816,13 @@ int mega_setup(tg_state *s) {
 	a.ll = s->mg_ll;
 	a.part_E = s->mg_part_E;
 	a.logits = s->logits;
+	TG_TRY(allocz((void **)&s->mg_probs, size_t(V) * 4));
+	a.probs = s->mg_probs;
+	{
+		const int region_floats = (a.off_h - a.off_D) / 4;
+		a.samp_ch = std::max(3072, std::min(region_floats, 24576) / 3072 * 3072);
+		if (a.samp_ch > region_floats) return fail(TG_ESHAPE, "sampler staging does not fit the weight ring");
+	}
 	a.samp_f = s->mg_samp_f;
 	a.samp_i = s->mg_samp_i;
 	a.xnorm_out = s->xnorm;
@@ -1526,6 +1533,7 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->d_tmaps);
 	cudaFree(s->d_layers);
 	cudaFree(s->mg_ll);
+	cudaFree(s->mg_probs);
 	cudaFree(s->mg_part_E);
 	cudaFree(s->mg_samp_f);
 	cudaFree(s->mg_samp_i);
@@ -2096,6 +2104,22 @@ int tg_minp_logits(float *logits, int n, float minp, float temp, float randf, in
 	TG_TRY(check_launch("minp"));
 	TG_CUDA(cudaMemcpy(tok, dt.p, 4, cudaMemcpyDeviceToHost));
 	TG_CUDA(cudaMemcpy(logits, dl.p, size_t(n) * 4, cudaMemcpyDeviceToHost));
+	return TG_OK;
+}
+
+int tg_inverse_cdf(const float *p, int n, float cum0, float randf, int *idx, float *cum_out) {
+	if (!p || !idx || n < 1) return fail(TG_EINVAL, "bad argument");
+	TG_TRY(ensure_device(0));
+	DevBuf dp, di, dc;
+	TG_TRY(dp.alloc(size_t(n) * 4));
+	TG_TRY(di.alloc(4));
+	TG_TRY(dc.alloc(4));
+	TG_CUDA(cudaMemcpy(dp.p, p, size_t(n) * 4, cudaMemcpyHostToDevice));
+	inverse_cdf_kernel<<<1, SM_THREADS>>>((const float *)dp.p, n, cum0, randf, (int *)di.p, (float *)dc.p);
+	count_launch();
+	TG_TRY(check_launch("inverse_cdf"));
+	TG_CUDA(cudaMemcpy(idx, di.p, 4, cudaMemcpyDeviceToHost));
+	if (cum_out) TG_CUDA(cudaMemcpy(cum_out, dc.p, 4, cudaMemcpyDeviceToHost));
 	return TG_OK;
 }
 
