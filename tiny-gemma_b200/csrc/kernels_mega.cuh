@@ -5,13 +5,15 @@
 // HBM time — split over five dependent phases. Separate kernels cost more in
 // launch gaps and cold starts than the data movement itself. Here
 //   * every CTA owns a fixed slice of each weight matrix (a column strip, or a
-//     column strip x K-split) and fetches it with TMA (cp.async.bulk.tensor.2d)
-//     into a shared-memory region reserved for that phase. A region is refilled
-//     for the NEXT layer as soon as the current layer has consumed it, so about
-//     one layer of weights per SM (186 KB) is always in flight and HBM never
-//     waits for the dependency chain;
-//   * phases hand over through small L2-resident vectors and a grid barrier
-//     (one atomic counter, bounded spin);
+//     column strip x K-split), stored contiguously in a re-tiled copy of the
+//     layer weights, and fetches it with bulk copies (cp.async.bulk) into a
+//     shared-memory region reserved for that phase. A region is refilled for
+//     the NEXT layer after the current layer has consumed it, so about one
+//     layer of weights per SM (186 KB) is always in flight and HBM never waits
+//     for the dependency chain;
+//   * phases hand over through small L2-resident vectors that validate
+//     themselves (a sentinel marks words not yet written), one grid barrier
+//     per layer (one atomic counter, bounded spin);
 //   * RMSNorms are recomputed redundantly by every CTA from those vectors, and
 //     the residual stream lives in each CTA's shared memory;
 //   * split-K partial sums are written once and summed in split order by their
@@ -24,8 +26,8 @@
 //   D  post-norm + residual + pre-norm + up & gate matvec + LUT-GeGLU -> act
 //   E  down matvec                        -> partial sums
 // then the lm_head (final residual + norm in its prologue, logits streamed
-// through a 6-stage TMA ring) and the sampler (argmax, or min-p with the
-// sequential fp32 inverse-CDF replay of reference ops.hpp:848-858).
+// through a TMA ring) and the sampler (argmax, or min-p with the sequential
+// fp32 inverse CDF of reference ops.hpp:848-858 evaluated by an exact scan).
 //
 // Every wait is bounded: a spin that runs out sets *err and a shared abort
 // flag, after which all waits fall through and the kernel returns.
