@@ -93,7 +93,12 @@ struct MgArgs {
 	//   ll_act [I]             GeGLU activations                    (D -> E)
 	float *ll;
 	int ll_stride, ll_pA, ll_att, ll_pC, ll_act;
-	float *part_E;  // [2][E.nsplit][D] partial sums of the down projection (E -> A, behind the grid barrier)
+	// Down projection -> next layer: {value, tag} words (8-byte stores are single-copy atomic), two
+	// buffers alternating by layer, each [E.nsplit][D] words followed by one presence word for every
+	// CTA that holds no down-projection unit. A word is valid when its tag is the layer's tag.
+	uint2 *pe;
+	int pe_stride;   // words per buffer
+	unsigned seq0;   // layer tags of this launch start above seq0
 	float *logits;                    // [V]
 	float *probs;                     // [V] exp(z - max) of the min-p sampler (before normalisation)
 	int samp_ch;                      // probabilities staged per round of the inverse CDF (multiple of 4, fits the weight ring)
@@ -174,6 +179,19 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
 // values; the consumer loads the data itself and repeats a load until none of its words is the
 // sentinel. 4-byte accesses are single-copy atomic, so a word is either old (sentinel) or new.
 // One L2 round trip hands the data over; no flag, no fence, no counter.
+__device__ __forceinline__ void st_tagged(uint2 *p, float v, unsigned tag) {
+	asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_tagged2(const uint2 *p) {  // two consecutive {value, tag} words
+	uint4 r;
+	asm volatile("ld.relaxed.gpu.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+	return r;
+}
+__device__ __forceinline__ uint2 ld_tagged_acquire(const uint2 *p) {
+	uint2 r;
+	asm volatile("ld.acquire.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+	return r;
+}
 constexpr unsigned MG_LL_EMPTY = 0xFFFFFFFFu;
 __device__ __forceinline__ void ll_store(float *p, float v) {
 	asm volatile("st.relaxed.gpu.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
@@ -536,15 +554,51 @@ __device__ __forceinline__ void mg_load_vec3(MgVec3 &v, const float *scale, cons
 // complete (self-validating hand-off), otherwise they are plain loads behind a
 // grid barrier. Splits are added in ascending order.
 __device__ __noinline__ void mg_resnorm(const MgArgs &a, MgCtx &c, float *h, float *xs, float *bred, bool has_t,
-                                        const float *part, int nsplit, bool ll, const MgVec3 v, float *x_out) {
+                                        const float *part, int nsplit, bool ll, const MgVec3 v, float *x_out,
+                                        unsigned tag = 0, int n_pres = 0) {
 	const int D = a.D, tid = threadIdx.x;
 	const bool in = 4 * tid < D;
 	float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
 	if (in) hv = *reinterpret_cast<const float4 *>(h + 4 * tid);  // own elements: written by this thread
 	if (has_t) {
 		float4 tv = make_float4(0.f, 0.f, 0.f, 0.f);
+		if (!ll) {
+			// tagged words {value, tag}: `part` is the layer's buffer of uint2, [nsplit][D] followed by
+			// n_pres presence words (CTAs without a unit of the producing phase); threads past D/4 poll those
+			const uint2 *pe = reinterpret_cast<const uint2 *>(part);
 #pragma unroll 1
-		for (int s0 = 0; s0 < nsplit; s0 += 8) {
+			for (int s0 = 0; s0 < nsplit; s0 += 4) {
+				uint4 w[4][2];
+				int spins = 0;
+				bool ok;
+				do {
+					ok = true;
+#pragma unroll
+					for (int q = 0; q < 4; q++) {
+						w[q][0] = w[q][1] = make_uint4(0u, tag, 0u, tag);
+						if (in && s0 + q < nsplit) {
+							const uint2 *src = pe + size_t(s0 + q) * D + 4 * tid;
+							w[q][0] = ld_tagged2(src);
+							w[q][1] = ld_tagged2(src + 2);
+						}
+					}
+					if (s0 == 0 && !in && tid - D / 4 < n_pres)
+						ok = ld_tagged_acquire(pe + size_t(nsplit) * D + (tid - D / 4)).y == tag;
+#pragma unroll
+					for (int q = 0; q < 4; q++)
+						ok = ok && w[q][0].y == tag && w[q][0].w == tag && w[q][1].y == tag && w[q][1].w == tag;
+				} while (!ok && ll_retry(c, spins));
+#pragma unroll
+				for (int q = 0; q < 4; q++) {
+					tv.x += __uint_as_float(w[q][0].x);
+					tv.y += __uint_as_float(w[q][0].z);
+					tv.z += __uint_as_float(w[q][1].x);
+					tv.w += __uint_as_float(w[q][1].z);
+				}
+			}
+		}
+#pragma unroll 1
+		for (int s0 = 0; ll && s0 < nsplit; s0 += 8) {
 			float4 pv[8];
 			int spins = 0;
 			bool ok;
@@ -555,12 +609,12 @@ __device__ __noinline__ void mg_resnorm(const MgArgs &a, MgCtx &c, float *h, flo
 					pv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
 					if (in && s0 + q < nsplit) {
 						const float *src = part + size_t(s0 + q) * D + 4 * tid;
-						pv[q] = ll ? ll_load4_once(src) : __ldcg(reinterpret_cast<const float4 *>(src));
+						pv[q] = ll_load4_once(src);
 					}
 				}
 #pragma unroll
 				for (int q = 0; q < 8; q++) ok = ok && ll_valid(pv[q]);
-			} while (ll && !ok && ll_retry(c, spins));
+			} while (!ok && ll_retry(c, spins));
 #pragma unroll
 			for (int q = 0; q < 8; q++) {
 				tv.x += pv[q].x;
@@ -812,15 +866,18 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 #define attn_part (llb + a.ll_att)
 #define part_C (llb + a.ll_pC)
 #define act (llb + a.ll_act)
-#define part_E_cur (a.part_E + size_t(lc & 1) * a.E.nsplit * D)
-#define part_E_prev (a.part_E + size_t((lc & 1) ^ 1) * a.E.nsplit * D)
+			// down projection -> next layer hand-off: tagged words, buffer and tag follow the launch-spanning layer count
+			const unsigned gl = a.seq0 + unsigned(lc);
+#define pe_cur (a.pe + size_t(gl & 1u) * a.pe_stride)
+#define pe_prev (a.pe + size_t((gl & 1u) ^ 1u) * a.pe_stride)
+			const int n_pres = G - a.E.units;
 			// ============================================================ A: QKV
 			float4 qsc = make_float4(0.f, 0.f, 0.f, 0.f);  // scales of this thread's 4 q|k|v columns (attention CTAs)
 			{
 				const bool active = cta < a.A.units;
 				const int tile = active ? cta % a.A.ntiles : 0, split = active ? cta / a.A.ntiles : 0;
 				const int k0 = split * a.A.kc;
-				mg_resnorm(a, ctx, h, xs, bred, l > 0, part_E_prev, a.E.nsplit, false, vA, nullptr);
+				mg_resnorm(a, ctx, h, xs, bred, l > 0, reinterpret_cast<const float *>(pe_prev), a.E.nsplit, false, vA, nullptr, gl, n_pres);
 				if (warp == 1 && l > 0 && (a.sched & 2)) mg_issue_E(a, s_ly, l, cta, R_E, &bar_E, pol);
 				MG_STAMP();
 				if (active) mg_wait_tma(ctx, &bar_A, pA);
@@ -839,13 +896,21 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 					else if (more)
 						mg_issue_A(a, s_ly, 0, cta, R_A, &bar_A, pol);
 				}
-				{  // wipe this CTA's share of the other copy of the hand-off arena
+				// Wipe the other copy of the hand-off arena (last used by the previous layer, next used by
+				// the next one). Every CTA has finished reading it: this CTA got past the prologue above,
+				// which needs the down-projection words (or presence word) of ALL CTAs, and those are
+				// stored after the storing CTA's last read of the previous layer's buffers. The CTAs that
+				// idle through the attention phase do the wiping; the fence orders it before their own
+				// next down-projection / presence store, which is what lets anyone write that copy again.
+				if (cta >= nsA) {
 					float4 *other = reinterpret_cast<float4 *>(a.ll + size_t((lc & 1) ^ 1) * a.ll_stride);
-					const int n4 = a.ll_stride / 4, per = (n4 + G - 1) / G;
+					const int nw = G - nsA, n4 = a.ll_stride / 4, per = (n4 + nw - 1) / nw;
 					const float e = __uint_as_float(MG_LL_EMPTY);
 #pragma unroll 1
-					for (int i = cta * per + tid; i < min(n4, (cta + 1) * per); i += MG_THREADS)
+					for (int i = (cta - nsA) * per + tid; i < min(n4, (cta - nsA + 1) * per); i += MG_THREADS)
 						__stcg(other + i, make_float4(e, e, e, e));
+					__syncthreads();
+					if (tid == 0) __threadfence();
 				}
 				// cold data of phase B
 				if (cta < nsA) {
@@ -1096,34 +1161,36 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				MG_STAMP();
 				if (active) {
 					const float s = mg_tile_colsum(R_E, a.E.kc, a.E.segs, xs, red);
-					if (tid < a.E.TN) __stcg(part_E_cur + size_t(split) * D + tile * a.E.TN + tid, s);
+					if (tid < a.E.TN) st_tagged(pe_cur + size_t(split) * D + tile * a.E.TN + tid, s, gl + 1u);
 				}
 				pE ^= 1;
 				MG_STAMP();
-				MgBar gb;
-				mg_arrive(ctx, gb);
+				// a CTA without a unit still reports that it is done reading this layer's hand-off buffers
+				if (!active && tid == 0) st_tagged(pe_cur + size_t(a.E.nsplit) * D + (cta - a.E.units), 0.0f, gl + 1u);
 				if (warp == 1 && l + 1 < L && !(a.sched & 2)) mg_issue_E(a, s_ly, l + 1, cta, R_E, &bar_E, pol);
 				if (l + 1 < L)
 					mg_load_vec3(vA, ly.sd, ly.mlp_post, s_ly[l + 1].attn_pre, D);
 				else
 					mg_load_vec3(vA, ly.sd, ly.mlp_post, a.final_norm, D);
-				mg_wait(ctx, gb);
 				MG_STAMP();
 			}
 #undef part_A
 #undef attn_part
 #undef part_C
 #undef act
-#undef part_E_cur
-#undef part_E_prev
+#undef pe_cur
+#undef pe_prev
 		}
 
 		// ================================================================ lm_head
 		// logits[v] = lm_scale[v] * sum_k x[k] W[k,v]; this CTA takes column tiles
 		// cta, cta+G, ...; a tile's K rows stream through a ring of MG_LM_STAGES
 		// stages of LM.box_rows rows laid over the (now idle) D and E regions.
-		mg_resnorm(a, ctx, h, xs, bred, true, a.part_E + size_t((step * L + L - 1) & 1) * a.E.nsplit * D, a.E.nsplit, false, vA,
-		           cta == 0 ? a.xnorm_out : nullptr);
+		{
+			const unsigned gl_last = a.seq0 + unsigned(step * L + L - 1);
+			mg_resnorm(a, ctx, h, xs, bred, true, reinterpret_cast<const float *>(a.pe + size_t(gl_last & 1u) * a.pe_stride),
+			           a.E.nsplit, false, vA, cta == 0 ? a.xnorm_out : nullptr, gl_last + 1u, G - a.E.units);
+		}
 		MG_STAMP();
 		float best = -INFINITY;  // running max of this CTA's (temperature-scaled) logits, threads < 128
 		int best_i = -1;

@@ -316,7 +316,9 @@ struct tg_state {
 	MgArgs mega{};
 	CUtensorMap *d_tmaps = nullptr;
 	MgLayer *d_layers = nullptr;
-	float *mg_ll = nullptr, *mg_part_E = nullptr, *mg_samp_f = nullptr, *mg_probs = nullptr;
+	float *mg_ll = nullptr, *mg_samp_f = nullptr, *mg_probs = nullptr;
+	uint2 *mg_pe = nullptr;
+	unsigned mg_seq = 0;  // layer tags consumed so far by the tagged hand-off
 	size_t mg_ll_bytes = 0;
 	int *mg_samp_i = nullptr;
 	unsigned *mg_bar = nullptr;
@@ -796,7 +798,8 @@ int mega_setup(tg_state *s) {
 	s->mg_ll_bytes = size_t(2) * a.ll_stride * 4;
 	TG_CUDA(cudaMalloc(&s->mg_ll, s->mg_ll_bytes));
 	TG_CUDA(cudaMemset(s->mg_ll, 0xFF, s->mg_ll_bytes));
-	TG_TRY(allocz((void **)&s->mg_part_E, size_t(2) * a.E.nsplit * D * 4));
+	a.pe_stride = a.E.nsplit * D + ((G - a.E.units + 3) & ~3) + 4;
+	TG_TRY(allocz((void **)&s->mg_pe, size_t(2) * a.pe_stride * sizeof(uint2)));
 	TG_TRY(allocz((void **)&s->mg_samp_f, size_t(3) * G * 4));
 	TG_TRY(allocz((void **)&s->mg_samp_i, size_t(G + 8) * 4));
 	TG_TRY(allocz((void **)&s->mg_bar, 64));
@@ -814,7 +817,7 @@ int mega_setup(tg_state *s) {
 	a.wte_s = m->wte_s;
 	a.sqrtD = float(std::sqrt(double(D)));
 	a.ll = s->mg_ll;
-	a.part_E = s->mg_part_E;
+	a.pe = s->mg_pe;
 	a.logits = s->logits;
 	TG_TRY(allocz((void **)&s->mg_probs, size_t(V) * 4));
 	a.probs = s->mg_probs;
@@ -912,6 +915,8 @@ int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, b
 	a.randf_cap = s->randf_cap;
 	a.tok_log = log_tokens ? s->tok_log : nullptr;
 	a.log_cap = s->log_cap;
+	a.seq0 = s->mg_seq;
+	s->mg_seq += unsigned(n_steps) * unsigned(m->cfg.n_layers);
 	// every word of the hand-off arena starts as "empty" (all ones)
 	TG_CUDA(cudaMemsetAsync(s->mg_ll, 0xFF, s->mg_ll_bytes, s->stream));
 	a.dbg = s->mg_dbg;
@@ -1534,7 +1539,7 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->d_layers);
 	cudaFree(s->mg_ll);
 	cudaFree(s->mg_probs);
-	cudaFree(s->mg_part_E);
+	cudaFree(s->mg_pe);
 	cudaFree(s->mg_samp_f);
 	cudaFree(s->mg_samp_i);
 	cudaFree(s->mg_bar);
