@@ -124,7 +124,10 @@ struct MgArgs {
 	int dbg_cta;     // which CTA records
 	int sched;       // when the next layer's large tiles are requested. Bit 0: up/gate after the down projection's poll (else
 	                 // right after the gate product); bit 1: down tiles after phase A's prologue (else after the down
-	                 // product). A burst of bulk copies delays the small hand-off loads issued while it lands.
+	                 // product). A burst of bulk copies delays whatever runs while it lands (hand-off loads by up to
+	                 // ~1 us, tile products by ~0.3 us); other placements that were measured (paced pieces at ten points
+	                 // of the layer, fetching during the attention phase, landing only under the tile products) moved
+	                 // the cost around without lowering it.
 	int dbg_cap;
 };
 
