@@ -136,6 +136,8 @@ struct GemmTcArgs {
 	float *partial;              // [nsplit][M][N] raw sums      (nsplit > 1: summed and scaled by a second kernel)
 	int M, N, K, m_tiles;
 	int nsplit;                  // K-splits = gridDim.z; K / 32 must be a multiple of it
+	unsigned *tickets;           // [gridDim.y * gridDim.x] zeros, or null. Non-null with nsplit > 1: the CTA that finishes
+	                             // a tile last adds the partial sums in split order, scales and writes C itself
 	int *err;
 };
 
@@ -149,10 +151,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 	__shared__ uint32_t tmem_base_s;
 	__shared__ int s_fail;
 	__shared__ int s_issued;  // k-blocks whose loads have been issued
+	__shared__ int s_last, s_cnt;
 
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int n0 = blockIdx.x * TC_BN;
 	const int mt0 = blockIdx.y * TC_MT;
+	const int nmt = min(TC_MT, a.m_tiles - mt0);  // row tiles this CTA really has
 	const int k_blocks_all = a.K / TC_BK;
 	const int k_blocks = k_blocks_all / a.nsplit;   // this CTA's share of K
 	const int kb_first = blockIdx.z * k_blocks;
@@ -167,6 +171,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 		mbar_init(&acc_bar, 1);
 		s_fail = 0;
 		s_issued = 0;
+		s_last = -1;
+		s_cnt = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
 	if (warp == 1) {  // TMEM: 2 accumulators x 128 fp32 columns
@@ -191,10 +197,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 				const int s = kb % TC_STAGES, use = kb / TC_STAGES;
 				if (use > 0 && !tc_wait(&free_bar[s], (use - 1) & 1, a.err)) { s_fail = 1; break; }
 				fence_proxy_async();
-				mbar_expect_tx(&full_bar[s], uint32_t(3 * TC_MT * TC_TILE_BYTES + TC_W_BYTES));
+				mbar_expect_tx(&full_bar[s], uint32_t(3 * nmt * TC_TILE_BYTES + TC_W_BYTES));
 				for (int term = 0; term < 3; term++)
-					for (int mt = 0; mt < TC_MT; mt++) {
-						const int mtg = min(mt0 + mt, a.m_tiles - 1);  // a missing second tile re-reads the first (results unused)
+					for (int mt = 0; mt < nmt; mt++) {
+						const int mtg = mt0 + mt;
 						const uint8_t *src = reinterpret_cast<const uint8_t *>(a.apack) + term * term_stride +
 						                     (size_t(mtg) * k_blocks_all + kb_first + kb) * TC_TILE_BYTES;
 						bulk_load(stage_a(s, term, mt), src, TC_TILE_BYTES, &full_bar[s]);
@@ -214,6 +220,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 				const uint32_t b_addr = smem_u32(stage_b(s));
 #pragma unroll
 				for (int mt = 0; mt < TC_MT; mt++) {
+					if (mt >= nmt) break;
 					const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN);
 #pragma unroll
 					for (int term = 0; term < 3; term++) {
@@ -261,7 +268,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 			tc_fence_after();
 			const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
 #pragma unroll 1
-			for (int mt = 0; mt < TC_MT; mt++) {
+			for (int mt = 0; mt < nmt; mt++) {
 				const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
 #pragma unroll 1
 				for (int c = 0; c < TC_BN / 32; c++) {
@@ -298,6 +305,59 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 								                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
 						}
 					}
+				}
+			}
+			if (a.nsplit > 1 && a.tickets) {
+				// in-kernel split-K reduction: the CTA that arrives last at this tile's ticket sums the
+				// partial tiles of all splits in split order (a fixed order: results are reproducible)
+				// (the four epilogue warps meet through a shared counter and a bounded spin, never a
+				// hardware barrier: a warp whose wait ran out must not be able to strand the others)
+				__threadfence();
+				__syncwarp();
+				unsigned *tk = a.tickets + blockIdx.y * gridDim.x + blockIdx.x;
+				if (lane == 0 && atomicAdd(&s_cnt, 1) == 3) {
+					const unsigned t = atomicAdd(tk, 1u);
+					*(volatile int *)&s_last = (t == unsigned(a.nsplit - 1)) ? 1 : 0;
+				}
+				int last = -1;
+				for (int spins = 0; spins < TC_SPIN_CAP; spins++) {
+					last = *(volatile int *)&s_last;
+					if (last >= 0) break;
+				}
+				if (last < 0 && lane == 0) atomicExch(a.err, 7);
+				if (last == 1) {
+					__threadfence();
+#pragma unroll 1
+					for (int mt = 0; mt < nmt; mt++) {
+						const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
+						if (row >= a.M) continue;
+#pragma unroll 1
+						for (int c4 = 0; c4 < TC_BN / 4; c4++) {
+							float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+							for (int s0 = 0; s0 < a.nsplit; s0 += 4) {
+								float4 v[4];
+#pragma unroll
+								for (int q = 0; q < 4; q++) {
+									v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+									if (s0 + q < a.nsplit)
+										v[q] = __ldcg(reinterpret_cast<const float4 *>(a.partial + (size_t(s0 + q) * a.M + row) * a.N + n0) + c4);
+								}
+#pragma unroll
+								for (int q = 0; q < 4; q++) {
+									sum.x += v[q].x;
+									sum.y += v[q].y;
+									sum.z += v[q].z;
+									sum.w += v[q].w;
+								}
+							}
+							const float4 sc = *reinterpret_cast<const float4 *>(a.scales + n0 + 4 * c4);
+							*reinterpret_cast<float4 *>(a.C + size_t(row) * a.ldc + n0 + 4 * c4) =
+							    make_float4(sum.x * sc.x, sum.y * sc.y, sum.z * sc.z, sum.w * sc.w);
+						}
+					}
+					__syncwarp();
+					if (lane == 0 && atomicAdd(&s_cnt, 1) == 7) *tk = 0u;  // all four warps are done: ready for the next launch
 				}
 			}
 		}

@@ -258,6 +258,10 @@ struct TcScratch {
 	size_t apack_bytes = 0;
 	float *partial = nullptr;  // split-K partial sums
 	size_t partial_floats = 0;
+	unsigned *tickets = nullptr;  // [TC_TICKETS] zeros: enables the in-kernel split-K reduction for shallow splits
+	int fused_max_split = 3;      // deeper splits use the reduce kernel: one CTA re-reading a whole tile of every split is
+	                              // latency-bound (measured: 9-way splits reduced in-kernel doubled the batched step time)
+	int max_split = 1 << 30;      // cap on the K-split depth (the batched step keeps the partial-sum traffic small)
 	int *err = nullptr;
 };
 
@@ -379,8 +383,15 @@ int state_alloc(tg_state *s) {
 	TG_CUDA(cudaMemsetAsync(s->tickets, 0, sizeof(unsigned) * (V / MV_TN), s->stream));
 	TG_CUDA(cudaMalloc(&s->attn_tickets, sizeof(unsigned) * B));
 	TG_CUDA(cudaMemsetAsync(s->attn_tickets, 0, sizeof(unsigned) * B, s->stream));
-	s->attn_nsplit_local = env_int("TG_ATTN_SPLIT_LOCAL", 16);
-	s->attn_nsplit_global = env_int("TG_ATTN_SPLIT_GLOBAL", 64);
+	// split-KV factor: enough CTAs (batch x splits) to fill the GPU about three times, no more —
+	// every split repeats the q/k norm + RoPE and adds a partial to merge
+	auto pick_split = [&](int cap) {
+		int ns = 1;
+		while (ns < cap && B * ns < 3 * g_num_sms) ns *= 2;
+		return ns;
+	};
+	s->attn_nsplit_local = env_int("TG_ATTN_SPLIT_LOCAL", pick_split(16));
+	s->attn_nsplit_global = env_int("TG_ATTN_SPLIT_GLOBAL", pick_split(64));
 	int nsmax = std::max(s->attn_nsplit_local, s->attn_nsplit_global);
 	TG_TRY(allocf(&s->attn_part, size_t(B) * nsmax * (AT_NH * AT_HD + 8)));
 	auto alloci = [&](int **p, size_t n) -> int {
@@ -988,12 +999,13 @@ int ensure_log(tg_state *s, int steps) {
 
 // K-split of the tensor-core GEMM: enough CTAs to fill the GPU, accumulation chains of at most 24
 // K-blocks (768 rows) for accuracy, as far as the partial-sum buffer allows.
-int tc_pick_split(int M, int K, int N, size_t partial_floats) {
+constexpr size_t TC_TICKETS = 4096;
+int tc_pick_split(int M, int K, int N, size_t partial_floats, int max_split) {
 	const int k_blocks = K / TC_BK;
 	const int ctas = (N / TC_BN) * (((M + TC_BM - 1) / TC_BM + TC_MT - 1) / TC_MT);
 	const int want = std::max((g_num_sms + ctas - 1) / ctas, (k_blocks + 23) / 24);
 	int best = 1;
-	for (int ns = 1; ns <= k_blocks; ns++) {
+	for (int ns = 1; ns <= std::min(k_blocks, max_split); ns++) {
 		if (k_blocks % ns) continue;
 		if (ns > 1 && size_t(ns) * M * N > partial_floats) break;
 		best = ns;
@@ -1035,16 +1047,17 @@ int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream
 	a.N = w.N;
 	a.K = w.K;
 	a.m_tiles = (M + TC_BM - 1) / TC_BM;
-	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats);
-	while (a.nsplit > max_split) a.nsplit = 1;
+	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats, std::min(max_split, sc.max_split));
 	a.ldc = ldc;
 	a.partial = sc.partial;
 	a.err = sc.err;
 	dim3 grid(w.N / TC_BN, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
+	const bool fused = sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
+	a.tickets = fused ? sc.tickets : nullptr;
 	qgemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(wmap, a);
 	count_launch();
 	TG_TRY(check_launch("qgemm_tc"));
-	if (a.nsplit > 1) {
+	if (a.nsplit > 1 && !fused) {
 		const size_t n = size_t(M) * w.N;
 		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, sc.partial, w.s, M, w.N, a.nsplit, ldc);
 		count_launch();
@@ -1066,6 +1079,9 @@ int batched_setup(tg_state *s) {
 	TG_CUDA(cudaMalloc(&s->btc.apack, s->btc.apack_bytes));
 	s->btc.partial_floats = std::min(size_t(24) * B * std::max(I, qd), size_t(1) << 28);
 	TG_CUDA(cudaMalloc(&s->btc.partial, s->btc.partial_floats * 4));
+	TG_CUDA(cudaMalloc(&s->btc.tickets, TC_TICKETS * sizeof(unsigned)));
+	TG_CUDA(cudaMemset(s->btc.tickets, 0, TC_TICKETS * sizeof(unsigned)));
+	s->btc.max_split = env_int("TG_BATCH_MAX_SPLIT", 9);
 	s->btc.err = s->err_flag;
 	(void)V;
 	s->batched_ok = true;
@@ -1535,6 +1551,7 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->bup);
 	cudaFree(s->btc.apack);
 	cudaFree(s->btc.partial);
+	cudaFree(s->btc.tickets);
 	cudaFree(s->d_tmaps);
 	cudaFree(s->d_layers);
 	cudaFree(s->mg_ll);
