@@ -49,7 +49,7 @@ CACHE = os.environ.get("TG_CACHE_DIR", "/tmp")
 PUBLISHED_DECODE_TOK_S = 16.45  # reference README.md:69, Ryzen 5 5500, 1 thread, real weights
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded token from one ncu capture of the decode kernel
 # (profiles/mega_decode_kernel_1B_dram_traffic.md, profiles/mega_decode_kernel_270m_ncu_full.md)
-DRAM_TRAFFIC_PER_STEP = {"1B": 1005218304, "270m": 273278037}
+DRAM_TRAFFIC_PER_STEP = {"1B": 1005668181, "270m": 273534288}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -68,6 +68,15 @@ def algorithmic_bytes_per_token(cfg, positions) -> float:
     for p in positions:
         kv += 2048.0 * (n_local * min(p + 1, cfg.n_pos_local) + n_global * (p + 1))
     return weights + kv / max(len(positions), 1)
+
+
+def measured_tensor_peak():
+    """burst dense bf16 TFLOP/s of MEASURED_PEAKS.json (a kernel timed alone), else the 1590 fallback"""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
 
 
 def measured_peaks():
@@ -261,6 +270,46 @@ def matvec_sweep(capi, torch, hbm_peak):
     return out
 
 
+def gemm_sweep(capi, torch, tf_peak):
+    """isolated int8-weight GEMM (prefill / batched-step operator) at Gemma-3-1B shapes, device-resident.
+    TFLOP/s counts the algorithmic 2*M*K*N; the tensor cores execute three bf16 products per fp32
+    activation (split into three bf16 terms), so the tensor-pipe work is three times that."""
+    import ctypes as C
+
+    lib = capi.load()
+    out = []
+    g = torch.Generator(device="cuda").manual_seed(6)
+    for K, N in [(1152, 6912), (6912, 1152), (1152, 1024)]:
+        w = torch.randint(-127, 128, (K, N), dtype=torch.int8, device="cuda", generator=g)
+        s = torch.rand(N, device="cuda", generator=g) * 1e-2 + 1e-4
+        for M in (16, 178, 1024, 4096):
+            a = torch.randn(M, K, device="cuda", generator=g)
+            c = torch.empty(M, N, device="cuda")
+            stream = torch.cuda.current_stream()
+            sp = C.c_void_p(stream.cuda_stream)
+
+            def run():
+                rc = lib.tg_dev_qgemm(C.c_void_p(c.data_ptr()), C.c_void_p(a.data_ptr()), C.c_void_p(w.data_ptr()),
+                                      C.c_void_p(s.data_ptr()), M, K, N, sp)
+                if rc:
+                    raise RuntimeError(lib.tg_last_error().decode())
+
+            for _ in range(3):
+                run()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(10):
+                run()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us = 1e3 * e0.elapsed_time(e1) / 10
+            tf = 2.0 * M * K * N / us / 1e6
+            out.append({"M": M, "K": K, "N": N, "us": us, "TFLOPs": tf, "tensor_TFLOPs": 3 * tf,
+                        "tensor_frac": 3 * tf / tf_peak if tf_peak else None})
+    return out
+
+
 def run_ours(args):
     rank, local_rank, world = dist_env()
     import torch
@@ -383,6 +432,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_extras:
         try:
             line["matvec_sweep"] = matvec_sweep(capi, torch, hbm_peak)
+            line["gemm_sweep"] = gemm_sweep(capi, torch, measured_tensor_peak())
         except Exception as e:  # the sweep is an extra; the headline line must still print
             line["matvec_sweep_error"] = str(e)
         st.close()
