@@ -1429,7 +1429,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 							*reinterpret_cast<float4 *>(cbuf + i) = v;
 						}
 						__syncthreads();
-						const int r = cdf_cross_block<MG_NWARPS>(cbuf, n, &s_f[5], randf, s_cdf);
+						const int r = cdf_cross_block<MG_NWARPS>(cbuf, n, &s_f[5], randf, s_cdf, c0 == 0 ? 1024 : 0);
 						if (r >= 0) {
 							if (tid == 0) s_i[1] = c0 + r;
 							break;

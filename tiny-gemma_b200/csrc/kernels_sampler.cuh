@@ -159,14 +159,64 @@ constexpr int CDF_PER_WARP = 32 * CDF_PER_LANE;
 // memory; *cum_io (shared) holds the running sum before p[0] and receives the sum after the last
 // element consumed. Returns the first index i with fl(cum + p[0] + ... + p[i]) >= randf, or -1.
 // scratch: 2 * NW + 8 ints of shared memory.
+// The first elements of a row are added one by one by a single thread: the running sum starts at
+// zero and changes binade about log2(position) times, and every change would cost a whole scan
+// round (≈ 1 us, the time of ≈ 400 sequential additions). p >= 0, so the sum never decreases and
+// a group of 8 is searched only when its last partial sum has reached randf.
+__device__ __forceinline__ void cdf_cross_seq(const float *p, int end, float randf, float &cum, int &pos, int &res) {
+	float c = cum;
+	int i = pos;
+	for (; i + 8 <= end; i += 8) {
+		const float4 a = *reinterpret_cast<const float4 *>(p + i), b = *reinterpret_cast<const float4 *>(p + i + 4);
+		float cs[8];
+		cs[0] = c + a.x;
+		cs[1] = cs[0] + a.y;
+		cs[2] = cs[1] + a.z;
+		cs[3] = cs[2] + a.w;
+		cs[4] = cs[3] + b.x;
+		cs[5] = cs[4] + b.y;
+		cs[6] = cs[5] + b.z;
+		cs[7] = cs[6] + b.w;
+		if (cs[7] >= randf) {
+			int k = 7;
+#pragma unroll
+			for (int t = 6; t >= 0; t--)
+				if (cs[t] >= randf) k = t;
+			res = i + k;
+			cum = cs[k];
+			pos = i + k + 1;
+			return;
+		}
+		c = cs[7];
+	}
+	for (; i < end; i++) {
+		c += p[i];
+		if (c >= randf) {
+			res = i;
+			cum = c;
+			pos = i + 1;
+			return;
+		}
+	}
+	cum = c;
+	pos = i;
+}
+
+// `seq_limit`: leading elements that one thread adds sequentially (see cdf_cross_seq) before the
+// block-wide scan takes over; pass ~1000 for the start of a row, 0 for later chunks. p must be
+// 16-byte aligned.
 template <int NW>
-__device__ int cdf_cross_block(const float *p, int n, float *cum_io, float randf, int *scratch) {
+__device__ int cdf_cross_block(const float *p, int n, float *cum_io, float randf, int *scratch, int seq_limit = 0) {
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	CdfFn *wt = reinterpret_cast<CdfFn *>(scratch);  // per-warp composite
 	int *s_pos = scratch + 2 * NW, *s_res = scratch + 2 * NW + 1;
 	if (tid == 0) {
-		*s_pos = 0;
-		*s_res = -1;
+		float cum = *cum_io;
+		int pos = 0, res = -1;
+		if (seq_limit > 0) cdf_cross_seq(p, min(n, seq_limit), randf, cum, pos, res);
+		*cum_io = cum;
+		*s_pos = pos;
+		*s_res = res;
 	}
 	__syncthreads();
 	for (int guard = 0; guard < n + 64; guard++) {  // every round consumes at least one element
@@ -360,7 +410,7 @@ __global__ void __launch_bounds__(SM_THREADS) minp_kernel(SampleArgs a) {
 		}
 		__syncthreads();
 		if (found < 0) {
-			const int r = cdf_cross_block<SM_NWARPS>(chunk, n, &s_cum, randf, scratch);
+			const int r = cdf_cross_block<SM_NWARPS>(chunk, n, &s_cum, randf, scratch, c0 == 0 ? 1024 : 0);
 			if (r >= 0) found = c0 + r;
 		}
 		__syncthreads();
@@ -387,7 +437,7 @@ __global__ void __launch_bounds__(SM_THREADS) inverse_cdf_kernel(const float *p,
 		const int m = min(MP_CHUNK, n - c0);
 		for (int i = tid; i < m; i += SM_THREADS) chunk[i] = p[c0 + i];
 		__syncthreads();
-		const int r = cdf_cross_block<SM_NWARPS>(chunk, m, &s_cum, randf, scratch);
+		const int r = cdf_cross_block<SM_NWARPS>(chunk, m, &s_cum, randf, scratch, c0 == 0 ? 1024 : 0);
 		if (r >= 0) found = c0 + r;
 		__syncthreads();
 	}
