@@ -368,6 +368,68 @@ def test_error_paths(capi, model_270m, synth, tmp_path):
 
 
 # ------------------------------------------------------------------ 1B
+def test_long_prompt_vs_live_reference_270m(capi, ref_or_none, weights_270m, synth):
+    """2100-token prompt against the compiled reference run live: the local ring wraps four times, global
+    layers hold 2100 positions; prefill logits, then four decode steps. (The reference's prefill lets a
+    sliding-window query see 513 keys, qs-512..qs, while its ring cache gives a decoded token 512: both
+    are reproduced, so prefill(S) and prefill(S-1)+decode legitimately differ on long prompts.)"""
+    if ref_or_none is None:
+        pytest.skip("needs oracle/_ref/libtgref.so")
+    S = 2100
+    rm = ref_or_none.model("270m", weights_270m)
+    rs = rm.state(1 << 20)
+    m = capi.Model("270m").load_file(weights_270m)
+    m.set_tables(*rs.tables())
+    st = m.state(1, S + 16)
+    ids = synth.random_prompt(S, 4242)
+    lr = rs.prefill(ids)
+    lg = st.prefill(ids)[0]
+    assert rel_l2(lg, lr) <= 5e-5
+    tok = int(np.argmax(lr))
+    for _ in range(4):
+        lr = rs.decode(tok)
+        lg = st.decode([tok])[0]
+        assert rel_l2(lg, lr) <= 5e-5
+        tok = int(ref_or_none.argmax_logits(lr))
+    assert st.position() == S + 4
+    st.close()
+    m.close()
+    rs.close()
+    rm.close()
+
+
+@pytest.mark.parametrize("size", ["270m", "1B"])
+def test_long_context_16384_independent_paths_agree(capi, synth, weights_270m, weights_1b, size, monkeypatch):
+    """16384-token prompt + decode (the long-context configuration). The CPU reference needs minutes at this
+    size, so the check is agreement between independent implementations of the same arithmetic: prefill with
+    the tensor-core GEMM vs the exact CUDA-core GEMM, then decode with the persistent kernel vs the per-phase
+    kernels, teacher-forced. Each pair shares no GEMM / matvec / attention-loop code."""
+    S = 16384
+    path = weights_1b if size == "1B" else weights_270m
+    m = capi.Model(size).load_file(path)
+    m.build_tables(1 << 20)
+    ids = synth.random_prompt(S, 4242)
+    a = m.state(1, S + 16)
+    la = a.prefill(ids)[0]
+    monkeypatch.setenv("TG_GEMM_TC", "0")
+    monkeypatch.setenv("TG_MEGA", "0")
+    b = m.state(1, S + 16)
+    lb = b.prefill(ids)[0]
+    monkeypatch.delenv("TG_GEMM_TC")
+    monkeypatch.delenv("TG_MEGA")
+    assert rel_l2(la, lb) <= 5e-5
+    assert a.position() == b.position() == S
+    tok = a.sample_argmax()
+    for _ in range(6):
+        la = a.decode(tok)[0]
+        lb = b.decode(tok)[0]
+        assert rel_l2(la, lb) <= 5e-5
+        tok = a.sample_argmax()
+    a.close()
+    b.close()
+    m.close()
+
+
 def test_e2e_1b_vs_live_reference(capi, ref_or_none, weights_1b, synth):
     if ref_or_none is None:
         pytest.skip("needs oracle/_ref/libtgref.so")
