@@ -57,6 +57,10 @@ struct MgPhase {
 	int ntiles;    // column tiles
 	int units;     // ntiles * nsplit (<= grid size)
 	int bytes;     // shared-memory bytes of this phase's region
+	// thread mapping constants (integer division by a run-time value costs ~100 clk per use, and the tile
+	// helpers need two or three of them per call): rstep = 384 / segs, m_x = ceil(2^32 / x) for __umulhi
+	int rstep;
+	unsigned m_segs, m_rstep;
 };
 
 struct MgLayer {
@@ -345,14 +349,14 @@ __device__ __forceinline__ void mg_fma16(float (&acc)[16], const int4 &v, float 
 // advances by 16 * 384 bytes per step.
 __device__ __forceinline__ bool mg_seg_major(int segs) { return (segs & (segs - 1)) != 0; }
 
-__device__ __forceinline__ void mg_tile_dot(float (&acc)[16], const uint8_t *tile, int rows, int segs, const float *xs) {
-	const int rstep = MG_THREADS / segs;
+__device__ __forceinline__ void mg_tile_dot(float (&acc)[16], const uint8_t *tile, int rows, const MgPhase &ph, const float *xs) {
+	const int segs = ph.segs, rstep = ph.rstep;
 	int row, grp;
 	if (mg_seg_major(segs)) {
-		grp = threadIdx.x / rstep;
+		grp = int(__umulhi(threadIdx.x, ph.m_rstep));
 		row = threadIdx.x - grp * rstep;
 	} else {
-		row = threadIdx.x / segs;
+		row = segs == 1 ? int(threadIdx.x) : int(__umulhi(threadIdx.x, ph.m_segs));  // (2^32 / 1 does not fit the constant)
 		grp = threadIdx.x - row * segs;
 	}
 	const uint8_t *p = tile + 16 * (row * segs + grp);
@@ -385,7 +389,8 @@ __device__ __forceinline__ void mg_tile_dot(float (&acc)[16], const uint8_t *til
 // each (the shuffle unit issues one warp instruction per clock per SM). The
 // per-warp results meet in `red` ([12][TN] floats). Returns the total of column
 // threadIdx.x for threads < TN. The order of additions is fixed.
-__device__ __forceinline__ float mg_tile_reduce(float (&v)[16], int segs, float *red) {
+__device__ __forceinline__ float mg_tile_reduce(float (&v)[16], const MgPhase &ph, float *red) {
+	const int segs = ph.segs;
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 	const bool sm = mg_seg_major(segs);
 	const int TN = 16 * segs;
@@ -436,8 +441,7 @@ __device__ __forceinline__ float mg_tile_reduce(float (&v)[16], int segs, float 
 		v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
 		writer = (lane & 1) == 0;
 	}
-	const int rstep = MG_THREADS / segs;
-	const int grp = sm ? int(threadIdx.x) / rstep : (lane & (segs - 1));
+	const int grp = sm ? int(__umulhi(threadIdx.x, ph.m_rstep)) : (lane & (segs - 1));
 	__syncthreads();  // `red` may still be read from a previous use
 	if (writer) {
 #pragma unroll
@@ -448,7 +452,7 @@ __device__ __forceinline__ float mg_tile_reduce(float (&v)[16], int segs, float 
 	float s = 0.0f;
 	if (int(threadIdx.x) < TN) {
 		if (sm) {
-			const int wpg = MG_NWARPS / segs, g = threadIdx.x >> 4;  // warps per group
+			const int g = threadIdx.x >> 4, wpg = ph.rstep >> 5;  // column group, warps per group
 			for (int w = g * wpg; w < (g + 1) * wpg; w++) s += red[w * TN + threadIdx.x];
 		} else {
 #pragma unroll
@@ -460,12 +464,12 @@ __device__ __forceinline__ float mg_tile_reduce(float (&v)[16], int segs, float 
 
 // One shared copy of "tile . x -> column sums": the phases run once per layer,
 // so inlining this at every call site only thrashes the instruction cache.
-__device__ __noinline__ float mg_tile_colsum(const uint8_t *tile, int rows, int segs, const float *xs, float *red) {
+__device__ __noinline__ float mg_tile_colsum(const uint8_t *tile, int rows, const MgPhase &ph, const float *xs, float *red) {
 	float acc[16];
 #pragma unroll
 	for (int i = 0; i < 16; i++) acc[i] = 0.0f;
-	mg_tile_dot(acc, tile, rows, segs, xs);
-	return mg_tile_reduce(acc, segs, red);
+	mg_tile_dot(acc, tile, rows, ph, xs);
+	return mg_tile_reduce(acc, ph, red);
 }
 
 // TMA issue for one phase region: `nmat` matrices (1, or 2 for up+gate), each
@@ -886,7 +890,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				if (active) mg_wait_tma(ctx, &bar_A, pA);
 				MG_STAMP();
 				if (active) {
-					const float s = mg_tile_colsum(R_A, a.A.kc, a.A.segs, xs + k0, red);
+					const float s = mg_tile_colsum(R_A, a.A.kc, a.A, xs + k0, red);
 					// q, k, v tiles are consecutive and equally wide: tile -> column of the q|k|v vector
 					if (tid < a.A.TN) ll_store(part_A + size_t(split) * NQ + tile * a.A.TN + tid, s);
 				}
@@ -1088,7 +1092,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				MG_STAMP();
 				if (active) {
 					mg_wait_tma(ctx, &bar_C, pC);
-					const float s = mg_tile_colsum(R_C, a.C.kc, a.C.segs, xs, red);
+					const float s = mg_tile_colsum(R_C, a.C.kc, a.C, xs, red);
 					if (tid < a.C.TN) ll_store(part_C + size_t(split) * D + tile * a.C.TN + tid, s);
 				}
 				pC ^= 1;
@@ -1115,10 +1119,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				if (active) mg_wait_tma(ctx, &bar_D, pD);
 				MG_STAMP();
 				float up = 0.0f;
-				if (active) up = mg_tile_colsum(R_D, D, a.Dp.segs, xs, red);
+				if (active) up = mg_tile_colsum(R_D, D, a.Dp, xs, red);
 				MG_STAMP();
 				if (active) {
-					const float gate = mg_tile_colsum(R_D + a.Dp.TN * D, D, a.Dp.segs, xs, red);
+					const float gate = mg_tile_colsum(R_D + a.Dp.TN * D, D, a.Dp, xs, red);
 					if (tid < a.Dp.TN) ll_store(act + cta * a.Dp.TN + tid, a.lut(gate * sg_r) * (up * su_r));
 				}
 				pD ^= 1;
@@ -1163,7 +1167,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				if (warp == 1 && l + 1 < L && (a.sched & 1)) mg_issue_D(a, s_ly, l + 1, cta, R_D, &bar_D, pol);
 				MG_STAMP();
 				if (active) {
-					const float s = mg_tile_colsum(R_E, a.E.kc, a.E.segs, xs, red);
+					const float s = mg_tile_colsum(R_E, a.E.kc, a.E, xs, red);
 					if (tid < a.E.TN) st_tagged(pe_cur + size_t(split) * D + tile * a.E.TN + tid, s, gl + 1u);
 				}
 				pE ^= 1;
@@ -1224,10 +1228,11 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 			}
 			float acc[16];
 			float sc_tile = 0.0f;
-			const int rstep = MG_THREADS / ph.segs;
+			const int rstep = ph.rstep;
+			const int row0 = ph.segs == 1 ? tid : int(__umulhi(tid, ph.m_segs));
+			int stg = 0, c = 0, tile = cta;  // ring stage, stage within the tile, column tile: advanced at the loop's end
 #pragma unroll 1
 			for (int q = 0; q < total; q++) {
-				const int stg = q % MG_LM_STAGES, c = q % spt, tile = cta + (q / spt) * G;
 				if (c == 0) {
 #pragma unroll
 					for (int i = 0; i < 16; i++) acc[i] = 0.0f;
@@ -1238,7 +1243,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				{
 					const uint8_t *tp = ring + stg * stage_bytes + 16 * tid;
 					const float *xc = xs + c * stage_rows;
-					int row = tid / ph.segs;
+					int row = row0;
 #pragma unroll 1
 					for (; row + 3 * rstep < stage_rows; row += 4 * rstep) {
 						int4 v0 = *reinterpret_cast<const int4 *>(tp);
@@ -1272,7 +1277,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 				pemp ^= (1u << stg);
 				__syncwarp();
 				if (c == spt - 1) {
-					float s = mg_tile_reduce(acc, ph.segs, red);
+					float s = mg_tile_reduce(acc, ph, red);
 					if (tid < ph.TN) {
 						const int v = tile * ph.TN + tid;
 						const float lg = s * sc_tile;
@@ -1283,6 +1288,11 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const __grid
 							best_i = v;
 						}
 					}
+				}
+				if (++stg == MG_LM_STAGES) stg = 0;
+				if (++c == spt) {
+					c = 0;
+					tile += G;
 				}
 			}
 		}

@@ -678,6 +678,13 @@ int largest_box_rows(int kc) {
 	return 1;
 }
 
+// thread-mapping constants of a phase: x / d == __umulhi(x, ceil(2^32 / d)) for x * d < 2^32
+void mg_fill_mapping(MgPhase *ph) {
+	ph->rstep = MG_THREADS / ph->segs;
+	ph->m_segs = unsigned((0x100000000ull + ph->segs - 1) / ph->segs);
+	ph->m_rstep = unsigned((0x100000000ull + ph->rstep - 1) / ph->rstep);
+}
+
 // Choose the tile width and K-split of one phase so that as many of the G CTAs
 // as possible get exactly one unit. n_cols lists the matrices that share the
 // phase's column tiling (Q,K,V) — a tile never straddles two of them.
@@ -708,7 +715,8 @@ bool plan_phase(MgPhase *out, int K, const std::vector<int> &n_cols, int nmat, b
 			if (score > best_score) {
 				best_score = score;
 				const int br = largest_box_rows(kc);
-				*out = MgPhase{TN, segs, ns, kc, br, kc / br, ntiles, units, int(bytes)};
+				*out = MgPhase{TN, segs, ns, kc, br, kc / br, ntiles, units, int(bytes), 0, 0u, 0u};
+				mg_fill_mapping(out);
 			}
 		}
 	}
@@ -733,7 +741,8 @@ int mega_setup(tg_state *s) {
 	if (!plan_phase(&a.A, D, {qd, kd, kd}, 1, true, G, budget / 8) || !plan_phase(&a.C, qd, {D}, 1, true, G, budget / 8) ||
 	    !plan_phase(&a.Dp, D, {I}, 2, false, G, budget) || !plan_phase(&a.E, I, {D}, 1, true, G, budget / 2))
 		return fail(TG_ESHAPE, "no phase plan fits");
-	a.LM = MgPhase{MG_LM_TN, MG_LM_TN / 16, 1, D, largest_box_rows(D), D / largest_box_rows(D), V / MG_LM_TN, V / MG_LM_TN, 0};
+	a.LM = MgPhase{MG_LM_TN, MG_LM_TN / 16, 1, D, largest_box_rows(D), D / largest_box_rows(D), V / MG_LM_TN, V / MG_LM_TN, 0, 0, 0u, 0u};
+	mg_fill_mapping(&a.LM);
 	a.lm_bps = (a.LM.nboxes % 2 == 0) ? 2 : 1;  // TMA boxes per ring stage
 	const int ring = MG_LM_STAGES * a.LM.TN * a.LM.box_rows * a.lm_bps;
 	auto up = [](int v) { return (v + 1023) & ~1023; };
