@@ -261,7 +261,8 @@ struct TcScratch {
 	unsigned *tickets = nullptr;  // [TC_TICKETS] zeros: enables the in-kernel split-K reduction for shallow splits
 	int fused_max_split = 3;      // deeper splits use the reduce kernel: one CTA re-reading a whole tile of every split is
 	                              // latency-bound (measured: 9-way splits reduced in-kernel doubled the batched step time)
-	int max_split = 1 << 30;      // cap on the K-split depth (the batched step keeps the partial-sum traffic small)
+	int max_split = 9;            // cap on the K-split depth: deeper splits (one or two K-blocks per CTA) cost more in partial-sum
+	                              // traffic and per-CTA fixed cost than they gain in parallelism (TG_GEMM_MAX_SPLIT overrides)
 	int *err = nullptr;
 };
 
@@ -710,7 +711,8 @@ bool plan_phase(MgPhase *out, int K, const std::vector<int> &n_cols, int nmat, b
 			const long bytes = long(nmat) * TN * kc;
 			if (bytes > max_bytes) continue;
 			// as many busy SMs as possible; then few K-splits (every CTA re-reads all split partial sums in
-			// its norm prologue); rows narrower than a 32-byte DRAM sector are avoided
+			// its norm prologue); 16-column tiles are avoided (measured: O projection as 16 x 512 x 2 splits
+			// instead of 32 x 256 x 4 doubles the attention-merge rows per CTA and loses 2.5 %)
 			long score = long(units) * 1000 - ns * env_int("TG_MEGA_SPLIT_COST", 40) - (TN < 32 ? 2000 : 0);
 			if (score > best_score) {
 				best_score = score;
@@ -1056,7 +1058,7 @@ int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream
 	a.N = w.N;
 	a.K = w.K;
 	a.m_tiles = (M + TC_BM - 1) / TC_BM;
-	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats, std::min(max_split, sc.max_split));
+	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats, std::min(max_split, env_int("TG_GEMM_MAX_SPLIT", sc.max_split)));
 	a.ldc = ldc;
 	a.partial = sc.partial;
 	a.err = sc.err;
