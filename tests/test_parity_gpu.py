@@ -278,20 +278,19 @@ def test_device_loop_equals_stepwise(capi, model_270m, golden):
         tok = b.sample_argmax()
         step.append(int(tok[0]))
     assert list(toks_loop) == step
-    # sampled loop: the in-kernel min-p sampler against the standalone one on the same
-    # logits (teacher-forced with the loop's tokens). The two add the softmax denominator in
-    # different fixed orders, so it can differ in the last bit; a token may then move to the
-    # neighbouring index when the uniform lies within an ulp of a CDF step.
+    # sampled loop: the sampler inside the persistent kernel against the step-by-step one
+    # (tg_decode + tg_sample_minp). For one sequence the step-by-step sampler spreads the row over
+    # the GPU with the same partition and the same order of every floating-point sum, and the
+    # inverse CDF is exact in both, so the tokens must be identical.
     rf = np.random.default_rng(1).random(32, dtype=np.float32)
     ta = a.generate([step[-1]], 32, 0.1, 0.7, rf)[:, 0]
     feed = np.array([step[-1]], np.int32)
-    diffs = []
+    tb = []
     for i in range(32):
         b.decode(feed, want_logits=False)
-        tok = b.sample_minp(0.1, 0.7, rf[i:i + 1])
-        diffs.append(abs(int(tok[0]) - int(ta[i])))
-        feed = ta[i:i + 1].astype(np.int32)
-    assert max(diffs) <= 1 and sum(1 for d in diffs if d) <= 3, diffs
+        feed = b.sample_minp(0.1, 0.7, rf[i:i + 1]).astype(np.int32)
+        tb.append(int(feed[0]))
+    assert list(ta) == tb
     a.close()
     b.close()
 

@@ -421,6 +421,156 @@ __global__ void __launch_bounds__(SM_THREADS) minp_kernel(SampleArgs a) {
 	}
 }
 
+
+// ------------------------------------------------------------------ grid-wide min-p (one sequence)
+// ops::minp_logits for a single row spread over G CTAs of SG_THREADS threads (cooperative launch: the
+// CTAs meet at a bounded grid barrier). It partitions the row and orders every floating-point sum
+// exactly like the sampler inside the persistent decode kernel — CTA c owns the 128-column tiles
+// c, c + G, ...; per-thread strided sums, a 12-warp block sum, the G partial sums added by one warp
+// in lane-strided order — so a token sampled step by step (tg_decode + tg_sample_minp) is the token
+// the device-resident loop samples. The row is overwritten with the probabilities, as the
+// reference does.
+constexpr int SG_THREADS = 384;
+constexpr int SG_NWARPS = SG_THREADS / 32;
+constexpr int SG_TILE = 128;
+constexpr int SG_SPIN_CAP = 1 << 22;
+
+__device__ __forceinline__ bool sg_grid_sync(unsigned *bar, unsigned &epoch, unsigned G, int *fail) {
+	__syncthreads();
+	epoch += 1;
+	if (threadIdx.x == 0 && !*(volatile int *)fail) {
+		__threadfence();
+		const unsigned old = atomicAdd(bar, 1u);
+		if (old + 1u < epoch * G) {
+			int spins = 0;
+			unsigned v;
+			do {
+				asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar) : "memory");
+			} while (v < epoch * G && ++spins < SG_SPIN_CAP);
+			if (v < epoch * G) *fail = 1;  // the wait ran out: everybody falls through from here on
+		}
+	}
+	__syncthreads();
+	return !*(volatile int *)fail;
+}
+
+template <int NW>
+__device__ __forceinline__ float sg_block_sum(float v, float *red) {
+	v = warp_sum(v);
+	__syncthreads();
+	if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+	__syncthreads();
+	float t = 0.0f;
+#pragma unroll
+	for (int w = 0; w < NW; w++) t += red[w];
+	return t;
+}
+
+// part: [2 * G] floats of scratch, probs: [V] floats of scratch, bar: one zeroed word, err: error word
+__global__ void __launch_bounds__(SG_THREADS, 1) minp_grid_kernel(SampleArgs a, unsigned *bar, float *part, float *probs, int *err) {
+	__shared__ float red[SG_NWARPS];
+	__shared__ float chunk[MP_CHUNK];
+	__shared__ int scratch[2 * SG_NWARPS + 8];
+	__shared__ float s_cum, s_inv, s_max;
+	__shared__ int s_fail, s_tok;
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int cta = blockIdx.x, G = gridDim.x;
+	const int ntiles = a.V / SG_TILE;
+	const int my_tiles = (ntiles - cta + G - 1) / G;
+	unsigned epoch = 0;
+	if (tid == 0) s_fail = 0;
+	__syncthreads();
+	// (1)+(2) row maximum of z = logit / temp
+	float mx = -INFINITY;
+#pragma unroll 1
+	for (int j = tid; j < my_tiles * SG_TILE; j += SG_THREADS) {
+		const int v = (cta + (j / SG_TILE) * G) * SG_TILE + (j % SG_TILE);
+		mx = fmaxf(mx, __ldcg(a.logits + v) / a.temp);
+	}
+	mx = warp_max(mx);
+	if (lane == 0) red[warp] = mx;
+	__syncthreads();
+	if (tid == 0) {
+		float m = red[0];
+		for (int w = 1; w < SG_NWARPS; w++) m = fmaxf(m, red[w]);
+		__stcg(part + cta, m);
+	}
+	sg_grid_sync(bar, epoch, G, &s_fail);
+	if (warp == 0) {
+		float m = -INFINITY;
+#pragma unroll 1
+		for (int c = lane; c < G; c += 32) m = fmaxf(m, __ldcg(part + c));
+		m = warp_max(m);
+		if (lane == 0) s_max = m;
+	}
+	__syncthreads();
+	const float gmax = s_max;
+	// (3)+(4) p = exp(z - max); maxp = exp(0), so the cut is minp * exp(gmax - gmax); masked denominator
+	const float cut = a.minp * expf(gmax - gmax);
+	float ds = 0.0f;
+#pragma unroll 1
+	for (int j = tid; j < my_tiles * SG_TILE; j += SG_THREADS) {
+		const int v = (cta + (j / SG_TILE) * G) * SG_TILE + (j % SG_TILE);
+		const float pv = expf(__ldcg(a.logits + v) / a.temp - gmax);
+		__stcg(probs + v, pv);
+		ds += (pv < cut) ? 0.0f : pv;
+	}
+	ds = sg_block_sum<SG_NWARPS>(ds, red);
+	if (tid == 0) __stcg(part + G + cta, ds);
+	sg_grid_sync(bar, epoch, G, &s_fail);
+	if (warp == 0) {
+		float dv = 0.0f;
+#pragma unroll 1
+		for (int c = lane; c < G; c += 32) dv += __ldcg(part + G + c);
+		dv = warp_sum(dv);
+		if (lane == 0) s_inv = 1.0f / dv;
+	}
+	__syncthreads();
+	const float inv = s_inv;
+	// (5) every probability is scaled in place of its logit
+#pragma unroll 1
+	for (int j = tid; j < my_tiles * SG_TILE; j += SG_THREADS) {
+		const int v = (cta + (j / SG_TILE) * G) * SG_TILE + (j % SG_TILE);
+		__stcg(a.logits + v, __ldcg(probs + v) * inv);
+	}
+	// (6) inverse CDF by CTA 0
+	if (cta == 0 && !*(volatile int *)&s_fail) {
+		float randf = 0.0f;
+		const int rc = a.randf_count[0];
+		if (rc < a.randf_cap) randf = a.randf[size_t(rc) * a.B];
+		if (tid == 0) {
+			s_cum = 0.0f;
+			s_tok = -1;
+		}
+		__syncthreads();
+#pragma unroll 1
+		for (int c0 = 0; c0 < a.V; c0 += MP_CHUNK) {
+			const int n = min(MP_CHUNK, a.V - c0);
+#pragma unroll 4
+			for (int i = tid * 4; i < n; i += SG_THREADS * 4) {
+				float4 v = __ldcg(reinterpret_cast<const float4 *>(probs + c0 + i));
+				v.x *= inv;
+				v.y *= inv;
+				v.z *= inv;
+				v.w *= inv;
+				*reinterpret_cast<float4 *>(chunk + i) = v;
+			}
+			__syncthreads();
+			const int r = cdf_cross_block<SG_NWARPS>(chunk, n, &s_cum, randf, scratch, c0 == 0 ? 1024 : 0);
+			if (r >= 0) {
+				if (tid == 0) s_tok = c0 + r;
+				break;
+			}
+		}
+		__syncthreads();
+		if (tid == 0) {
+			emit_token(a, 0, s_tok < 0 ? 0 : s_tok);
+			a.randf_count[0] = rc + 1;
+		}
+	}
+	if (tid == 0 && *(volatile int *)&s_fail) atomicExch(err, 8);
+}
+
 // The inverse-CDF step in isolation over an explicit vector p[0..n) in global memory, starting
 // from the running sum cum0: *idx = first i with fl(cum0 + p[0] + ... + p[i]) >= randf, else -1.
 // One CTA; *cum_out receives the sum after the last element consumed.

@@ -972,6 +972,18 @@ SampleArgs sample_args(tg_state *s, float minp, float temp, bool log_tokens) {
 
 int enqueue_sampler(tg_state *s, float minp, float temp, bool log_tokens) {
 	SampleArgs a = sample_args(s, minp, temp, log_tokens);
+	if (minp < 1.0f && s->mega_ok && s->B == 1 && env_int("TG_MINP_GRID", 1)) {
+		// one sequence: the row is spread over the whole GPU, sums ordered like the persistent kernel's sampler
+		TG_CUDA(cudaMemsetAsync(s->mg_bar + 8, 0, 4, s->stream));
+		unsigned *bar = s->mg_bar + 8;
+		float *part = s->mg_samp_f;
+		float *probs = s->mg_probs;
+		int *err = s->err_flag;
+		void *params[] = {&a, &bar, &part, &probs, &err};
+		TG_CUDA(cudaLaunchCooperativeKernel((void *)minp_grid_kernel, dim3(s->mega_grid), dim3(SG_THREADS), params, 0, s->stream));
+		count_launch();
+		return check_launch("minp_grid");
+	}
 	if (minp < 1.0f) {  // transformer.hpp:208,229: min-p sampling iff minp < 1
 		minp_kernel<<<s->B, SM_THREADS, 0, s->stream>>>(a);
 		count_launch();
