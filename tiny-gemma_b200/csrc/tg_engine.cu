@@ -299,6 +299,7 @@ struct tg_state {
 	int *randf_count = nullptr;        // [B]
 	int *err_flag = nullptr;
 	int *host_pin = nullptr;           // pinned staging, 64 KiB
+	bool staging_busy = false;         // an enqueued copy may still read host_pin (set by the asynchronous tg_decode)
 	// prefill scratch (grow-only)
 	float *pf = nullptr;
 	size_t pf_floats = 0;
@@ -994,10 +995,20 @@ int enqueue_sampler(tg_state *s, float minp, float temp, bool log_tokens) {
 	return check_launch("argmax");
 }
 
+// the pinned staging buffer may be overwritten only when no enqueued copy still reads it
+int staging_acquire(tg_state *s) {
+	if (s->staging_busy) {
+		TG_CUDA(cudaStreamSynchronize(s->stream));
+		s->staging_busy = false;
+	}
+	return TG_OK;
+}
+
 int check_err_flag(tg_state *s) {
 	int flag = 0;
 	TG_CUDA(cudaMemcpyAsync(s->host_pin + 8192, s->err_flag, 4, cudaMemcpyDeviceToHost, s->stream));
 	TG_CUDA(cudaStreamSynchronize(s->stream));
+	s->staging_busy = false;
 	flag = s->host_pin[8192];
 	if (flag) {
 		cudaMemsetAsync(s->err_flag, 0, 4, s->stream);
@@ -1659,6 +1670,7 @@ int tg_prefill(tg_state *s, const int *ids, int S, float *logits_host) {
 	for (int b = 0; b < s->B; b++) TG_TRY(enqueue_prefill_seq(s, b, S));
 	// position_ptr = S; ring base per decode.hpp:98-103
 	std::vector<int> pos(s->B, S), rb(s->B, S >= c.n_pos_local ? S : 0);
+	TG_TRY(staging_acquire(s));
 	std::memcpy(s->host_pin, pos.data(), 4 * s->B);
 	std::memcpy(s->host_pin + s->B, rb.data(), 4 * s->B);
 	TG_CUDA(cudaMemcpyAsync(s->next_pos, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
@@ -1679,6 +1691,9 @@ int tg_decode(tg_state *s, const int *ids, float *logits_host) {
 	for (int b = 0; b < s->B; b++)
 		if (s->host_pos[b] >= s->max_pos_global) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
 	if (ids) {
+		for (int b = 0; b < s->B; b++)
+			if (ids[b] < 0 || ids[b] >= m->cfg.n_vocab) return fail(TG_EINVAL, "token id out of range");
+		TG_TRY(staging_acquire(s));
 		std::memcpy(s->host_pin, ids, 4 * s->B);
 		TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
 	}
@@ -1686,10 +1701,14 @@ int tg_decode(tg_state *s, const int *ids, float *logits_host) {
 		TG_TRY(mega_launch(s, 1, 0, 2.0f, 1.0f, false));
 	else
 		TG_TRY(enqueue_decode_step(s));
-	if (logits_host)
-		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, s->stream));
-	TG_TRY(check_err_flag(s));
 	for (int b = 0; b < s->B; b++) s->host_pos[b] += 1;
+	s->staging_busy = ids != nullptr;
+	if (logits_host) {
+		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, s->stream));
+		TG_TRY(check_err_flag(s));
+	}
+	// without a host read-back the call only enqueues: the step runs while the caller prepares the sampler
+	// call, and a device-side error (a wait that ran out) is reported by the next call that synchronises
 	return TG_OK;
 }
 
@@ -1698,7 +1717,7 @@ int tg_sample_argmax(tg_state *s, int *toks_host) {
 	TG_CUDA(cudaSetDevice(s->m->device));
 	TG_TRY(enqueue_sampler(s, 2.0f, 1.0f, false));
 	TG_CUDA(cudaMemcpyAsync(s->host_pin, s->tok, 4 * s->B, cudaMemcpyDeviceToHost, s->stream));
-	TG_CUDA(cudaStreamSynchronize(s->stream));
+	TG_TRY(check_err_flag(s));  // synchronises
 	if (toks_host) std::memcpy(toks_host, s->host_pin, 4 * s->B);
 	return TG_OK;
 }
@@ -1722,10 +1741,19 @@ int tg_state_set_randf(tg_state *s, const float *randf_host, int n) {
 int tg_sample_minp(tg_state *s, float minp, float temp, const float *randf_host, int *toks_host) {
 	if (!s || !randf_host) return fail(TG_EINVAL, "bad argument");
 	if (!(minp < 1.0f)) return fail(TG_EINVAL, "minp must be < 1 (the reference uses argmax otherwise, transformer.hpp:208)");
-	TG_TRY(tg_state_set_randf(s, randf_host, 1));
+	TG_CUDA(cudaSetDevice(s->m->device));
+	if (s->randf_cap >= 1 && size_t(s->B) * 4 <= 4096) {
+		// one uniform per sequence, staged through pinned memory: no synchronisation before the launch
+		float *stage = reinterpret_cast<float *>(s->host_pin + 4096);
+		std::memcpy(stage, randf_host, size_t(s->B) * 4);
+		TG_CUDA(cudaMemcpyAsync(s->randf, stage, size_t(s->B) * 4, cudaMemcpyHostToDevice, s->stream));
+		TG_CUDA(cudaMemsetAsync(s->randf_count, 0, 4 * s->B, s->stream));
+	} else {
+		TG_TRY(tg_state_set_randf(s, randf_host, 1));
+	}
 	TG_TRY(enqueue_sampler(s, minp, temp, false));
 	TG_CUDA(cudaMemcpyAsync(s->host_pin, s->tok, 4 * s->B, cudaMemcpyDeviceToHost, s->stream));
-	TG_CUDA(cudaStreamSynchronize(s->stream));
+	TG_TRY(check_err_flag(s));  // synchronises
 	if (toks_host) std::memcpy(toks_host, s->host_pin, 4 * s->B);
 	return TG_OK;
 }
@@ -1774,6 +1802,7 @@ int tg_generate(tg_state *s, const int *first_ids, int n_steps, float minp, floa
 		if (!randf_host) return fail(TG_EINVAL, "min-p sampling needs uniforms");
 		TG_TRY(tg_state_set_randf(s, randf_host, n_steps));
 	}
+	TG_TRY(staging_acquire(s));
 	std::memcpy(s->host_pin, first_ids, 4 * s->B);
 	TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
 	TG_TRY(tg_generate_async(s, n_steps, minp, temp));
@@ -1812,6 +1841,7 @@ int tg_decode_hidden(tg_state *s, const int *ids) {
 	for (int b = 0; b < s->B; b++)
 		if (s->host_pos[b] >= s->max_pos_global) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
 	if (ids) {
+		TG_TRY(staging_acquire(s));
 		std::memcpy(s->host_pin, ids, 4 * s->B);
 		TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
 	}
