@@ -54,6 +54,24 @@ constexpr int TC_SPIN_CAP = 1 << 24;
 
 // ------------------------------------------------------------------ split + pack
 // out: [3 terms][m_tiles][k_blocks][TC_TILE_BYTES]; rows >= M are zero.
+// fp32 x[8] (8 consecutive k of one row) -> the three bf16 terms, stored at the operand-layout offset
+__device__ __forceinline__ void tc_pack8(__nv_bfloat16 *out, size_t term_stride, int k_blocks, int row, int k8, const float (&x)[8]) {
+	__align__(16) __nv_bfloat16 hi[8], mid[8], lo[8];
+#pragma unroll
+	for (int i = 0; i < 8; i++) {
+		hi[i] = __float2bfloat16_rn(x[i]);
+		const float r1 = x[i] - __bfloat162float(hi[i]);  // exact
+		mid[i] = __float2bfloat16_rn(r1);
+		const float r2 = r1 - __bfloat162float(mid[i]);   // exact
+		lo[i] = __float2bfloat16_rn(r2);
+	}
+	const int mt = row / TC_BM, r = row % TC_BM, kb = (8 * k8) / TC_BK, kc = ((8 * k8) % TC_BK) / 8;
+	const size_t off = (size_t(mt) * k_blocks + kb) * (TC_TILE_BYTES / 2) + (r / 8) * 256 + kc * 64 + (r % 8) * 8;
+	*reinterpret_cast<uint4 *>(out + off) = *reinterpret_cast<const uint4 *>(hi);
+	*reinterpret_cast<uint4 *>(out + term_stride + off) = *reinterpret_cast<const uint4 *>(mid);
+	*reinterpret_cast<uint4 *>(out + 2 * term_stride + off) = *reinterpret_cast<const uint4 *>(lo);
+}
+
 __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bfloat16 *out, int M, int K, int m_tiles) {
 	const int k_blocks = K / TC_BK;
 	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);  // one thread per (row, 8 consecutive k)
@@ -69,20 +87,86 @@ __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bf
 #pragma unroll
 			for (int i = 0; i < 8; i++) x[i] = 0.0f;
 		}
-		__align__(16) __nv_bfloat16 hi[8], mid[8], lo[8];
-#pragma unroll
-		for (int i = 0; i < 8; i++) {
-			hi[i] = __float2bfloat16_rn(x[i]);
-			const float r1 = x[i] - __bfloat162float(hi[i]);  // exact
-			mid[i] = __float2bfloat16_rn(r1);
-			const float r2 = r1 - __bfloat162float(mid[i]);   // exact
-			lo[i] = __float2bfloat16_rn(r2);
+		tc_pack8(out, term_stride, k_blocks, row, k8, x);
+	}
+}
+
+// Residual + sandwich norms of one row, fused with the operand packing of the next GEMM:
+//   if t:  h += rmsnorm(t; w_post)            (reference modules.hpp: post-norm, then the residual add)
+//   if w_pre: pack( rmsnorm(h; w_pre) )       (the pre-norm of the following matmuls)
+// One CTA per row of the padded [m_tiles * 128] range (rows >= M are written as zeros). The sums run
+// over d = tid, tid + 256, ... exactly like rmsnorm_rows_kernel, so the values are the ones the
+// separate kernels produce. dim <= 2048, dim % 8 == 0.
+__global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
+                                                            __nv_bfloat16 *out, int M, int dim, int m_tiles) {
+	__shared__ float bred[8];
+	__shared__ float row_s[2048];
+	const int row = blockIdx.x, tid = threadIdx.x;
+	const int k_blocks = dim / TC_BK;
+	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
+	if (row >= M) {
+		if (w_pre) {
+			const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+			for (int k8 = tid; k8 < dim / 8; k8 += 256) tc_pack8(out, term_stride, k_blocks, row, k8, z);
 		}
-		const int mt = row / TC_BM, r = row % TC_BM, kb = (8 * k8) / TC_BK, kc = ((8 * k8) % TC_BK) / 8;
-		const size_t off = (size_t(mt) * k_blocks + kb) * (TC_TILE_BYTES / 2) + (r / 8) * 256 + kc * 64 + (r % 8) * 8;
-		*reinterpret_cast<uint4 *>(out + off) = *reinterpret_cast<const uint4 *>(hi);
-		*reinterpret_cast<uint4 *>(out + term_stride + off) = *reinterpret_cast<const uint4 *>(mid);
-		*reinterpret_cast<uint4 *>(out + 2 * term_stride + off) = *reinterpret_cast<const uint4 *>(lo);
+		return;
+	}
+	const size_t off = size_t(row) * dim;
+	if (t) {
+		float ss = 0.0f;
+		for (int d = tid; d < dim; d += 256) {
+			const float v = t[off + d];
+			ss = fmaf(v, v, ss);
+		}
+		ss = block_sum<8>(ss, bred);
+		const float r = inv_rms(ss, dim);
+		for (int d = tid; d < dim; d += 256) {
+			const float y = (t[off + d] * r) * (w_post[d] + 1.0f);
+			const float hn = h[off + d] + y;
+			h[off + d] = hn;
+			row_s[d] = hn;
+		}
+	} else {
+		for (int d = tid; d < dim; d += 256) row_s[d] = h[off + d];
+	}
+	if (!w_pre) return;
+	__syncthreads();
+	float ss = 0.0f;
+	for (int d = tid; d < dim; d += 256) {
+		const float v = row_s[d];
+		ss = fmaf(v, v, ss);
+	}
+	ss = block_sum<8>(ss, bred);
+	const float r = inv_rms(ss, dim);
+	for (int k8 = tid; k8 < dim / 8; k8 += 256) {
+		float x[8];
+#pragma unroll
+		for (int i = 0; i < 8; i++) x[i] = (row_s[8 * k8 + i] * r) * (w_pre[8 * k8 + i] + 1.0f);
+		tc_pack8(out, term_stride, k_blocks, row, k8, x);
+	}
+}
+
+// GeGLU fused with the packing of the down projection's operand: pack( lut(gate) * up ), rows >= M zero
+__global__ void __launch_bounds__(256) geglu_pack_kernel(const float *gate, const float *up, __nv_bfloat16 *out, int M, int K,
+                                                          int m_tiles, GeluLut lut) {
+	const int k_blocks = K / TC_BK;
+	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);
+	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
+	for (size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += size_t(gridDim.x) * blockDim.x) {
+		const int row = int(c / (K / 8)), k8 = int(c % (K / 8));
+		float x[8];
+		if (row < M) {
+			const float4 g0 = *reinterpret_cast<const float4 *>(gate + size_t(row) * K + 8 * k8);
+			const float4 g1 = *reinterpret_cast<const float4 *>(gate + size_t(row) * K + 8 * k8 + 4);
+			const float4 u0 = *reinterpret_cast<const float4 *>(up + size_t(row) * K + 8 * k8);
+			const float4 u1 = *reinterpret_cast<const float4 *>(up + size_t(row) * K + 8 * k8 + 4);
+			x[0] = lut(g0.x) * u0.x; x[1] = lut(g0.y) * u0.y; x[2] = lut(g0.z) * u0.z; x[3] = lut(g0.w) * u0.w;
+			x[4] = lut(g1.x) * u1.x; x[5] = lut(g1.y) * u1.y; x[6] = lut(g1.z) * u1.z; x[7] = lut(g1.w) * u1.w;
+		} else {
+#pragma unroll
+			for (int i = 0; i < 8; i++) x[i] = 0.0f;
+		}
+		tc_pack8(out, term_stride, k_blocks, row, k8, x);
 	}
 }
 
@@ -130,9 +214,15 @@ __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int *err
 
 struct GemmTcArgs {
 	const __nv_bfloat16 *apack;  // [3][m_tiles][k_blocks][8 KiB]
-	const float *scales;         // [N]
-	float *C;                    // [M] rows of ldc floats       (nsplit == 1: scaled result)
-	int ldc;                     // row stride of C (>= N; lets a GEMM write a column block of a wider row)
+	// Up to three weight matrices with the same K share one launch and one packed A (q|k|v, up|gate):
+	// group g owns the column tiles [tile_end[g-1], tile_end[g]) of the grid and columns col0[g].. of a
+	// partial-sum row (N = total columns of all groups).
+	int ngroups;
+	int tile_end[3];
+	int col0[3];
+	const float *scales[3];      // [N_g]
+	float *C[3];                 // [M] rows of ldc[g] floats    (nsplit == 1: scaled result)
+	int ldc[3];                  // row stride of C (>= N_g; lets a GEMM write a column block of a wider row)
 	float *partial;              // [nsplit][M][N] raw sums      (nsplit > 1: summed and scaled by a second kernel)
 	int M, N, K, m_tiles;
 	int nsplit;                  // K-splits = gridDim.z; K / 32 must be a multiple of it
@@ -141,7 +231,9 @@ struct GemmTcArgs {
 	int *err;
 };
 
-__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, GemmTcArgs a) {
+__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap0,
+                                                                 const __grid_constant__ CUtensorMap wmap1,
+                                                                 const __grid_constant__ CUtensorMap wmap2, GemmTcArgs a) {
 	extern __shared__ uint8_t tc_smem_raw[];
 	uint8_t *smem = reinterpret_cast<uint8_t *>((uintptr_t(tc_smem_raw) + 1023) & ~uintptr_t(1023));
 	__shared__ uint64_t full_bar[TC_STAGES];   // A tiles + W tile landed (transaction bytes)
@@ -154,7 +246,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 	__shared__ int s_last, s_cnt;
 
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-	const int n0 = blockIdx.x * TC_BN;
+	const int grp = (int(blockIdx.x) >= a.tile_end[0]) + (int(blockIdx.x) >= a.tile_end[1]);  // tile_end of unused groups = INT_MAX
+	const int n0 = (int(blockIdx.x) - (grp ? a.tile_end[grp - 1] : 0)) * TC_BN;  // column inside the group's matrix
+	const int pcol = a.col0[grp] + n0;                                              // column inside a partial-sum row
+	const CUtensorMap *wmap = grp == 0 ? &wmap0 : (grp == 1 ? &wmap1 : &wmap2);
+	float *const Cg = a.C[grp];
+	const float *const scg = a.scales[grp];
+	const int ldcg = a.ldc[grp];
 	const int mt0 = blockIdx.y * TC_MT;
 	const int nmt = min(TC_MT, a.m_tiles - mt0);  // row tiles this CTA really has
 	const int k_blocks_all = a.K / TC_BK;
@@ -205,7 +303,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 						                     (size_t(mtg) * k_blocks_all + kb_first + kb) * TC_TILE_BYTES;
 						bulk_load(stage_a(s, term, mt), src, TC_TILE_BYTES, &full_bar[s]);
 					}
-				tma_load_2d(stage_w(s), &wmap, n0, (kb_first + kb) * TC_BK, &full_bar[s], pol);
+				tma_load_2d(stage_w(s), wmap, n0, (kb_first + kb) * TC_BK, &full_bar[s], pol);
 				s_issued = kb + 1;
 			}
 		}
@@ -286,8 +384,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 					if ((mt0 + mt) < a.m_tiles && row < a.M) {
 						if (a.nsplit == 1) {
-							float *dst = a.C + size_t(row) * a.ldc + n0 + c * 32;
-							const float *sc = a.scales + n0 + c * 32;
+							float *dst = Cg + size_t(row) * ldcg + n0 + c * 32;
+							const float *sc = scg + n0 + c * 32;
 #pragma unroll
 							for (int i = 0; i < 32; i += 4) {
 								float4 o;
@@ -298,7 +396,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 								*reinterpret_cast<float4 *>(dst + i) = o;
 							}
 						} else {
-							float *dst = a.partial + (size_t(blockIdx.z) * a.M + row) * a.N + n0 + c * 32;
+							float *dst = a.partial + (size_t(blockIdx.z) * a.M + row) * a.N + pcol + c * 32;
 #pragma unroll
 							for (int i = 0; i < 32; i += 4)
 								*reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
@@ -341,7 +439,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 								for (int q = 0; q < 4; q++) {
 									v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
 									if (s0 + q < a.nsplit)
-										v[q] = __ldcg(reinterpret_cast<const float4 *>(a.partial + (size_t(s0 + q) * a.M + row) * a.N + n0) + c4);
+										v[q] = __ldcg(reinterpret_cast<const float4 *>(a.partial + (size_t(s0 + q) * a.M + row) * a.N + pcol) + c4);
 								}
 #pragma unroll
 								for (int q = 0; q < 4; q++) {
@@ -351,8 +449,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 									sum.w += v[q].w;
 								}
 							}
-							const float4 sc = *reinterpret_cast<const float4 *>(a.scales + n0 + 4 * c4);
-							*reinterpret_cast<float4 *>(a.C + size_t(row) * a.ldc + n0 + 4 * c4) =
+							const float4 sc = *reinterpret_cast<const float4 *>(scg + n0 + 4 * c4);
+							*reinterpret_cast<float4 *>(Cg + size_t(row) * ldcg + n0 + 4 * c4) =
 							    make_float4(sum.x * sc.x, sum.y * sc.y, sum.z * sc.z, sum.w * sc.w);
 						}
 					}

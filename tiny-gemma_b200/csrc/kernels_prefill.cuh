@@ -125,6 +125,26 @@ __global__ void qgemm_splitk_reduce_kernel(float *C, const float *partial, const
 	C[m * ldc + n] = s * scales[n];
 }
 
+// the same for a launch over up to three matrices (columns col0[g] .. of a partial-sum row belong to group g)
+struct ReduceGroups {
+	int ngroups;
+	int col0[4];  // col0[ngroups] = total columns
+	const float *scales[3];
+	float *C[3];
+	int ldc[3];
+};
+__global__ void qgemm_splitk_reduce_groups_kernel(ReduceGroups g, const float *partial, int M, int N, int nsplit) {
+	size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= size_t(M) * N) return;
+	float s = 0.0f;
+	for (int sp = 0; sp < nsplit; sp++) s += partial[size_t(sp) * M * N + i];
+	const size_t m = i / N;
+	const int n = int(i % N);
+	const int gi = (n >= g.col0[1] && g.ngroups > 1) + (n >= g.col0[2] && g.ngroups > 2);
+	const int nl = n - g.col0[gi];
+	g.C[gi][m * g.ldc[gi] + nl] = s * g.scales[gi][nl];
+}
+
 // out[b, :] = table lookup per element: gate = lut(gate) * up over [rows][n] with row strides
 // (the batched decode step keeps up and gate in separate buffers)
 

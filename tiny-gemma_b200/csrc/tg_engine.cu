@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <climits>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -1063,41 +1064,76 @@ int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStre
 	return check_launch("split_pack");
 }
 
-int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream_t st, int ldc = 0, int max_split = 1 << 30) {
-	if (ldc <= 0) ldc = w.N;
+// One launch for up to three weight matrices with the same K that multiply the same packed A
+// (q|k|v, up|gate): more column tiles per launch, one split-K reduce instead of three.
+int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const int *ldcs, int M, const TcScratch &sc,
+                         cudaStream_t st, int max_split = 1 << 30) {
 	static bool configured = false;
 	const size_t smem = size_t(TC_STAGES) * TC_STAGE_BYTES + 1024;
 	if (!configured) {
 		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
 		configured = true;
 	}
-	CUtensorMap wmap;
-	TG_TRY(make_tmap(&wmap, w.q, w.K, w.N, TC_BN, TC_BK));
+	CUtensorMap wmap[3];
 	GemmTcArgs a{};
+	ReduceGroups rg{};
+	int ntot = 0, tiles = 0;
+	const int K = ws[0]->K;
+	for (int g = 0; g < 3; g++) {
+		const int gg = std::min(g, ng - 1);  // unused slots repeat the last matrix (never selected)
+		if (ws[gg]->K != K) return fail(TG_ESHAPE, "grouped GEMM: the matrices must share K");
+		TG_TRY(make_tmap(&wmap[g], ws[gg]->q, K, ws[gg]->N, TC_BN, TC_BK));
+		if (g < ng) {
+			a.col0[g] = ntot;
+			a.scales[g] = ws[g]->s;
+			a.C[g] = Cs[g];
+			a.ldc[g] = (ldcs && ldcs[g] > 0) ? ldcs[g] : ws[g]->N;
+			ntot += ws[g]->N;
+			tiles += ws[g]->N / TC_BN;
+			a.tile_end[g] = tiles;
+			rg.col0[g] = a.col0[g];
+			rg.scales[g] = a.scales[g];
+			rg.C[g] = a.C[g];
+			rg.ldc[g] = a.ldc[g];
+		} else {
+			a.col0[g] = ntot;
+			a.tile_end[g] = INT_MAX;
+			a.scales[g] = a.scales[ng - 1];
+			a.C[g] = a.C[ng - 1];
+			a.ldc[g] = a.ldc[ng - 1];
+		}
+	}
+	rg.ngroups = ng;
+	rg.col0[ng] = ntot;
+	for (int g = ng + 1; g < 4; g++) rg.col0[g] = INT_MAX;
+	a.ngroups = ng;
 	a.apack = sc.apack;
-	a.scales = w.s;
-	a.C = C;
 	a.M = M;
-	a.N = w.N;
-	a.K = w.K;
+	a.N = ntot;
+	a.K = K;
 	a.m_tiles = (M + TC_BM - 1) / TC_BM;
-	a.nsplit = tc_pick_split(M, w.K, w.N, sc.partial_floats, std::min(max_split, env_int("TG_GEMM_MAX_SPLIT", sc.max_split)));
-	a.ldc = ldc;
+	a.nsplit = tc_pick_split(M, K, ntot, sc.partial_floats, std::min(max_split, env_int("TG_GEMM_MAX_SPLIT", sc.max_split)));
 	a.partial = sc.partial;
 	a.err = sc.err;
-	dim3 grid(w.N / TC_BN, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
+	dim3 grid(tiles, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
 	const bool fused = sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
 	a.tickets = fused ? sc.tickets : nullptr;
-	qgemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(wmap, a);
+	qgemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(wmap[0], wmap[1], wmap[2], a);
 	count_launch();
 	TG_TRY(check_launch("qgemm_tc"));
 	if (a.nsplit > 1 && !fused) {
-		const size_t n = size_t(M) * w.N;
-		qgemm_splitk_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(C, sc.partial, w.s, M, w.N, a.nsplit, ldc);
+		const size_t n = size_t(M) * ntot;
+		qgemm_splitk_reduce_groups_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(rg, sc.partial, M, ntot, a.nsplit);
 		count_launch();
 		TG_TRY(check_launch("qgemm_reduce"));
 	}
 	return TG_OK;
+}
+int launch_gemm_tc(float *C, const QW &w, int M, const TcScratch &sc, cudaStream_t st, int ldc = 0, int max_split = 1 << 30) {
+	float *Cs[1] = {C};
+	const QW *ws[1] = {&w};
+	const int ldcs[1] = {ldc};
+	return launch_gemm_tc_group(1, Cs, ws, ldcs, M, sc, st, max_split);
 }
 
 // ------------------------------------------------------------- batched decode step
@@ -1143,14 +1179,20 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 	ea.sqrtD = float(std::sqrt(double(D)));
 	embed_decode_kernel<<<B, 256, 0, st>>>(ea);
 	count_launch();
+	const int m_tiles = (B + TC_BM - 1) / TC_BM;
+	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre) {
+		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles);
+		count_launch();
+	};
+	resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre);
 	for (int l = 0; l < c.n_layers; l++) {
 		const LayerW &w = m->layers[l];
-		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->bx, h, w.attn_pre, nullptr, D);
-		count_launch();
-		TG_TRY(pack_activations(s->bx, B, D, s->btc, st));
-		TG_TRY(launch_gemm_tc(s->qkv, w.Q, B, s->btc, st, NQ));
-		TG_TRY(launch_gemm_tc(s->qkv + qd, w.K, B, s->btc, st, NQ));
-		TG_TRY(launch_gemm_tc(s->qkv + qd + kd, w.V, B, s->btc, st, NQ));
+		{
+			float *Cs[3] = {s->qkv, s->qkv + qd, s->qkv + qd + kd};
+			const QW *ws[3] = {&w.Q, &w.K, &w.V};
+			const int ldcs[3] = {NQ, NQ, NQ};
+			TG_TRY(launch_gemm_tc_group(3, Cs, ws, ldcs, B, s->btc, st));
+		}
 		{
 			AttnArgs a{};
 			a.qkv = s->qkv;
@@ -1175,20 +1217,16 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 		}
 		TG_TRY(pack_activations(s->attn_out, B, qd, s->btc, st));
 		TG_TRY(launch_gemm_tc(s->t, w.O, B, s->btc, st));
-		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(h, s->t, w.attn_post, h, D);
+		resnorm_pack(s->t, w.attn_post, w.mlp_pre);
+		{
+			float *Cs[2] = {s->bup, s->act};
+			const QW *ws[2] = {&w.U, &w.G};
+			TG_TRY(launch_gemm_tc_group(2, Cs, ws, nullptr, B, s->btc, st));
+		}
+		geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(s->act, s->bup, s->btc.apack, B, I, m_tiles, lut);
 		count_launch();
-		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->bx, h, w.mlp_pre, nullptr, D);
-		count_launch();
-		TG_TRY(pack_activations(s->bx, B, D, s->btc, st));
-		TG_TRY(launch_gemm_tc(s->bup, w.U, B, s->btc, st));
-		TG_TRY(launch_gemm_tc(s->act, w.G, B, s->btc, st));
-		const size_t n = size_t(B) * I;
-		geglu_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(s->act, s->bup, n, lut);
-		count_launch();
-		TG_TRY(pack_activations(s->act, B, I, s->btc, st));
 		TG_TRY(launch_gemm_tc(s->t, w.Dn, B, s->btc, st));
-		rmsnorm_rows_kernel<<<B, 256, 0, st>>>(h, s->t, w.mlp_post, h, D);
-		count_launch();
+		resnorm_pack(s->t, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr);
 		TG_TRY(check_launch("batched layer"));
 	}
 	rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->xnorm, h, m->final_norm, nullptr, D);
@@ -1269,14 +1307,31 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 	                                        float(std::sqrt(double(D))), s->err_flag);
 	count_launch();
 	TG_TRY(check_launch("embed_prefill"));
+	const int m_tiles = (S + TC_BM - 1) / TC_BM;
+	// Tensor-core path: the norms are fused with the operand packing of the GEMM that follows them
+	// (resnorm_pack_kernel, geglu_pack_kernel), so a layer is 7 GEMMs (+ their split-K reduces) and 6 other launches.
+	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre) {
+		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, tc.apack, S, D, m_tiles);
+		count_launch();
+	};
+	if (use_tc) {
+		if (tc_pack_bytes(S, std::max(I, std::max(D, qd))) > tc.apack_bytes) return fail(TG_ENOMEM, "tensor-core GEMM scratch too small");
+		resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre);
+	}
 	for (int l = 0; l < c.n_layers; l++) {
 		const LayerW &w = m->layers[l];
-		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.attn_pre, nullptr, D);
-		count_launch();
-		TG_TRY(gemm(q, xn, w.Q, true));
-		TG_TRY(gemm(k, xn, w.K, false));
-		TG_TRY(gemm(v, xn, w.V, false));
 		const int slots = s->slots[l];
+		if (use_tc) {
+			float *Cs[3] = {q, k, v};
+			const QW *ws[3] = {&w.Q, &w.K, &w.V};
+			TG_TRY(launch_gemm_tc_group(3, Cs, ws, nullptr, S, tc, st));
+		} else {
+			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.attn_pre, nullptr, D);
+			count_launch();
+			TG_TRY(gemm(q, xn, w.Q, true));
+			TG_TRY(gemm(k, xn, w.K, false));
+			TG_TRY(gemm(v, xn, w.V, false));
+		}
 		qk_norm_rope_prefill_kernel<<<S, 192, 0, st>>>(q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
 		                                               m->rope[w.is_local ? 1 : 0][1],
 		                                               s->kcache[l] + size_t(b) * slots * AT_HD,
@@ -1286,18 +1341,31 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		count_launch();
 		TG_TRY(check_launch("attn_prefill"));
 		TG_TRY(gemm(tt, ao, w.O, true));
-		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.attn_post, h, D);
-		count_launch();
-		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.mlp_pre, nullptr, D);
-		count_launch();
-		TG_TRY(gemm(up, xn, w.U, true));
-		TG_TRY(gemm(gate, xn, w.G, false));
-		size_t n = size_t(S) * I;
-		geglu_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(gate, up, n, lut);
-		count_launch();
-		TG_TRY(gemm(tt, gate, w.Dn, true));
-		rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.mlp_post, h, D);
-		count_launch();
+		if (use_tc) {
+			resnorm_pack(tt, w.attn_post, w.mlp_pre);
+			{
+				float *Cs[2] = {up, gate};
+				const QW *ws[2] = {&w.U, &w.G};
+				TG_TRY(launch_gemm_tc_group(2, Cs, ws, nullptr, S, tc, st));
+			}
+			geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(gate, up, tc.apack, S, I, m_tiles, lut);
+			count_launch();
+			TG_TRY(launch_gemm_tc(tt, w.Dn, S, tc, st));
+			resnorm_pack(tt, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr);
+		} else {
+			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.attn_post, h, D);
+			count_launch();
+			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.mlp_pre, nullptr, D);
+			count_launch();
+			TG_TRY(gemm(up, xn, w.U, true));
+			TG_TRY(gemm(gate, xn, w.G, false));
+			size_t n = size_t(S) * I;
+			geglu_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(gate, up, n, lut);
+			count_launch();
+			TG_TRY(gemm(tt, gate, w.Dn, true));
+			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.mlp_post, h, D);
+			count_launch();
+		}
 		TG_TRY(check_launch("prefill layer"));
 	}
 	// lm_head on the last position (modules.hpp:232-240)
