@@ -97,8 +97,12 @@ __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bf
 // One CTA per row of the padded [m_tiles * 128] range (rows >= M are written as zeros). The sums run
 // over d = tid, tid + 256, ... exactly like rmsnorm_rows_kernel, so the values are the ones the
 // separate kernels produce. dim <= 2048, dim % 8 == 0.
+// The branch output t is either a finished [M][dim] matrix (nsplit == 0) or the raw K-split partial
+// sums of the GEMM that produced it: t[d] = tscale[d] * sum_sp tpart[(sp * M + row) * ldp + d], splits
+// added in ascending order as the reduce kernel does.
 __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
-                                                            __nv_bfloat16 *out, int M, int dim, int m_tiles) {
+                                                            __nv_bfloat16 *out, int M, int dim, int m_tiles, int nsplit,
+                                                            int ldp, const float *tscale) {
 	__shared__ float bred[8];
 	__shared__ float row_s[2048];
 	const int row = blockIdx.x, tid = threadIdx.x;
@@ -113,15 +117,24 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 	}
 	const size_t off = size_t(row) * dim;
 	if (t) {
+		__shared__ float t_s[2048];
 		float ss = 0.0f;
 		for (int d = tid; d < dim; d += 256) {
-			const float v = t[off + d];
+			float v;
+			if (nsplit > 0) {
+				v = 0.0f;
+				for (int sp = 0; sp < nsplit; sp++) v += t[(size_t(sp) * M + row) * ldp + d];
+				v *= tscale[d];
+			} else {
+				v = t[off + d];
+			}
+			t_s[d] = v;
 			ss = fmaf(v, v, ss);
 		}
 		ss = block_sum<8>(ss, bred);
 		const float r = inv_rms(ss, dim);
 		for (int d = tid; d < dim; d += 256) {
-			const float y = (t[off + d] * r) * (w_post[d] + 1.0f);
+			const float y = (t_s[d] * r) * (w_post[d] + 1.0f);
 			const float hn = h[off + d] + y;
 			h[off + d] = hn;
 			row_s[d] = hn;
@@ -147,15 +160,34 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 }
 
 // GeGLU fused with the packing of the down projection's operand: pack( lut(gate) * up ), rows >= M zero
+// With nsplit > 0, `up` points at the raw partial sums of the grouped up|gate GEMM (rows of 2K: up
+// columns, then gate columns) and su / sg are the column scales; otherwise gate / up are finished.
 __global__ void __launch_bounds__(256) geglu_pack_kernel(const float *gate, const float *up, __nv_bfloat16 *out, int M, int K,
-                                                          int m_tiles, GeluLut lut) {
+                                                          int m_tiles, GeluLut lut, int nsplit, const float *su, const float *sg) {
 	const int k_blocks = K / TC_BK;
 	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);
 	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
 	for (size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += size_t(gridDim.x) * blockDim.x) {
 		const int row = int(c / (K / 8)), k8 = int(c % (K / 8));
 		float x[8];
-		if (row < M) {
+		if (row < M && nsplit > 0) {
+			float4 u0 = make_float4(0.f, 0.f, 0.f, 0.f), u1 = u0, g0 = u0, g1 = u0;
+			for (int sp = 0; sp < nsplit; sp++) {
+				const float *pr = up + (size_t(sp) * M + row) * (2 * size_t(K)) + 8 * k8;
+				const float4 a0 = *reinterpret_cast<const float4 *>(pr), a1 = *reinterpret_cast<const float4 *>(pr + 4);
+				const float4 b0 = *reinterpret_cast<const float4 *>(pr + K), b1 = *reinterpret_cast<const float4 *>(pr + K + 4);
+				u0.x += a0.x; u0.y += a0.y; u0.z += a0.z; u0.w += a0.w;
+				u1.x += a1.x; u1.y += a1.y; u1.z += a1.z; u1.w += a1.w;
+				g0.x += b0.x; g0.y += b0.y; g0.z += b0.z; g0.w += b0.w;
+				g1.x += b1.x; g1.y += b1.y; g1.z += b1.z; g1.w += b1.w;
+			}
+			const float4 su0 = *reinterpret_cast<const float4 *>(su + 8 * k8), su1 = *reinterpret_cast<const float4 *>(su + 8 * k8 + 4);
+			const float4 sg0 = *reinterpret_cast<const float4 *>(sg + 8 * k8), sg1 = *reinterpret_cast<const float4 *>(sg + 8 * k8 + 4);
+			x[0] = lut(g0.x * sg0.x) * (u0.x * su0.x); x[1] = lut(g0.y * sg0.y) * (u0.y * su0.y);
+			x[2] = lut(g0.z * sg0.z) * (u0.z * su0.z); x[3] = lut(g0.w * sg0.w) * (u0.w * su0.w);
+			x[4] = lut(g1.x * sg1.x) * (u1.x * su1.x); x[5] = lut(g1.y * sg1.y) * (u1.y * su1.y);
+			x[6] = lut(g1.z * sg1.z) * (u1.z * su1.z); x[7] = lut(g1.w * sg1.w) * (u1.w * su1.w);
+		} else if (row < M) {
 			const float4 g0 = *reinterpret_cast<const float4 *>(gate + size_t(row) * K + 8 * k8);
 			const float4 g1 = *reinterpret_cast<const float4 *>(gate + size_t(row) * K + 8 * k8 + 4);
 			const float4 u0 = *reinterpret_cast<const float4 *>(up + size_t(row) * K + 8 * k8);
@@ -226,6 +258,8 @@ struct GemmTcArgs {
 	float *partial;              // [nsplit][M][N] raw sums      (nsplit > 1: summed and scaled by a second kernel)
 	int M, N, K, m_tiles;
 	int nsplit;                  // K-splits = gridDim.z; K / 32 must be a multiple of it
+	int raw;                     // 1: always write raw partial sums (even unsplit); the consumer kernel adds the splits
+	                             // and applies the column scales itself, so no reduce kernel runs
 	unsigned *tickets;           // [gridDim.y * gridDim.x] zeros, or null. Non-null with nsplit > 1: the CTA that finishes
 	                             // a tile last adds the partial sums in split order, scales and writes C itself
 	int *err;
@@ -383,7 +417,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 					    : "memory");
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 					if ((mt0 + mt) < a.m_tiles && row < a.M) {
-						if (a.nsplit == 1) {
+						if (a.nsplit == 1 && !a.raw) {
 							float *dst = Cg + size_t(row) * ldcg + n0 + c * 32;
 							const float *sc = scg + n0 + c * 32;
 #pragma unroll
@@ -405,7 +439,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 					}
 				}
 			}
-			if (a.nsplit > 1 && a.tickets) {
+			if (a.nsplit > 1 && a.tickets && !a.raw) {
 				// in-kernel split-K reduction: the CTA that arrives last at this tile's ticket sums the
 				// partial tiles of all splits in split order (a fixed order: results are reproducible)
 				// (the four epilogue warps meet through a shared counter and a bounded spin, never a

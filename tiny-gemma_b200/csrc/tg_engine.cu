@@ -1066,8 +1066,10 @@ int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStre
 
 // One launch for up to three weight matrices with the same K that multiply the same packed A
 // (q|k|v, up|gate): more column tiles per launch, one split-K reduce instead of three.
+// raw_nsplit != null: the kernel leaves raw partial sums in sc.partial ([nsplit][M][sum of N]) for a consumer
+// kernel that adds the splits and scales itself; *raw_nsplit receives the split count, no reduce is launched.
 int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const int *ldcs, int M, const TcScratch &sc,
-                         cudaStream_t st, int max_split = 1 << 30) {
+                         cudaStream_t st, int max_split = 1 << 30, int *raw_nsplit = nullptr) {
 	static bool configured = false;
 	const size_t smem = size_t(TC_STAGES) * TC_STAGE_BYTES + 1024;
 	if (!configured) {
@@ -1116,12 +1118,17 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 	a.partial = sc.partial;
 	a.err = sc.err;
 	dim3 grid(tiles, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
-	const bool fused = sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
+	const bool fused = !raw_nsplit && sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
 	a.tickets = fused ? sc.tickets : nullptr;
+	a.raw = raw_nsplit ? 1 : 0;
+	if (raw_nsplit) {
+		if (size_t(a.nsplit) * M * ntot > sc.partial_floats) return fail(TG_ENOMEM, "tensor-core GEMM partial-sum scratch too small");
+		*raw_nsplit = a.nsplit;
+	}
 	qgemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(wmap[0], wmap[1], wmap[2], a);
 	count_launch();
 	TG_TRY(check_launch("qgemm_tc"));
-	if (a.nsplit > 1 && !fused) {
+	if (a.nsplit > 1 && !fused && !raw_nsplit) {
 		const size_t n = size_t(M) * ntot;
 		qgemm_splitk_reduce_groups_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(rg, sc.partial, M, ntot, a.nsplit);
 		count_launch();
@@ -1180,11 +1187,16 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 	embed_decode_kernel<<<B, 256, 0, st>>>(ea);
 	count_launch();
 	const int m_tiles = (B + TC_BM - 1) / TC_BM;
-	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre) {
-		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles);
+	// t: finished matrix (nsplit 0) or the raw partial sums of the GEMM before (nsplit >= 1, column scales tscale)
+	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre, int nsplit, const float *tscale) {
+		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles, nsplit, D, tscale);
 		count_launch();
 	};
-	resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre);
+	auto gemm_raw = [&](int ng, const QW *const *ws, int *ns) -> int {
+		float *Cs[3] = {nullptr, nullptr, nullptr};
+		return launch_gemm_tc_group(ng, Cs, ws, nullptr, B, s->btc, st, 1 << 30, ns);
+	};
+	resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre, 0, nullptr);
 	for (int l = 0; l < c.n_layers; l++) {
 		const LayerW &w = m->layers[l];
 		{
@@ -1216,17 +1228,23 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 			TG_TRY(check_launch("attn_decode"));
 		}
 		TG_TRY(pack_activations(s->attn_out, B, qd, s->btc, st));
-		TG_TRY(launch_gemm_tc(s->t, w.O, B, s->btc, st));
-		resnorm_pack(s->t, w.attn_post, w.mlp_pre);
+		int ns = 0;
 		{
-			float *Cs[2] = {s->bup, s->act};
-			const QW *ws[2] = {&w.U, &w.G};
-			TG_TRY(launch_gemm_tc_group(2, Cs, ws, nullptr, B, s->btc, st));
+			const QW *ws[1] = {&w.O};
+			TG_TRY(gemm_raw(1, ws, &ns));
 		}
-		geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(s->act, s->bup, s->btc.apack, B, I, m_tiles, lut);
+		resnorm_pack(s->btc.partial, w.attn_post, w.mlp_pre, ns, w.O.s);
+		{
+			const QW *ws[2] = {&w.U, &w.G};
+			TG_TRY(gemm_raw(2, ws, &ns));
+		}
+		geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(nullptr, s->btc.partial, s->btc.apack, B, I, m_tiles, lut, ns, w.U.s, w.G.s);
 		count_launch();
-		TG_TRY(launch_gemm_tc(s->t, w.Dn, B, s->btc, st));
-		resnorm_pack(s->t, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr);
+		{
+			const QW *ws[1] = {&w.Dn};
+			TG_TRY(gemm_raw(1, ws, &ns));
+		}
+		resnorm_pack(s->btc.partial, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr, ns, w.Dn.s);
 		TG_TRY(check_launch("batched layer"));
 	}
 	rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->xnorm, h, m->final_norm, nullptr, D);
@@ -1310,13 +1328,17 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 	const int m_tiles = (S + TC_BM - 1) / TC_BM;
 	// Tensor-core path: the norms are fused with the operand packing of the GEMM that follows them
 	// (resnorm_pack_kernel, geglu_pack_kernel), so a layer is 7 GEMMs (+ their split-K reduces) and 6 other launches.
-	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre) {
-		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, tc.apack, S, D, m_tiles);
+	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre, int nsplit, const float *tscale) {
+		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, tc.apack, S, D, m_tiles, nsplit, D, tscale);
 		count_launch();
+	};
+	auto gemm_raw = [&](int ng, const QW *const *ws, int *ns) -> int {
+		float *Cs[3] = {nullptr, nullptr, nullptr};
+		return launch_gemm_tc_group(ng, Cs, ws, nullptr, S, tc, st, 1 << 30, ns);
 	};
 	if (use_tc) {
 		if (tc_pack_bytes(S, std::max(I, std::max(D, qd))) > tc.apack_bytes) return fail(TG_ENOMEM, "tensor-core GEMM scratch too small");
-		resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre);
+		resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre, 0, nullptr);
 	}
 	for (int l = 0; l < c.n_layers; l++) {
 		const LayerW &w = m->layers[l];
@@ -1340,19 +1362,28 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
 		TG_TRY(check_launch("attn_prefill"));
-		TG_TRY(gemm(tt, ao, w.O, true));
 		if (use_tc) {
-			resnorm_pack(tt, w.attn_post, w.mlp_pre);
+			// the O, up|gate and down GEMMs leave raw K-split partial sums; the kernel that consumes them adds the splits
+			int ns = 0;
+			TG_TRY(pack_activations(ao, S, qd, tc, st));
 			{
-				float *Cs[2] = {up, gate};
-				const QW *ws[2] = {&w.U, &w.G};
-				TG_TRY(launch_gemm_tc_group(2, Cs, ws, nullptr, S, tc, st));
+				const QW *ws[1] = {&w.O};
+				TG_TRY(gemm_raw(1, ws, &ns));
 			}
-			geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(gate, up, tc.apack, S, I, m_tiles, lut);
+			resnorm_pack(tc.partial, w.attn_post, w.mlp_pre, ns, w.O.s);
+			{
+				const QW *ws[2] = {&w.U, &w.G};
+				TG_TRY(gemm_raw(2, ws, &ns));
+			}
+			geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(nullptr, tc.partial, tc.apack, S, I, m_tiles, lut, ns, w.U.s, w.G.s);
 			count_launch();
-			TG_TRY(launch_gemm_tc(tt, w.Dn, S, tc, st));
-			resnorm_pack(tt, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr);
+			{
+				const QW *ws[1] = {&w.Dn};
+				TG_TRY(gemm_raw(1, ws, &ns));
+			}
+			resnorm_pack(tc.partial, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr, ns, w.Dn.s);
 		} else {
+			TG_TRY(gemm(tt, ao, w.O, true));
 			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(h, tt, w.attn_post, h, D);
 			count_launch();
 			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.mlp_pre, nullptr, D);
