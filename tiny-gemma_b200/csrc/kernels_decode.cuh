@@ -397,6 +397,10 @@ constexpr int AT_NH = 4;
 
 struct AttnArgs {
 	const float *qkv;   // [B][1536] = q(4x256) | k(256) | v(256)
+	// qkv_nsplit > 0: qkv instead holds the raw K-split partial sums of the grouped q|k|v GEMM,
+	// [qkv_nsplit][B][1536], and sq / sk / sv are the column scales (splits are added in ascending order)
+	int qkv_nsplit, qkv_B;
+	const float *sq, *sk, *sv;
 	const float *rmsq;  // [256]
 	const float *rmsk;  // [256]
 	const float *cosT;  // [n_pos][256]
@@ -467,6 +471,18 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
 		valid = pos + 1;
 	}
 	const float *row = a.qkv + size_t(b) * (AT_NH * AT_HD + 2 * AT_HD);
+	if (a.qkv_nsplit > 0) {
+		__shared__ float rowbuf[AT_NH * AT_HD + 2 * AT_HD];
+		constexpr int NQ = AT_NH * AT_HD + 2 * AT_HD;
+		for (int n = tid; n < NQ; n += AT_THREADS) {
+			float acc = 0.0f;
+			for (int sp = 0; sp < a.qkv_nsplit; sp++) acc += a.qkv[(size_t(sp) * a.qkv_B + b) * NQ + n];
+			const float sc = n < AT_NH * AT_HD ? a.sq[n] : (n < AT_NH * AT_HD + AT_HD ? a.sk[n - AT_NH * AT_HD] : a.sv[n - AT_NH * AT_HD - AT_HD]);
+			rowbuf[n] = acc * sc;
+		}
+		__syncthreads();
+		row = rowbuf;
+	}
 	const float *cosr = a.cosT + size_t(pos) * AT_HD, *sinr = a.sinT + size_t(pos) * AT_HD;
 	if (warp < AT_NH) {
 		// the reference scales q by 1/sqrt(256) = 2^-4 before the dot products (ops.hpp:262,283)

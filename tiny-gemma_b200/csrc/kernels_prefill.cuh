@@ -158,21 +158,33 @@ __global__ void geglu_kernel(float *gate, const float *up, size_t n, GeluLut lut
 // q [S][4*256] and k [S][256], and KVCache::update_prefill (reference
 // decode.hpp:72-105): the last min(S, slots) prompt positions go to cache
 // slots 0.. in order. One CTA (5 warps + 1) per prompt position.
-__global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, float *k, const float *v, const float *rmsq,
+// With nsplit > 0 the projections arrive as the raw K-split partial sums of the grouped q|k|v GEMM
+// (part[(sp * S + s) * 1536 + n], columns q | k | v) with the column scales sq / sk / sv; the splits are
+// added in ascending order and scaled here, and v is written out as well.
+__global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, float *k, float *v, const float *rmsq,
                                                                     const float *rmsk, const float *cosT,
                                                                     const float *sinT, float *kcache, float *vcache,
-                                                                    int S, int slots) {
+                                                                    int S, int slots, const float *part, int nsplit,
+                                                                    const float *sq, const float *sk, const float *sv) {
 	const int s = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const float *cosr = cosT + size_t(s) * 256, *sinr = sinT + size_t(s) * 256;
 	const int start = (S >= slots) ? (S - slots) : 0;
 	const int c = s - start;  // cache slot, if >= 0
-	auto norm_rope = [&](float *x, const float *w) {
+	// raw element n of this position's q|k|v row (n = column in the concatenated 1536), scaled by scale[ns]
+	auto raw = [&](int n, const float *scale, int ns) -> float {
+		float a = 0.0f;
+		for (int sp = 0; sp < nsplit; sp++) a += part[(size_t(sp) * S + s) * 1536 + n];
+		return a * scale[ns];
+	};
+	// x: the head's 256 floats (finished projection if nsplit == 0; always the destination)
+	auto norm_rope = [&](float *x, const float *w, int n0, const float *scale, int ns0) {
 		float lo[4], hi[4];
 		float ss = 0.0f;
 #pragma unroll
 		for (int i = 0; i < 4; i++) {
-			lo[i] = x[4 * lane + i];
-			hi[i] = x[128 + 4 * lane + i];
+			const int d = 4 * lane + i;
+			lo[i] = nsplit > 0 ? raw(n0 + d, scale, ns0 + d) : x[d];
+			hi[i] = nsplit > 0 ? raw(n0 + 128 + d, scale, ns0 + 128 + d) : x[128 + d];
 			ss = fmaf(lo[i], lo[i], ss);
 			ss = fmaf(hi[i], hi[i], ss);
 		}
@@ -188,16 +200,24 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
 		}
 	};
 	if (warp < 4) {
-		norm_rope(q + size_t(s) * 1024 + warp * 256, rmsq);
+		norm_rope(q + size_t(s) * 1024 + warp * 256, rmsq, warp * 256, sq, warp * 256);
 	} else if (warp == 4) {
 		float *kr = k + size_t(s) * 256;
-		norm_rope(kr, rmsk);
+		norm_rope(kr, rmsk, 1024, sk, 0);
 		__syncwarp();
 		if (c >= 0)
 			for (int d = lane; d < 256; d += 32) kcache[size_t(c) * 256 + d] = kr[d];
 	} else {
-		if (c >= 0)
-			for (int d = lane; d < 256; d += 32) vcache[size_t(c) * 256 + d] = v[size_t(s) * 256 + d];
+		for (int d = lane; d < 256; d += 32) {
+			float val;
+			if (nsplit > 0) {
+				val = raw(1280 + d, sv, d);
+				v[size_t(s) * 256 + d] = val;
+			} else {
+				val = v[size_t(s) * 256 + d];
+			}
+			if (c >= 0) vcache[size_t(c) * 256 + d] = val;
+		}
 	}
 }
 

@@ -1169,7 +1169,7 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 	tg_model *m = s->m;
 	const tg_config &c = m->cfg;
 	const int B = s->B, D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
-	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim, NQ = qd + 2 * kd;
+	const int qd = c.n_head * c.head_dim;
 	cudaStream_t st = s->stream;
 	const GeluLut lut = make_lut(m);
 	float *h = s->h[0];
@@ -1199,15 +1199,19 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 	resnorm_pack(nullptr, nullptr, m->layers[0].attn_pre, 0, nullptr);
 	for (int l = 0; l < c.n_layers; l++) {
 		const LayerW &w = m->layers[l];
+		int ns_qkv = 0;
 		{
-			float *Cs[3] = {s->qkv, s->qkv + qd, s->qkv + qd + kd};
 			const QW *ws[3] = {&w.Q, &w.K, &w.V};
-			const int ldcs[3] = {NQ, NQ, NQ};
-			TG_TRY(launch_gemm_tc_group(3, Cs, ws, ldcs, B, s->btc, st));
+			TG_TRY(gemm_raw(3, ws, &ns_qkv));  // raw partial sums: the attention kernel adds the splits and scales
 		}
 		{
 			AttnArgs a{};
-			a.qkv = s->qkv;
+			a.qkv = s->btc.partial;
+			a.qkv_nsplit = ns_qkv;
+			a.qkv_B = B;
+			a.sq = w.Q.s;
+			a.sk = w.K.s;
+			a.sv = w.V.s;
 			a.rmsq = w.rmsq;
 			a.rmsk = w.rmsk;
 			a.cosT = m->rope[w.is_local ? 1 : 0][0];
@@ -1343,10 +1347,10 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 	for (int l = 0; l < c.n_layers; l++) {
 		const LayerW &w = m->layers[l];
 		const int slots = s->slots[l];
+		int ns_qkv = 0;  // > 0: q|k|v are raw partial sums, finished by the norm + RoPE kernel
 		if (use_tc) {
-			float *Cs[3] = {q, k, v};
 			const QW *ws[3] = {&w.Q, &w.K, &w.V};
-			TG_TRY(launch_gemm_tc_group(3, Cs, ws, nullptr, S, tc, st));
+			TG_TRY(gemm_raw(3, ws, &ns_qkv));
 		} else {
 			rmsnorm_rows_kernel<<<S, 256, 0, st>>>(xn, h, w.attn_pre, nullptr, D);
 			count_launch();
@@ -1357,7 +1361,8 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		qk_norm_rope_prefill_kernel<<<S, 192, 0, st>>>(q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
 		                                               m->rope[w.is_local ? 1 : 0][1],
 		                                               s->kcache[l] + size_t(b) * slots * AT_HD,
-		                                               s->vcache[l] + size_t(b) * slots * AT_HD, S, slots);
+		                                               s->vcache[l] + size_t(b) * slots * AT_HD, S, slots, tc.partial, ns_qkv,
+		                                               w.Q.s, w.K.s, w.V.s);
 		count_launch();
 		attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
