@@ -281,12 +281,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int grp = (int(blockIdx.x) >= a.tile_end[0]) + (int(blockIdx.x) >= a.tile_end[1]);  // tile_end of unused groups = INT_MAX
-	const int n0 = (int(blockIdx.x) - (grp ? a.tile_end[grp - 1] : 0)) * TC_BN;  // column inside the group's matrix
-	const int pcol = a.col0[grp] + n0;                                              // column inside a partial-sum row
+	const int n0 = (int(blockIdx.x) - (grp == 0 ? 0 : (grp == 1 ? a.tile_end[0] : a.tile_end[1]))) * TC_BN;  // column inside the group's matrix
+	// (selects over constant indices: a run-time index into the parameter arrays would move them to local memory)
+	const int pcol = (grp == 0 ? a.col0[0] : (grp == 1 ? a.col0[1] : a.col0[2])) + n0;  // column inside a partial-sum row
 	const CUtensorMap *wmap = grp == 0 ? &wmap0 : (grp == 1 ? &wmap1 : &wmap2);
-	float *const Cg = a.C[grp];
-	const float *const scg = a.scales[grp];
-	const int ldcg = a.ldc[grp];
+	float *const Cg = grp == 0 ? a.C[0] : (grp == 1 ? a.C[1] : a.C[2]);
+	const float *const scg = grp == 0 ? a.scales[0] : (grp == 1 ? a.scales[1] : a.scales[2]);
+	const int ldcg = grp == 0 ? a.ldc[0] : (grp == 1 ? a.ldc[1] : a.ldc[2]);
 	const int mt0 = blockIdx.y * TC_MT;
 	const int nmt = min(TC_MT, a.m_tiles - mt0);  // row tiles this CTA really has
 	const int k_blocks_all = a.K / TC_BK;
@@ -352,15 +353,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 				const uint32_t b_addr = smem_u32(stage_b(s));
 #pragma unroll
 				for (int mt = 0; mt < TC_MT; mt++) {
-					if (mt >= nmt) break;
-					const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN);
+					if (mt < nmt) {  // (a predicate, not a break: the loop stays fully unrolled — one thread issues every MMA)
+						const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN);
 #pragma unroll
-					for (int term = 0; term < 3; term++) {
-						const uint32_t a_addr = smem_u32(stage_a(s, term, mt));
+						for (int term = 0; term < 3; term++) {
+							const uint32_t a_addr = smem_u32(stage_a(s, term, mt));
 #pragma unroll
-						for (int j = 0; j < TC_BK / 16; j++) {
-							const uint32_t acc = (kb > 0 || term > 0 || j > 0) ? 1u : 0u;
-							tc_mma(d_tmem, tc_smem_desc(a_addr + j * 256), tc_smem_desc(b_addr + j * 256), idesc, acc);
+							for (int j = 0; j < TC_BK / 16; j++) {
+								const uint32_t acc = (kb > 0 || term > 0 || j > 0) ? 1u : 0u;
+								tc_mma(d_tmem, tc_smem_desc(a_addr + j * 256), tc_smem_desc(b_addr + j * 256), idesc, acc);
+							}
 						}
 					}
 				}

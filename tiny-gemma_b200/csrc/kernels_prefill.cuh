@@ -140,9 +140,14 @@ __global__ void qgemm_splitk_reduce_groups_kernel(ReduceGroups g, const float *p
 	for (int sp = 0; sp < nsplit; sp++) s += partial[size_t(sp) * M * N + i];
 	const size_t m = i / N;
 	const int n = int(i % N);
+	// (selects over constant indices: indexing the parameter arrays with a run-time value would move them to local memory)
 	const int gi = (n >= g.col0[1] && g.ngroups > 1) + (n >= g.col0[2] && g.ngroups > 2);
-	const int nl = n - g.col0[gi];
-	g.C[gi][m * g.ldc[gi] + nl] = s * g.scales[gi][nl];
+	const int c0 = gi == 0 ? g.col0[0] : (gi == 1 ? g.col0[1] : g.col0[2]);
+	float *Cp = gi == 0 ? g.C[0] : (gi == 1 ? g.C[1] : g.C[2]);
+	const float *sp_ = gi == 0 ? g.scales[0] : (gi == 1 ? g.scales[1] : g.scales[2]);
+	const int ld = gi == 0 ? g.ldc[0] : (gi == 1 ? g.ldc[1] : g.ldc[2]);
+	const int nl = n - c0;
+	Cp[m * ld + nl] = s * sp_[nl];
 }
 
 // out[b, :] = table lookup per element: gate = lut(gate) * up over [rows][n] with row strides
