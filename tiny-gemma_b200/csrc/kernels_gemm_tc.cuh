@@ -258,6 +258,9 @@ struct GemmTcArgs {
 	float *partial;              // [nsplit][M][N] raw sums      (nsplit > 1: summed and scaled by a second kernel)
 	int M, N, K, m_tiles;
 	int nsplit;                  // K-splits = gridDim.z; K / 32 must be a multiple of it
+	int halves;                  // 2: this CTA's K range is accumulated in two TMEM accumulators (first / second half of its
+	                             // K-blocks) that the epilogue adds in fp32 registers: halves the accumulation chain (the tensor
+	                             // core truncates when it adds into the accumulator) without any partial-sum traffic. Else 1.
 	int raw;                     // 1: always write raw partial sums (even unsplit); the consumer kernel adds the splits
 	                             // and applies the column scales itself, so no reduce kernel runs
 	unsigned *tickets;           // [gridDim.y * gridDim.x] zeros, or null. Non-null with nsplit > 1: the CTA that finishes
@@ -308,8 +311,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 		s_cnt = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
-	if (warp == 1) {  // TMEM: 2 accumulators x 128 fp32 columns
-		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(256)
+	if (warp == 1) {  // TMEM: (2 row tiles) x (2 K halves) accumulators of 128 fp32 columns
+		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512)
 		             : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 	}
@@ -351,16 +354,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 				if (!tc_wait(&full_bar[s], use & 1, a.err) || !tc_wait(&conv_bar[s], use & 1, a.err)) { s_fail = 1; break; }
 				tc_fence_after();
 				const uint32_t b_addr = smem_u32(stage_b(s));
+				const int kb_half = (a.halves == 2) ? (k_blocks + 1) / 2 : k_blocks;  // first K-block of the second accumulator
+				const bool second = kb >= kb_half;
+				const bool first_of_acc = (kb == 0) || (kb == kb_half);
 #pragma unroll
 				for (int mt = 0; mt < TC_MT; mt++) {
 					if (mt < nmt) {  // (a predicate, not a break: the loop stays fully unrolled — one thread issues every MMA)
-						const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN);
+						const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN) + (second ? uint32_t(TC_MT * TC_BN) : 0u);
 #pragma unroll
 						for (int term = 0; term < 3; term++) {
 							const uint32_t a_addr = smem_u32(stage_a(s, term, mt));
 #pragma unroll
 							for (int j = 0; j < TC_BK / 16; j++) {
-								const uint32_t acc = (kb > 0 || term > 0 || j > 0) ? 1u : 0u;
+								const uint32_t acc = (!first_of_acc || term > 0 || j > 0) ? 1u : 0u;
 								tc_mma(d_tmem, tc_smem_desc(a_addr + j * 256), tc_smem_desc(b_addr + j * 256), idesc, acc);
 							}
 						}
@@ -418,6 +424,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 					    : "r"(taddr)
 					    : "memory");
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					if (a.halves == 2 && k_blocks > 1) {
+						uint32_t r2[32];
+						const uint32_t taddr2 = taddr + uint32_t(TC_MT * TC_BN);
+						asm volatile(
+						    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+						    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+						    : "=r"(r2[0]), "=r"(r2[1]), "=r"(r2[2]), "=r"(r2[3]), "=r"(r2[4]), "=r"(r2[5]), "=r"(r2[6]), "=r"(r2[7]),
+						      "=r"(r2[8]), "=r"(r2[9]), "=r"(r2[10]), "=r"(r2[11]), "=r"(r2[12]), "=r"(r2[13]), "=r"(r2[14]), "=r"(r2[15]),
+						      "=r"(r2[16]), "=r"(r2[17]), "=r"(r2[18]), "=r"(r2[19]), "=r"(r2[20]), "=r"(r2[21]), "=r"(r2[22]), "=r"(r2[23]),
+						      "=r"(r2[24]), "=r"(r2[25]), "=r"(r2[26]), "=r"(r2[27]), "=r"(r2[28]), "=r"(r2[29]), "=r"(r2[30]), "=r"(r2[31])
+						    : "r"(taddr2)
+						    : "memory");
+						asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+						for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+					}
 					if ((mt0 + mt) < a.m_tiles && row < a.M) {
 						if (a.nsplit == 1 && !a.raw) {
 							float *dst = Cg + size_t(row) * ldcg + n0 + c * 32;
@@ -518,7 +540,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 		}
 		__syncwarp();
 		tc_fence_after();
-		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 	}
 }
 

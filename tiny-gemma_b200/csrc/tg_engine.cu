@@ -1038,7 +1038,9 @@ constexpr size_t TC_TICKETS = 4096;
 int tc_pick_split(int M, int K, int N, size_t partial_floats, int max_split) {
 	const int k_blocks = K / TC_BK;
 	const int ctas = (N / TC_BN) * (((M + TC_BM - 1) / TC_BM + TC_MT - 1) / TC_MT);
-	const int want = std::max((g_num_sms + ctas - 1) / ctas, (k_blocks + 23) / 24);
+	// accumulation chains are kept to <= 24 K-blocks; a CTA keeps two accumulators per tile (first / second half of
+	// its K range), so it can take up to 48 K-blocks
+	const int want = std::max((g_num_sms + ctas - 1) / ctas, (k_blocks + 47) / 48);
 	int best = 1;
 	for (int ns = 1; ns <= std::min(k_blocks, max_split); ns++) {
 		if (k_blocks % ns) continue;
@@ -1121,6 +1123,7 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 	const bool fused = !raw_nsplit && sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
 	a.tickets = fused ? sc.tickets : nullptr;
 	a.raw = raw_nsplit ? 1 : 0;
+	a.halves = env_int("TG_GEMM_HALVES", 2);
 	if (raw_nsplit) {
 		if (size_t(a.nsplit) * M * ntot > sc.partial_floats) return fail(TG_ENOMEM, "tensor-core GEMM partial-sum scratch too small");
 		*raw_nsplit = a.nsplit;
