@@ -353,4 +353,111 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float
 	}
 }
 
+// Short prompts: the kernel above gives a warp one query and all four heads and walks the keys one
+// at a time, which is a long dependent chain (dot, five shuffle rounds, exp) per key on only S/8
+// CTAs. Here a warp owns one (query, head), a CTA two queries (S/2 CTAs), and four keys are scored
+// together so that their shuffle chains overlap; the softmax update then runs over the four in key
+// order. Per (query, head) the arithmetic and its order are those of attn_prefill_kernel.
+__global__ void __launch_bounds__(256) attn_prefill_small_kernel(float *o, const float *q, const float *k, const float *v,
+                                                                 int S, int is_local, int window) {
+	__shared__ __align__(16) float ks[AP_TILE][256];
+	__shared__ __align__(16) float vs[AP_TILE][256];
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	const int s0 = blockIdx.x * 2;
+	const int s = s0 + (warp >> 2), h = warp & 3;  // this warp's query (may be >= S: then it only helps loading) and head
+	const int s_last = min(S - 1, s0 + 1);
+	int cta_j0 = 0;
+	if (is_local) cta_j0 = (s0 >= window) ? s0 - window : 0;
+	int my_j0 = 0;
+	if (is_local) my_j0 = (s >= window) ? s - window : 0;
+	float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0, o0 = q0, o1 = q0;
+	float m = -INFINITY, l = 0.0f;
+	if (s < S) {
+		const float *qr = q + size_t(s) * 1024 + h * 256;
+		q0 = *reinterpret_cast<const float4 *>(qr + 4 * lane);
+		q1 = *reinterpret_cast<const float4 *>(qr + 128 + 4 * lane);
+		q0.x *= 0.0625f; q0.y *= 0.0625f; q0.z *= 0.0625f; q0.w *= 0.0625f;  // exact: see attn_prefill_kernel
+		q1.x *= 0.0625f; q1.y *= 0.0625f; q1.z *= 0.0625f; q1.w *= 0.0625f;
+	}
+	float4 pk[4], pv[4];
+	auto fetch = [&](int jt) {
+#pragma unroll
+		for (int u = 0; u < 4; u++) {
+			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
+			const int j = jt + r;
+			if (j <= s_last) {
+				pk[u] = *reinterpret_cast<const float4 *>(k + size_t(j) * 256 + 4 * c4);
+				pv[u] = *reinterpret_cast<const float4 *>(v + size_t(j) * 256 + 4 * c4);
+			} else {
+				pk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+				pv[u] = pk[u];
+			}
+		}
+	};
+	fetch(cta_j0);
+	for (int jt = cta_j0; jt <= s_last; jt += AP_TILE) {
+		__syncthreads();  // previous tile fully consumed
+#pragma unroll
+		for (int u = 0; u < 4; u++) {
+			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
+			*reinterpret_cast<float4 *>(&ks[r][4 * c4]) = pk[u];
+			*reinterpret_cast<float4 *>(&vs[r][4 * c4]) = pv[u];
+		}
+		__syncthreads();
+		if (jt + AP_TILE <= s_last) fetch(jt + AP_TILE);
+		if (s < S) {
+			const int ja = max(jt, my_j0), jb = min(jt + AP_TILE - 1, s);
+			for (int j4 = ja; j4 <= jb; j4 += 4) {
+				float sc[4];
+#pragma unroll
+				for (int u = 0; u < 4; u++) {
+					const int r = min(j4 + u, jb) - jt;  // (keys past jb repeat the last one; their scores are not used)
+					const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r][4 * lane]);
+					const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r][128 + 4 * lane]);
+					float t = q0.x * k0v.x;
+					t = fmaf(q0.y, k0v.y, t);
+					t = fmaf(q0.z, k0v.z, t);
+					t = fmaf(q0.w, k0v.w, t);
+					t = fmaf(q1.x, k1v.x, t);
+					t = fmaf(q1.y, k1v.y, t);
+					t = fmaf(q1.z, k1v.z, t);
+					t = fmaf(q1.w, k1v.w, t);
+					sc[u] = t;
+				}
+#pragma unroll
+				for (int of = 16; of > 0; of >>= 1) {
+#pragma unroll
+					for (int u = 0; u < 4; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], of);
+				}
+#pragma unroll
+				for (int u = 0; u < 4; u++) {
+					if (j4 + u <= jb) {
+						const int r = j4 + u - jt;
+						const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r][4 * lane]);
+						const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r][128 + 4 * lane]);
+						const float mn = fmaxf(m, sc[u]);
+						const float corr = expf(m - mn);
+						const float p = expf(sc[u] - mn);
+						l = fmaf(l, corr, p);
+						o0.x = fmaf(p, v0v.x, o0.x * corr);
+						o0.y = fmaf(p, v0v.y, o0.y * corr);
+						o0.z = fmaf(p, v0v.z, o0.z * corr);
+						o0.w = fmaf(p, v0v.w, o0.w * corr);
+						o1.x = fmaf(p, v1v.x, o1.x * corr);
+						o1.y = fmaf(p, v1v.y, o1.y * corr);
+						o1.z = fmaf(p, v1v.z, o1.z * corr);
+						o1.w = fmaf(p, v1v.w, o1.w * corr);
+						m = mn;
+					}
+				}
+			}
+		}
+	}
+	if (s >= S) return;
+	const float inv = 1.0f / l;
+	float *orow = o + size_t(s) * 1024 + h * 256;
+	*reinterpret_cast<float4 *>(orow + 4 * lane) = make_float4(o0.x * inv, o0.y * inv, o0.z * inv, o0.w * inv);
+	*reinterpret_cast<float4 *>(orow + 128 + 4 * lane) = make_float4(o1.x * inv, o1.y * inv, o1.z * inv, o1.w * inv);
+}
+
 }  // namespace tg

@@ -1367,7 +1367,10 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		                                               s->vcache[l] + size_t(b) * slots * AT_HD, S, slots, tc.partial, ns_qkv,
 		                                               w.Q.s, w.K.s, w.V.s);
 		count_launch();
-		attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+		if (S <= env_int("TG_ATTN_SMALL_MAX", 1024))  // short prompts: one (query, head) per warp, S/2 CTAs
+			attn_prefill_small_kernel<<<(S + 1) / 2, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+		else
+			attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
 		TG_TRY(check_launch("attn_prefill"));
 		if (use_tc) {
