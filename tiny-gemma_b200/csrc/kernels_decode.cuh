@@ -475,8 +475,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
 		__shared__ float rowbuf[AT_NH * AT_HD + 2 * AT_HD];
 		constexpr int NQ = AT_NH * AT_HD + 2 * AT_HD;
 		for (int n = tid; n < NQ; n += AT_THREADS) {
-			float acc = 0.0f;
-			for (int sp = 0; sp < a.qkv_nsplit; sp++) acc += a.qkv[(size_t(sp) * a.qkv_B + b) * NQ + n];
+			const float acc = sum_splits(a.qkv + size_t(b) * NQ + n, size_t(a.qkv_B) * NQ, a.qkv_nsplit);
 			const float sc = n < AT_NH * AT_HD ? a.sq[n] : (n < AT_NH * AT_HD + AT_HD ? a.sk[n - AT_NH * AT_HD] : a.sv[n - AT_NH * AT_HD - AT_HD]);
 			rowbuf[n] = acc * sc;
 		}

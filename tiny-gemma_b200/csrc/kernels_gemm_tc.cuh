@@ -122,9 +122,7 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 		for (int d = tid; d < dim; d += 256) {
 			float v;
 			if (nsplit > 0) {
-				v = 0.0f;
-				for (int sp = 0; sp < nsplit; sp++) v += t[(size_t(sp) * M + row) * ldp + d];
-				v *= tscale[d];
+				v = sum_splits(t + size_t(row) * ldp + d, size_t(M) * ldp, nsplit) * tscale[d];
 			} else {
 				v = t[off + d];
 			}
@@ -172,14 +170,27 @@ __global__ void __launch_bounds__(256) geglu_pack_kernel(const float *gate, cons
 		float x[8];
 		if (row < M && nsplit > 0) {
 			float4 u0 = make_float4(0.f, 0.f, 0.f, 0.f), u1 = u0, g0 = u0, g1 = u0;
-			for (int sp = 0; sp < nsplit; sp++) {
-				const float *pr = up + (size_t(sp) * M + row) * (2 * size_t(K)) + 8 * k8;
-				const float4 a0 = *reinterpret_cast<const float4 *>(pr), a1 = *reinterpret_cast<const float4 *>(pr + 4);
-				const float4 b0 = *reinterpret_cast<const float4 *>(pr + K), b1 = *reinterpret_cast<const float4 *>(pr + K + 4);
-				u0.x += a0.x; u0.y += a0.y; u0.z += a0.z; u0.w += a0.w;
-				u1.x += a1.x; u1.y += a1.y; u1.z += a1.z; u1.w += a1.w;
-				g0.x += b0.x; g0.y += b0.y; g0.z += b0.z; g0.w += b0.w;
-				g1.x += b1.x; g1.y += b1.y; g1.z += b1.z; g1.w += b1.w;
+			for (int s0 = 0; s0 < nsplit; s0 += 3) {  // three splits' loads in flight, added in split order
+				float4 a0[3], a1[3], b0[3], b1[3];
+#pragma unroll
+				for (int q = 0; q < 3; q++) {
+					const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+					a0[q] = a1[q] = b0[q] = b1[q] = z;
+					if (s0 + q < nsplit) {
+						const float *pr = up + (size_t(s0 + q) * M + row) * (2 * size_t(K)) + 8 * k8;
+						a0[q] = *reinterpret_cast<const float4 *>(pr);
+						a1[q] = *reinterpret_cast<const float4 *>(pr + 4);
+						b0[q] = *reinterpret_cast<const float4 *>(pr + K);
+						b1[q] = *reinterpret_cast<const float4 *>(pr + K + 4);
+					}
+				}
+#pragma unroll
+				for (int q = 0; q < 3; q++) {
+					u0.x += a0[q].x; u0.y += a0[q].y; u0.z += a0[q].z; u0.w += a0[q].w;
+					u1.x += a1[q].x; u1.y += a1[q].y; u1.z += a1[q].z; u1.w += a1[q].w;
+					g0.x += b0[q].x; g0.y += b0[q].y; g0.z += b0[q].z; g0.w += b0[q].w;
+					g1.x += b1[q].x; g1.y += b1[q].y; g1.z += b1[q].z; g1.w += b1[q].w;
+				}
 			}
 			const float4 su0 = *reinterpret_cast<const float4 *>(su + 8 * k8), su1 = *reinterpret_cast<const float4 *>(su + 8 * k8 + 4);
 			const float4 sg0 = *reinterpret_cast<const float4 *>(sg + 8 * k8), sg1 = *reinterpret_cast<const float4 *>(sg + 8 * k8 + 4);

@@ -177,9 +177,7 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
 	const int c = s - start;  // cache slot, if >= 0
 	// raw element n of this position's q|k|v row (n = column in the concatenated 1536), scaled by scale[ns]
 	auto raw = [&](int n, const float *scale, int ns) -> float {
-		float a = 0.0f;
-		for (int sp = 0; sp < nsplit; sp++) a += part[(size_t(sp) * S + s) * 1536 + n];
-		return a * scale[ns];
+		return sum_splits(part + size_t(s) * 1536 + n, size_t(S) * 1536, nsplit) * scale[ns];
 	};
 	// x: the head's 256 floats (finished projection if nsplit == 0; always the destination)
 	auto norm_rope = [&](float *x, const float *w, int n0, const float *scale, int ns0) {

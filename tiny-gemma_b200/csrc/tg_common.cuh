@@ -88,4 +88,18 @@ struct GeluLut {
 	}
 };
 
+// sum over K-splits of p[sp * stride], added in ascending split order; the loads of up to eight
+// splits are in flight together (missing splits contribute an exact + 0.0f)
+__device__ __forceinline__ float sum_splits(const float *p, size_t stride, int nsplit) {
+	float v = 0.0f;
+	for (int s0 = 0; s0 < nsplit; s0 += 8) {
+		float a[8];
+#pragma unroll
+		for (int q = 0; q < 8; q++) a[q] = (s0 + q < nsplit) ? p[size_t(s0 + q) * stride] : 0.0f;
+#pragma unroll
+		for (int q = 0; q < 8; q++) v += a[q];
+	}
+	return v;
+}
+
 }  // namespace tg
