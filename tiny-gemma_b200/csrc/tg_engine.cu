@@ -1643,7 +1643,7 @@ int tg_state_create(tg_model *m, int batch, int max_pos_global, tg_state **out) 
 	s->B = batch;
 	s->max_pos_global = max_pos_global;
 	int rc = state_alloc(s);
-	if (rc == TG_OK && batch >= env_int("TG_BATCH_TC_MIN", 16)) rc = batched_setup(s);
+	if (rc == TG_OK && batch >= env_int("TG_BATCH_TC_MIN", 4)) rc = batched_setup(s);
 	if (rc == TG_OK && batch == 1 && env_int("TG_MEGA", 1)) {
 		int mrc = mega_setup(s);
 		if (mrc != TG_OK) {
