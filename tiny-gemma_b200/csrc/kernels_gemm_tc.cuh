@@ -119,15 +119,41 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 	if (t) {
 		__shared__ float t_s[2048];
 		float ss = 0.0f;
-		for (int d = tid; d < dim; d += 256) {
-			float v;
-			if (nsplit > 0) {
-				v = sum_splits(t + size_t(row) * ldp + d, size_t(M) * ldp, nsplit) * tscale[d];
-			} else {
-				v = t[off + d];
+		if (nsplit > 0) {
+			// Thread tid owns d = tid, tid + 256, ... (at most 8 values). The partial sums of three splits for
+			// all of them are requested together: a row costs ceil(nsplit / 3) L2 round trips, not nsplit * 8.
+			float acc[8];
+#pragma unroll
+			for (int j = 0; j < 8; j++) acc[j] = 0.0f;
+			const size_t sstride = size_t(M) * ldp;
+			const float *base = t + size_t(row) * ldp + tid;
+			for (int s0 = 0; s0 < nsplit; s0 += 3) {
+				float a[3][8];
+#pragma unroll
+				for (int q = 0; q < 3; q++)
+#pragma unroll
+					for (int j = 0; j < 8; j++)
+						a[q][j] = (s0 + q < nsplit && tid + 256 * j < dim) ? base[size_t(s0 + q) * sstride + 256 * j] : 0.0f;
+#pragma unroll
+				for (int q = 0; q < 3; q++)
+#pragma unroll
+					for (int j = 0; j < 8; j++) acc[j] += a[q][j];
 			}
-			t_s[d] = v;
-			ss = fmaf(v, v, ss);
+#pragma unroll
+			for (int j = 0; j < 8; j++) {
+				const int d = tid + 256 * j;
+				if (d < dim) {
+					const float v = acc[j] * tscale[d];
+					t_s[d] = v;
+					ss = fmaf(v, v, ss);
+				}
+			}
+		} else {
+			for (int d = tid; d < dim; d += 256) {
+				const float v = t[off + d];
+				t_s[d] = v;
+				ss = fmaf(v, v, ss);
+			}
 		}
 		ss = block_sum<8>(ss, bred);
 		const float r = inv_rms(ss, dim);

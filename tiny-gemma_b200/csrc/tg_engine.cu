@@ -1245,7 +1245,7 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 			const QW *ws[2] = {&w.U, &w.G};
 			TG_TRY(gemm_raw(2, ws, &ns));
 		}
-		geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(nullptr, s->btc.partial, s->btc.apack, B, I, m_tiles, lut, ns, w.U.s, w.G.s);
+		geglu_pack_kernel<<<unsigned((size_t(m_tiles) * TC_BM * (I / 8) + 255) / 256), 256, 0, st>>>(nullptr, s->btc.partial, s->btc.apack, B, I, m_tiles, lut, ns, w.U.s, w.G.s);
 		count_launch();
 		{
 			const QW *ws[1] = {&w.Dn};
@@ -1386,7 +1386,7 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 				const QW *ws[2] = {&w.U, &w.G};
 				TG_TRY(gemm_raw(2, ws, &ns));
 			}
-			geglu_pack_kernel<<<2 * g_num_sms, 256, 0, st>>>(nullptr, tc.partial, tc.apack, S, I, m_tiles, lut, ns, w.U.s, w.G.s);
+			geglu_pack_kernel<<<unsigned(std::min<size_t>((size_t(m_tiles) * TC_BM * (I / 8) + 255) / 256, 65535 * 16)), 256, 0, st>>>(nullptr, tc.partial, tc.apack, S, I, m_tiles, lut, ns, w.U.s, w.G.s);
 			count_launch();
 			{
 				const QW *ws[1] = {&w.Dn};
