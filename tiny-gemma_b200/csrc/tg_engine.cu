@@ -1040,7 +1040,9 @@ int tc_pick_split(int M, int K, int N, size_t partial_floats, int max_split) {
 	const int ctas = (N / TC_BN) * (((M + TC_BM - 1) / TC_BM + TC_MT - 1) / TC_MT);
 	// accumulation chains are kept to <= 24 K-blocks; a CTA keeps two accumulators per tile (first / second half of
 	// its K range), so it can take up to 48 K-blocks
-	const int want = std::max((g_num_sms + ctas - 1) / ctas, (k_blocks + 47) / 48);
+	// split only while every split still fits one wave (ctas * splits <= SMs): a second, partly filled wave
+	// costs as much as the split saves
+	const int want = std::max(env_int("TG_GEMM_SPLIT_CEIL", 0) ? (g_num_sms + ctas - 1) / ctas : std::max(1, g_num_sms / ctas), (k_blocks + 47) / 48);
 	int best = 1;
 	for (int ns = 1; ns <= std::min(k_blocks, max_split); ns++) {
 		if (k_blocks % ns) continue;
