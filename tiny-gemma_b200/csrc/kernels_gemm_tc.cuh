@@ -449,8 +449,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 				const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
 #pragma unroll 1
 				for (int c = 0; c < TC_BN / 32; c++) {
-					uint32_t r[32];
+					uint32_t r[32], r2[32];
 					const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(mt * TC_BN + c * 32);
+					const bool two = a.halves == 2 && k_blocks > 1;  // second accumulator in use
+					// both accumulators are requested before the single wait: a TMEM load + wait is ~600 clk of latency
 					asm volatile(
 					    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
 					    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -460,9 +462,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 					      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
 					    : "r"(taddr)
 					    : "memory");
-					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-					if (a.halves == 2 && k_blocks > 1) {
-						uint32_t r2[32];
+					if (two) {
 						const uint32_t taddr2 = taddr + uint32_t(TC_MT * TC_BN);
 						asm volatile(
 						    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -473,7 +473,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 						      "=r"(r2[24]), "=r"(r2[25]), "=r"(r2[26]), "=r"(r2[27]), "=r"(r2[28]), "=r"(r2[29]), "=r"(r2[30]), "=r"(r2[31])
 						    : "r"(taddr2)
 						    : "memory");
-						asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					}
+					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					if (two) {
 #pragma unroll
 						for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
 					}
