@@ -129,6 +129,21 @@ __device__ __forceinline__ void mv_tile_rows(float (&acc)[MB][16], const int8_t 
 	const size_t step = size_t(MV_ROWS_PER_ITER) * N;
 	const int iters = kc / MV_ROWS_PER_ITER;
 	int it = 0;
+	// eight 16-byte loads in flight per thread (32 KB per CTA): a K-split slice of 256 rows is one round trip to DRAM
+	for (; it + 8 <= iters; it += 8) {
+		int4 v[8];
+#pragma unroll
+		for (int u = 0; u < 8; u++) v[u] = ld_stream_int4(p + u * step);
+		p += 8 * step;
+		const int r = it * MV_ROWS_PER_ITER + r0;
+#pragma unroll
+		for (int u = 0; u < 8; u++) {
+			float xv[MB];
+#pragma unroll
+			for (int b = 0; b < MB; b++) xv[b] = xs[b * xs_stride + r + 32 * u];
+			mv_accumulate<MB>(acc, v[u], xv);
+		}
+	}
 	for (; it + 4 <= iters; it += 4) {
 		int4 v0 = ld_stream_int4(p);
 		int4 v1 = ld_stream_int4(p + step);
@@ -325,15 +340,16 @@ __global__ void __launch_bounds__(MV_THREADS) qmatvec_kernel(MvArgs a) {
 			__threadfence();
 			if (tid < MV_TN) {
 				for (int b = 0; b < a.B; b++) {
+					// the splits are added in ascending order, eight loads in flight at a time (a chain of
+					// dependent loads over 30 splits cost more than the matvec itself)
 					float s1 = 0.0f, s2 = 0.0f;
-					for (int sp = 0; sp < a.nsplit; sp++) {
-						const float *prow = a.partial + (size_t(sp) * a.B + b) * a.part_stride;
-						if (EPI == EPI_SCALE) {
-							s1 += __ldcg(prow + pcol);
-						} else {
-							s1 += __ldcg(prow + n0 + tid);
-							s2 += __ldcg(prow + a.seg[1].out_off + n0 + tid);
-						}
+					const float *prow0 = a.partial + size_t(b) * a.part_stride;
+					const size_t sstride = size_t(a.B) * a.part_stride;
+					if (EPI == EPI_SCALE) {
+						s1 = sum_splits<true>(prow0 + pcol, sstride, a.nsplit);
+					} else {
+						s1 = sum_splits<true>(prow0 + n0 + tid, sstride, a.nsplit);
+						s2 = sum_splits<true>(prow0 + a.seg[1].out_off + n0 + tid, sstride, a.nsplit);
 					}
 					if (EPI == EPI_SCALE) {
 						a.out[size_t(b) * a.out_stride + pcol] = s1 * sg.scale[n0 + tid];

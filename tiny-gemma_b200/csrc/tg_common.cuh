@@ -89,13 +89,18 @@ struct GeluLut {
 };
 
 // sum over K-splits of p[sp * stride], added in ascending split order; the loads of up to eight
-// splits are in flight together (missing splits contribute an exact + 0.0f)
+// splits are in flight together (missing splits contribute an exact + 0.0f). L2 = true reads around
+// the L1 (ld.global.cg): for partial sums written by other CTAs of the SAME kernel.
+template <bool L2 = false>
 __device__ __forceinline__ float sum_splits(const float *p, size_t stride, int nsplit) {
 	float v = 0.0f;
 	for (int s0 = 0; s0 < nsplit; s0 += 8) {
 		float a[8];
 #pragma unroll
-		for (int q = 0; q < 8; q++) a[q] = (s0 + q < nsplit) ? p[size_t(s0 + q) * stride] : 0.0f;
+		for (int q = 0; q < 8; q++) {
+			a[q] = 0.0f;
+			if (s0 + q < nsplit) a[q] = L2 ? __ldcg(p + size_t(s0 + q) * stride) : p[size_t(s0 + q) * stride];
+		}
 #pragma unroll
 		for (int q = 0; q < 8; q++) v += a[q];
 	}
