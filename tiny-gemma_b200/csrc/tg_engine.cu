@@ -2044,7 +2044,8 @@ int tg_dev_qmatvec(float *y, const float *x, const int8_t *w, const float *scale
 	TG_CUDA(cudaGetDevice(&dev));
 	int sms = 0;
 	if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) g_num_sms = sms;
-	MvPlan p = plan_matvec(K, N / MV_TN, env_int("TG_MV_TARGET_CTAS", 2 * g_num_sms), env_int("TG_MV_MAX_SPLIT", 1 << 30));
+	// K-split depth capped (measured on the isolated operator: deeper splits only lengthen the last CTA's sum)
+	MvPlan p = plan_matvec(K, N / MV_TN, env_int("TG_MV_TARGET_CTAS", 2 * g_num_sms), env_int("TG_MV_MAX_SPLIT", K >= 4096 ? 32 : 16));
 	size_t need = size_t(p.nsplit) * N;
 	if (need > partial_floats[dev]) {
 		if (partial[dev]) cudaFree(partial[dev]);
