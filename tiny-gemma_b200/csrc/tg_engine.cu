@@ -941,6 +941,9 @@ int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, b
 	a.log_cap = s->log_cap;
 	a.seq0 = s->mg_seq;
 	s->mg_seq += unsigned(n_steps) * unsigned(m->cfg.n_layers);
+	// CTAs per global-attention layer follow the context: 32 up to ~1K positions, 64 beyond (measured at 16K
+	// positions: 937 -> 1049 tok/s; at 200-700 positions 64 is no gain). TG_MEGA_ATT_GLOBAL fixes the number.
+	if (!std::getenv("TG_MEGA_ATT_GLOBAL") && s->host_pos[0] >= 1024) a.att_global = std::min(MG_MAX_ATT, s->mega_grid);
 	// every word of the hand-off arena starts as "empty" (all ones)
 	TG_CUDA(cudaMemsetAsync(s->mg_ll, 0xFF, s->mg_ll_bytes, s->stream));
 	a.dbg = s->mg_dbg;
