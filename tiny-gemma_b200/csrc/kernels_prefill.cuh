@@ -183,11 +183,42 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
 	auto norm_rope = [&](float *x, const float *w, int n0, const float *scale, int ns0) {
 		float lo[4], hi[4];
 		float ss = 0.0f;
+		if (nsplit > 0) {
+			// the lane's eight elements x four splits are requested together; splits are added in ascending order
+#pragma unroll
+			for (int i = 0; i < 4; i++) lo[i] = hi[i] = 0.0f;
+			const size_t sstride = size_t(S) * 1536;
+			const float *base = part + size_t(s) * 1536 + n0 + 4 * lane;
+			for (int s0 = 0; s0 < nsplit; s0 += 4) {
+				float4 a[4], b[4];
+#pragma unroll
+				for (int q = 0; q < 4; q++) {
+					a[q] = b[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+					if (s0 + q < nsplit) {
+						a[q] = *reinterpret_cast<const float4 *>(base + size_t(s0 + q) * sstride);
+						b[q] = *reinterpret_cast<const float4 *>(base + size_t(s0 + q) * sstride + 128);
+					}
+				}
+#pragma unroll
+				for (int q = 0; q < 4; q++) {
+					lo[0] += a[q].x; lo[1] += a[q].y; lo[2] += a[q].z; lo[3] += a[q].w;
+					hi[0] += b[q].x; hi[1] += b[q].y; hi[2] += b[q].z; hi[3] += b[q].w;
+				}
+			}
+#pragma unroll
+			for (int i = 0; i < 4; i++) {
+				lo[i] *= scale[ns0 + 4 * lane + i];
+				hi[i] *= scale[ns0 + 128 + 4 * lane + i];
+			}
+		} else {
+#pragma unroll
+			for (int i = 0; i < 4; i++) {
+				lo[i] = x[4 * lane + i];
+				hi[i] = x[128 + 4 * lane + i];
+			}
+		}
 #pragma unroll
 		for (int i = 0; i < 4; i++) {
-			const int d = 4 * lane + i;
-			lo[i] = nsplit > 0 ? raw(n0 + d, scale, ns0 + d) : x[d];
-			hi[i] = nsplit > 0 ? raw(n0 + 128 + d, scale, ns0 + 128 + d) : x[128 + d];
 			ss = fmaf(lo[i], lo[i], ss);
 			ss = fmaf(hi[i], hi[i], ss);
 		}
