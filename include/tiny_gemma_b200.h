@@ -183,6 +183,9 @@ int tg_dev_qmatvec(float *y_dev, const float *x_dev, const int8_t *w_dev, const 
  * (different streams) race; serialise them. */
 int tg_dev_qmatvec_static(float *y_dev, const float *x_dev, const int8_t *w_dev, const float *scales_dev, int K, int N,
                           void *cuda_stream);
+/* tg_dev_qgemm synchronises the stream before it returns (it reads the kernel's error word), except
+ * while the stream is being captured into a CUDA graph: then it only records its launches, and an
+ * error raised by a replay is reported by the next call made outside a capture. */
 int tg_dev_qgemm(float *c_dev, const float *a_dev, const int8_t *w_dev, const float *scales_dev, int M, int K, int N,
                  void *cuda_stream);
 

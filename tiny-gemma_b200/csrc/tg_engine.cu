@@ -2176,6 +2176,11 @@ int tg_dev_qgemm(float *c, const float *a, const int8_t *w, const float *scales,
 		}
 		TG_TRY(pack_activations(a, M, K, tc[dev], (cudaStream_t)stream));
 		TG_TRY(launch_gemm_tc(c, q, M, tc[dev], (cudaStream_t)stream));
+		// while the stream is being captured into a graph nothing may synchronise: the error word stays
+		// set on the device and the next call outside a capture reports it
+		cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+		TG_CUDA(cudaStreamIsCapturing((cudaStream_t)stream, &cap));
+		if (cap != cudaStreamCaptureStatusNone) return TG_OK;
 		int flag = 0;
 		TG_CUDA(cudaMemcpyAsync(&flag, tc[dev].err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
 		TG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
