@@ -50,6 +50,11 @@ def test_qgemm_ragged_and_large_m(capi, port):
     for M in (1, 63, 65, 1024):
         x, w, s = cases.linear_case(640, 1024, M, seed=9)
         assert rel_l2(capi.qgemm(x, w, s), port.linear_prefill(x, w, s)) <= 5e-6
+    # more than 256 rows take the 256-column tile shape: a ragged last row tile, and column counts that
+    # are not a multiple of 256 (the last tile reaches past the matrix)
+    for M, K, N in ((300, 1152, 1152), (513, 2048, 640), (384, 6912, 1152), (257, 1152, 6912)):
+        x, w, s = cases.linear_case(K, N, M, seed=10)
+        assert rel_l2(capi.qgemm(x, w, s), port.linear_prefill(x, w, s)) <= 5e-6
 
 
 def test_matvec_is_linear_and_deterministic(capi):

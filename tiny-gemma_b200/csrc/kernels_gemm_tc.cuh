@@ -13,13 +13,13 @@
 //                       tensor core's shared-memory layout, tile by tile, so
 //                       that a GEMM CTA fetches an operand tile with ONE bulk
 //                       copy.
-//   qgemm_tc_kernel     one CTA = one 128-column tile of W x two 128-row tiles
-//                       of A (M <= 256 per CTA; more rows -> grid.y). Warp
+//   qgemm_tc_kernel     one CTA = one BN-column tile of W x MT 128-row tiles of A,
+//                       <MT, BN> = <2, 128> or <1, 256> (more rows -> grid.y). Warp
 //                       roles: warp 0 producer (bulk copies of A tiles, TMA of
 //                       the int8 W tile), warp 1 MMA issuer, warps 2-5 convert
 //                       W int8 -> bf16 into the operand layout and run the
 //                       epilogue (TMEM -> registers -> x scale -> C).
-//                       3-stage ring over K in blocks of 32. K may be split over
+//                       3- or 4-stage ring over K in blocks of 32. K may be split over
 //                       gridDim.z CTAs (raw partial sums, added in split order
 //                       and scaled by qgemm_splitk_reduce_kernel): it fills the
 //                       GPU when N/128 is small and keeps the accumulation
@@ -27,10 +27,16 @@
 //                       into the fp32 accumulator, so the error grows with the
 //                       chain length (2e-5 at K = 6912 unsplit).
 //
-// Shared-memory operand layout (K-major, no swizzle): 8 x 8 bf16 "core
-// matrices" of 128 contiguous bytes (8 rows of 16 bytes); byte offset of
-// element (r, k) in a [128][32] tile = (r/8)*512 + (k/8)*128 + (r%8)*16 + (k%8)*2,
-// i.e. leading (K) offset 128 B, stride (row-group) offset 512 B.
+// Shared-memory operand layouts (no swizzle): 8 x 8 bf16 "core matrices" of 128
+// contiguous bytes (8 rows of 16 bytes).
+//   A (K-major):  byte offset of (r, k) in a [128][32] tile
+//                 = (r/8)*512 + (k/8)*128 + (r%8)*16 + (k%8)*2
+//   B (N-major, as W is stored): byte offset of (k, n) in a [32][BN] tile
+//                 = (n/8)*512 + (k/8)*128 + (k%8)*16 + (n%8)*2
+// i.e. for both: 128 B between the two 8-wide K groups of an MMA (leading
+// offset), 512 B between groups of 8 rows / columns (stride offset). Keeping B
+// N-major lets a converter thread turn 8 consecutive int8 of a W row (one
+// 8-byte load) into one 16-byte row of a core matrix.
 //
 // All waits are bounded; a wait that runs out sets *err and the CTA drains and
 // frees its TMEM before returning.
@@ -44,12 +50,23 @@
 namespace tg {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 32;
-constexpr int TC_STAGES = 3;
-constexpr int TC_MT = 2;                       // 128-row tiles of A per CTA
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 8 KiB: one [128][32] bf16 operand tile
-constexpr int TC_W_BYTES = TC_BK * TC_BN;         // 4 KiB: int8 W tile
-constexpr int TC_STAGE_BYTES = 3 * TC_MT * TC_TILE_BYTES + TC_W_BYTES + TC_TILE_BYTES;  // A terms + W int8 + B bf16
-constexpr int TC_THREADS = 192;
+// Two tile shapes of one kernel template <MT, BN>: MT 128-row tiles of A x BN columns of W per CTA.
+//   <2, 128>  (small M: one CTA covers up to 256 rows, W converted once for both row tiles)
+//   <1, 256>  (large M: every fetched A tile is used against 256 columns; the kernel is bound by the
+//              L2 -> SM traffic of the three-term A operand, 6 bytes per activation element)
+// Both keep MT * BN * 2 = 512 TMEM columns: two accumulators (K halves) per row tile.
+template <int MT, int BN> struct TcShape {
+	static constexpr int A_BYTES = 3 * MT * TC_TILE_BYTES;   // one K-block of the three A terms
+	static constexpr int W_BYTES = TC_BK * BN;               // int8 W tile
+	static constexpr int B_BYTES = BN * TC_BK * 2;           // its bf16 operand form
+	// two rings: the large A stages, and the small W / B stages whose loads run further ahead so that the
+	// int8 -> bf16 conversion of a K-block is finished before its A tiles land
+	static constexpr int NA = (MT == 2) ? 3 : 5;
+	static constexpr int NB = 4;
+	static constexpr int SMEM = NA * A_BYTES + NB * (W_BYTES + B_BYTES) + 1024;
+};
+constexpr int TC_THREADS = 224;
 constexpr int TC_SPIN_CAP = 1 << 24;
 
 // ------------------------------------------------------------------ split + pack
@@ -249,9 +266,9 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
 	d |= uint64_t(1) << 46;                      // descriptor version of this architecture
 	return d;                                    // base offset 0, layout type 0 = no swizzle
 }
-// instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = 128
-__device__ __forceinline__ uint32_t tc_idesc() {
-	return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TC_BN >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
+// instruction descriptor: D fp32, A and B bf16, A K-major, B N-major (bit 16), M = 128, N = bn
+__device__ __forceinline__ uint32_t tc_idesc(int bn) {
+	return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(bn >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
 }
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
 	asm volatile(
@@ -269,6 +286,18 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
 	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
 	             "l"(src), "r"(bytes), "r"(smem_u32(bar))
 	             : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread (completion: tcgen05.wait::ld)
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+	asm volatile(
+	    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+	    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+	    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+	      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+	      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+	      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+	    : "r"(taddr)
+	    : "memory");
 }
 __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int *err) {
 	int spins = 0;
@@ -289,6 +318,7 @@ struct GemmTcArgs {
 	int ngroups;
 	int tile_end[3];
 	int col0[3];
+	int ncols[3];                // N_g (a multiple of 128; the last column tile of a group may reach past it)
 	const float *scales[3];      // [N_g]
 	float *C[3];                 // [M] rows of ldc[g] floats    (nsplit == 1: scaled result)
 	int ldc[3];                  // row stride of C (>= N_g; lets a GEMM write a column block of a wider row)
@@ -305,50 +335,61 @@ struct GemmTcArgs {
 	int *err;
 };
 
+template <int MT, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap0,
                                                                  const __grid_constant__ CUtensorMap wmap1,
                                                                  const __grid_constant__ CUtensorMap wmap2, GemmTcArgs a) {
+	using SH = TcShape<MT, BN>;
+	constexpr int NA = SH::NA, NB = SH::NB;
 	extern __shared__ uint8_t tc_smem_raw[];
 	uint8_t *smem = reinterpret_cast<uint8_t *>((uintptr_t(tc_smem_raw) + 1023) & ~uintptr_t(1023));
-	__shared__ uint64_t full_bar[TC_STAGES];   // A tiles + W tile landed (transaction bytes)
-	__shared__ uint64_t conv_bar[TC_STAGES];   // W converted to bf16 (4 converter warps arrive)
-	__shared__ uint64_t free_bar[TC_STAGES];   // MMAs that read the stage have completed (tcgen05.commit)
+	__shared__ uint64_t afull_bar[TcShape<MT, BN>::NA];  // A tiles of the stage landed (transaction bytes)
+	__shared__ uint64_t afree_bar[TcShape<MT, BN>::NA];  // the MMAs that read the A stage have completed (tcgen05.commit)
+	__shared__ uint64_t wfull_bar[TcShape<MT, BN>::NB];  // int8 W tile landed
+	__shared__ uint64_t conv_bar[TcShape<MT, BN>::NB];   // W converted to bf16 (4 converter warps arrive)
+	__shared__ uint64_t bfree_bar[TcShape<MT, BN>::NB];  // the MMAs that read the bf16 tile have completed
 	__shared__ uint64_t acc_bar;               // all MMAs done: accumulators ready
 	__shared__ uint32_t tmem_base_s;
 	__shared__ int s_fail;
-	__shared__ int s_issued;  // k-blocks whose loads have been issued
+	__shared__ int s_issued_a, s_issued_w;  // k-blocks whose loads have been issued
 	__shared__ int s_last, s_cnt;
 
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int grp = (int(blockIdx.x) >= a.tile_end[0]) + (int(blockIdx.x) >= a.tile_end[1]);  // tile_end of unused groups = INT_MAX
-	const int n0 = (int(blockIdx.x) - (grp == 0 ? 0 : (grp == 1 ? a.tile_end[0] : a.tile_end[1]))) * TC_BN;  // column inside the group's matrix
+	const int n0 = (int(blockIdx.x) - (grp == 0 ? 0 : (grp == 1 ? a.tile_end[0] : a.tile_end[1]))) * BN;  // column inside the group's matrix
 	// (selects over constant indices: a run-time index into the parameter arrays would move them to local memory)
 	const int pcol = (grp == 0 ? a.col0[0] : (grp == 1 ? a.col0[1] : a.col0[2])) + n0;  // column inside a partial-sum row
 	const CUtensorMap *wmap = grp == 0 ? &wmap0 : (grp == 1 ? &wmap1 : &wmap2);
 	float *const Cg = grp == 0 ? a.C[0] : (grp == 1 ? a.C[1] : a.C[2]);
 	const float *const scg = grp == 0 ? a.scales[0] : (grp == 1 ? a.scales[1] : a.scales[2]);
 	const int ldcg = grp == 0 ? a.ldc[0] : (grp == 1 ? a.ldc[1] : a.ldc[2]);
-	const int mt0 = blockIdx.y * TC_MT;
-	const int nmt = min(TC_MT, a.m_tiles - mt0);  // row tiles this CTA really has
+	const int ncg = grp == 0 ? a.ncols[0] : (grp == 1 ? a.ncols[1] : a.ncols[2]);
+	const int mt0 = blockIdx.y * MT;
+	const int nmt = min(MT, a.m_tiles - mt0);  // row tiles this CTA really has
 	const int k_blocks_all = a.K / TC_BK;
 	const int k_blocks = k_blocks_all / a.nsplit;   // this CTA's share of K
 	const int kb_first = blockIdx.z * k_blocks;
 	const size_t term_stride = size_t(a.m_tiles) * k_blocks_all * TC_TILE_BYTES;  // bytes
 
 	if (tid == 0) {
-		for (int s = 0; s < TC_STAGES; s++) {
-			mbar_init(&full_bar[s], 1);
+		for (int s = 0; s < NA; s++) {
+			mbar_init(&afull_bar[s], 1);
+			mbar_init(&afree_bar[s], 1);
+		}
+		for (int s = 0; s < NB; s++) {
+			mbar_init(&wfull_bar[s], 1);
 			mbar_init(&conv_bar[s], 4);
-			mbar_init(&free_bar[s], 1);
+			mbar_init(&bfree_bar[s], 1);
 		}
 		mbar_init(&acc_bar, 1);
 		s_fail = 0;
-		s_issued = 0;
+		s_issued_a = 0;
+		s_issued_w = 0;
 		s_last = -1;
 		s_cnt = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
-	if (warp == 1) {  // TMEM: (2 row tiles) x (2 K halves) accumulators of 128 fp32 columns
+	if (warp == 1) {  // TMEM: (MT row tiles) x (2 K halves) accumulators of BN fp32 columns = 512 columns
 		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512)
 		             : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -358,49 +399,60 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 	tc_fence_after();
 	const uint32_t tmem_base = tmem_base_s;
 
-	auto stage_a = [&](int s, int term, int mt) { return smem + size_t(s) * TC_STAGE_BYTES + (term * TC_MT + mt) * TC_TILE_BYTES; };
-	auto stage_w = [&](int s) { return smem + size_t(s) * TC_STAGE_BYTES + 3 * TC_MT * TC_TILE_BYTES; };
-	auto stage_b = [&](int s) { return smem + size_t(s) * TC_STAGE_BYTES + 3 * TC_MT * TC_TILE_BYTES + TC_W_BYTES; };
+	auto stage_a = [&](int s, int term, int mt) { return smem + size_t(s) * SH::A_BYTES + (term * MT + mt) * TC_TILE_BYTES; };
+	auto stage_w = [&](int s) { return smem + size_t(NA) * SH::A_BYTES + size_t(s) * SH::W_BYTES; };
+	auto stage_b = [&](int s) { return smem + size_t(NA) * SH::A_BYTES + size_t(NB) * SH::W_BYTES + size_t(s) * SH::B_BYTES; };
 
 	if (warp == 0) {
-		// ------------------------------------------------------------ producer
+		// ------------------------------------------------------------ producer of the A stages
 		if (lane == 0) {
-			const uint64_t pol = l2_evict_first_policy();
 			for (int kb = 0; kb < k_blocks; kb++) {
-				const int s = kb % TC_STAGES, use = kb / TC_STAGES;
-				if (use > 0 && !tc_wait(&free_bar[s], (use - 1) & 1, a.err)) { s_fail = 1; break; }
-				fence_proxy_async();
-				mbar_expect_tx(&full_bar[s], uint32_t(3 * nmt * TC_TILE_BYTES + TC_W_BYTES));
+				const int s = kb % NA, use = kb / NA;
+				if (use > 0 && !tc_wait(&afree_bar[s], (use - 1) & 1, a.err)) { s_fail = 1; break; }
+				mbar_expect_tx(&afull_bar[s], uint32_t(3 * nmt * TC_TILE_BYTES));
 				for (int term = 0; term < 3; term++)
 					for (int mt = 0; mt < nmt; mt++) {
 						const int mtg = mt0 + mt;
 						const uint8_t *src = reinterpret_cast<const uint8_t *>(a.apack) + term * term_stride +
 						                     (size_t(mtg) * k_blocks_all + kb_first + kb) * TC_TILE_BYTES;
-						bulk_load(stage_a(s, term, mt), src, TC_TILE_BYTES, &full_bar[s]);
+						bulk_load(stage_a(s, term, mt), src, TC_TILE_BYTES, &afull_bar[s]);
 					}
-				tma_load_2d(stage_w(s), wmap, n0, (kb_first + kb) * TC_BK, &full_bar[s], pol);
-				s_issued = kb + 1;
+				s_issued_a = kb + 1;
+			}
+		}
+	} else if (warp == 6) {
+		// ------------------------------------------------------------ producer of the int8 W tiles
+		if (lane == 0) {
+			const uint64_t pol = l2_evict_first_policy();
+			for (int kb = 0; kb < k_blocks; kb++) {
+				const int s = kb % NB, use = kb / NB;
+				// the slot's int8 tile was converted and its bf16 tile read by the MMAs of the previous use
+				if (use > 0 && !tc_wait(&bfree_bar[s], (use - 1) & 1, a.err)) { s_fail = 1; break; }
+				fence_proxy_async();
+				mbar_expect_tx(&wfull_bar[s], uint32_t(SH::W_BYTES));
+				tma_load_2d(stage_w(s), wmap, n0, (kb_first + kb) * TC_BK, &wfull_bar[s], pol);
+				s_issued_w = kb + 1;
 			}
 		}
 	} else if (warp == 1) {
 		// ------------------------------------------------------------ MMA issuer
 		if (lane == 0) {
-			const uint32_t idesc = tc_idesc();
+			const uint32_t idesc = tc_idesc(BN);
 			for (int kb = 0; kb < k_blocks; kb++) {
-				const int s = kb % TC_STAGES, use = kb / TC_STAGES;
-				if (!tc_wait(&full_bar[s], use & 1, a.err) || !tc_wait(&conv_bar[s], use & 1, a.err)) { s_fail = 1; break; }
+				const int sa = kb % NA, ua = kb / NA, sb = kb % NB, ub = kb / NB;
+				if (!tc_wait(&conv_bar[sb], ub & 1, a.err) || !tc_wait(&afull_bar[sa], ua & 1, a.err)) { s_fail = 1; break; }
 				tc_fence_after();
-				const uint32_t b_addr = smem_u32(stage_b(s));
+				const uint32_t b_addr = smem_u32(stage_b(sb));
 				const int kb_half = (a.halves == 2) ? (k_blocks + 1) / 2 : k_blocks;  // first K-block of the second accumulator
 				const bool second = kb >= kb_half;
 				const bool first_of_acc = (kb == 0) || (kb == kb_half);
 #pragma unroll
-				for (int mt = 0; mt < TC_MT; mt++) {
+				for (int mt = 0; mt < MT; mt++) {
 					if (mt < nmt) {  // (a predicate, not a break: the loop stays fully unrolled — one thread issues every MMA)
-						const uint32_t d_tmem = tmem_base + uint32_t(mt * TC_BN) + (second ? uint32_t(TC_MT * TC_BN) : 0u);
+						const uint32_t d_tmem = tmem_base + uint32_t(mt * BN) + (second ? uint32_t(MT * BN) : 0u);
 #pragma unroll
 						for (int term = 0; term < 3; term++) {
-							const uint32_t a_addr = smem_u32(stage_a(s, term, mt));
+							const uint32_t a_addr = smem_u32(stage_a(sa, term, mt));
 #pragma unroll
 							for (int j = 0; j < TC_BK / 16; j++) {
 								const uint32_t acc = (!first_of_acc || term > 0 || j > 0) ? 1u : 0u;
@@ -409,32 +461,51 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 						}
 					}
 				}
-				tc_commit(&free_bar[s]);  // arrives when the MMAs above have read the stage
+				// both arrive when the MMAs above have read their operands
+				tc_commit(&afree_bar[sa]);
+				tc_commit(&bfree_bar[sb]);
 			}
 			tc_commit(&acc_bar);
 		}
 	} else {
 		// ------------------------------------------------------------ converters (warps 2..5, 128 threads)
-		const int ct = tid - 64;  // 0..127 = column n of the W tile
 		for (int kb = 0; kb < k_blocks; kb++) {
-			const int s = kb % TC_STAGES, use = kb / TC_STAGES;
-			bool ok = tc_wait(&full_bar[s], use & 1, a.err);
-			// the bf16 tile of this stage was last read by the MMAs of use-1, which free_bar covers;
-			// the producer waited for it before refilling the stage, so full_bar implies it
+			const int s = kb % NB, use = kb / NB;
+			// the slot's bf16 tile was last read by the MMAs of the previous use; the W producer waited for
+			// them (bfree_bar) before it refilled the slot, so wfull_bar implies the tile may be overwritten
+			bool ok = tc_wait(&wfull_bar[s], use & 1, a.err);
 			if (!ok) { s_fail = 1; break; }
 			const uint8_t *w = stage_w(s);
 			uint8_t *b = stage_b(s);
+			// The bf16 tile is N-major like W itself: a core matrix is 8 k-rows of 8 consecutive columns
+			// (16 bytes each); byte offset of (k, n) = (n/8)*512 + (k/8)*128 + (k%8)*16 + (n%8)*2. One work
+			// item = 8 consecutive int8 of one k-row (one 8-byte load) -> 8 bf16 (one 16-byte store). A warp
+			// takes one group of 8 k-rows; its lanes cover the column groups, and the k-row of a lane rotates
+			// with the lane index, so the loads (16 lanes: 16 different column groups) and the stores
+			// (8 lanes: 8 different k-rows of a core matrix) are both free of bank conflicts.
+			constexpr int G = BN / 8;        // column groups: 16 or 32
+			constexpr int SUB = 32 / G;      // k-rows a warp covers per pass: 2 or 1
+			const int kg = (warp - 2);       // this warp's group of 8 k-rows
+			const int g = lane % G;
+			uint2 raw[8 / SUB];
 #pragma unroll
-			for (int kc = 0; kc < TC_BK / 8; kc++) {
+			for (int it = 0; it < 8 / SUB; it++) {
+				const int kk = (g + it * SUB + lane / G) & 7;
+				raw[it] = *reinterpret_cast<const uint2 *>(w + (kg * 8 + kk) * BN + 8 * g);
+			}
+#pragma unroll
+			for (int it = 0; it < 8 / SUB; it++) {
+				const int kk = (g + it * SUB + lane / G) & 7;
 				__align__(16) __nv_bfloat162 v[4];
 #pragma unroll
 				for (int i = 0; i < 4; i++) {
-					const uint32_t u0 = w[(kc * 8 + 2 * i) * TC_BN + ct], u1 = w[(kc * 8 + 2 * i + 1) * TC_BN + ct];
+					const uint32_t word = (i < 2) ? raw[it].x : raw[it].y;
+					const uint32_t u0 = (word >> (16 * (i & 1))) & 0xFFu, u1 = (word >> (16 * (i & 1) + 8)) & 0xFFu;
 					const float f0 = __uint_as_float(0x4B000000u | (u0 ^ 0x80u)) - 8388736.0f;
 					const float f1 = __uint_as_float(0x4B000000u | (u1 ^ 0x80u)) - 8388736.0f;
 					v[i] = __floats2bfloat162_rn(f0, f1);  // |int8| <= 128: exact in bf16
 				}
-				*reinterpret_cast<uint4 *>(b + (ct / 8) * 512 + kc * 128 + (ct % 8) * 16) = *reinterpret_cast<const uint4 *>(v);
+				*reinterpret_cast<uint4 *>(b + g * 512 + kg * 128 + kk * 16) = *reinterpret_cast<const uint4 *>(v);
 			}
 			fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
 			__syncwarp();
@@ -444,63 +515,65 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 		if (!*(volatile int *)&s_fail && tc_wait(&acc_bar, 0, a.err)) {
 			tc_fence_after();
 			const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
-#pragma unroll 1
-			for (int mt = 0; mt < nmt; mt++) {
-				const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
-#pragma unroll 1
-				for (int c = 0; c < TC_BN / 32; c++) {
-					uint32_t r[32], r2[32];
-					const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(mt * TC_BN + c * 32);
-					const bool two = a.halves == 2 && k_blocks > 1;  // second accumulator in use
-					// both accumulators are requested before the single wait: a TMEM load + wait is ~600 clk of latency
-					asm volatile(
-					    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-					    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-					    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-					      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-					      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-					      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-					    : "r"(taddr)
-					    : "memory");
-					if (two) {
-						const uint32_t taddr2 = taddr + uint32_t(TC_MT * TC_BN);
-						asm volatile(
-						    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-						    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-						    : "=r"(r2[0]), "=r"(r2[1]), "=r"(r2[2]), "=r"(r2[3]), "=r"(r2[4]), "=r"(r2[5]), "=r"(r2[6]), "=r"(r2[7]),
-						      "=r"(r2[8]), "=r"(r2[9]), "=r"(r2[10]), "=r"(r2[11]), "=r"(r2[12]), "=r"(r2[13]), "=r"(r2[14]), "=r"(r2[15]),
-						      "=r"(r2[16]), "=r"(r2[17]), "=r"(r2[18]), "=r"(r2[19]), "=r"(r2[20]), "=r"(r2[21]), "=r"(r2[22]), "=r"(r2[23]),
-						      "=r"(r2[24]), "=r"(r2[25]), "=r"(r2[26]), "=r"(r2[27]), "=r"(r2[28]), "=r"(r2[29]), "=r"(r2[30]), "=r"(r2[31])
-						    : "r"(taddr2)
-						    : "memory");
-					}
-					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-					if (two) {
+			// the operand rings are idle now (every load landed, every MMA read its operands): a corner of
+			// them stages the output blocks, 32 x 36 floats per warp
+			float *stg = reinterpret_cast<float *>(smem) + quad * (32 * 36);
+			fence_proxy_async();
+			const bool two = a.halves == 2 && k_blocks > 1;  // second accumulator in use
+			const bool fin = a.nsplit == 1 && !a.raw;        // finished result (scaled); else raw partial sums
+			constexpr int CH = BN / 32;                      // 32-column blocks per row tile
+			// block e = (row tile e / CH, columns 32 * (e % CH) ..): request its accumulator(s) from TMEM
+			auto request = [&](int e, uint32_t (&r)[32], uint32_t (&r2)[32]) {
+				const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t((e / CH) * BN + (e % CH) * 32);
+				tc_ld32(taddr, r);
+				if (two) tc_ld32(taddr + uint32_t(MT * BN), r2);
+			};
+			auto finish = [&](int e, uint32_t (&r)[32], uint32_t (&r2)[32]) {
+				const int mt = e / CH, c = e % CH;
+				if (two) {
 #pragma unroll
-						for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
-					}
-					if ((mt0 + mt) < a.m_tiles && row < a.M) {
-						if (a.nsplit == 1 && !a.raw) {
-							float *dst = Cg + size_t(row) * ldcg + n0 + c * 32;
-							const float *sc = scg + n0 + c * 32;
-#pragma unroll
-							for (int i = 0; i < 32; i += 4) {
-								float4 o;
-								o.x = __uint_as_float(r[i]) * sc[i];
-								o.y = __uint_as_float(r[i + 1]) * sc[i + 1];
-								o.z = __uint_as_float(r[i + 2]) * sc[i + 2];
-								o.w = __uint_as_float(r[i + 3]) * sc[i + 3];
-								*reinterpret_cast<float4 *>(dst + i) = o;
-							}
-						} else {
-							float *dst = a.partial + (size_t(blockIdx.z) * a.M + row) * a.N + pcol + c * 32;
-#pragma unroll
-							for (int i = 0; i < 32; i += 4)
-								*reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
-								                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-						}
-					}
+					for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
 				}
+				if ((mt0 + mt) < a.m_tiles && n0 + c * 32 < ncg) {  // (a wide tile may reach past the group's last column)
+					// A lane holds 32 consecutive columns of ONE row; written from here, a store instruction would
+					// touch 32 rows (32 lines). The 32 x 32 block goes through shared memory instead (rows padded to
+					// 36 floats: conflict-free both ways) and leaves as 8 instructions of 4 rows x 128 contiguous bytes.
+#pragma unroll
+					for (int i = 0; i < 32; i += 4)
+						*reinterpret_cast<float4 *>(stg + lane * 36 + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+						                                                             __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+					__syncwarp();
+					const int rsub = lane >> 3, c4 = lane & 7;
+					// (raw partial sums are multiplied by 1.0f, which is exact)
+					const float4 sc4 = fin ? *reinterpret_cast<const float4 *>(scg + n0 + c * 32 + 4 * c4) : make_float4(1.f, 1.f, 1.f, 1.f);
+					float *dbase = fin ? Cg + n0 + c * 32 + 4 * c4 : a.partial + size_t(blockIdx.z) * a.M * a.N + pcol + c * 32 + 4 * c4;
+					const size_t ld = fin ? size_t(ldcg) : size_t(a.N);
+					const int row0 = (mt0 + mt) * TC_BM + quad * 32;
+#pragma unroll
+					for (int j = 0; j < 8; j++) {
+						const int rr = j * 4 + rsub;
+						float4 v = *reinterpret_cast<const float4 *>(stg + rr * 36 + 4 * c4);
+						v.x *= sc4.x;
+						v.y *= sc4.y;
+						v.z *= sc4.z;
+						v.w *= sc4.w;
+						if (row0 + rr < a.M) *reinterpret_cast<float4 *>(dbase + size_t(row0 + rr) * ld) = v;
+					}
+					__syncwarp();
+				}
+			};
+			// two register sets alternate: the TMEM load of the next block (~600 clk) runs under the stores of this one
+			uint32_t ra[32], ra2[32], rb[32], rb2[32];
+			const int ne = nmt * CH;  // even
+			request(0, ra, ra2);
+#pragma unroll 1
+			for (int e = 0; e < ne; e += 2) {
+				asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+				request(e + 1, rb, rb2);
+				finish(e, ra, ra2);
+				asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+				if (e + 2 < ne) request(e + 2, ra, ra2);
+				finish(e + 1, rb, rb2);
 			}
 			if (a.nsplit > 1 && a.tickets && !a.raw) {
 				// in-kernel split-K reduction: the CTA that arrives last at this tile's ticket sums the
@@ -527,7 +600,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 						const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
 						if (row >= a.M) continue;
 #pragma unroll 1
-						for (int c4 = 0; c4 < TC_BN / 4; c4++) {
+						for (int c4 = 0; c4 < BN / 4; c4++) {
+							if (n0 + 4 * c4 >= ncg) break;
 							float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
 							for (int s0 = 0; s0 < a.nsplit; s0 += 4) {
@@ -563,10 +637,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 	if (warp == 0 && lane == 0) {
 		// every load that was issued must have landed before the shared memory is given up
 		// (already true on the normal path; matters only after a wait ran out)
-		const int issued = *(volatile int *)&s_issued;
-		for (int kb = max(0, issued - TC_STAGES); kb < issued; kb++) {
+		const int ia = *(volatile int *)&s_issued_a, iw = *(volatile int *)&s_issued_w;
+		for (int kb = max(0, ia - NA); kb < ia; kb++) {
 			int spins = 0;
-			while (!mbar_try_wait(&full_bar[kb % TC_STAGES], (kb / TC_STAGES) & 1) && ++spins < TC_SPIN_CAP) {
+			while (!mbar_try_wait(&afull_bar[kb % NA], (kb / NA) & 1) && ++spins < TC_SPIN_CAP) {
+			}
+		}
+		for (int kb = max(0, iw - NB); kb < iw; kb++) {
+			int spins = 0;
+			while (!mbar_try_wait(&wfull_bar[kb % NB], (kb / NB) & 1) && ++spins < TC_SPIN_CAP) {
 			}
 		}
 	}

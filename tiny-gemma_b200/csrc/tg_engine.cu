@@ -1038,20 +1038,23 @@ int ensure_log(tg_state *s, int steps) {
 // K-split of the tensor-core GEMM: enough CTAs to fill the GPU, accumulation chains of at most 24
 // K-blocks (768 rows) for accuracy, as far as the partial-sum buffer allows.
 constexpr size_t TC_TICKETS = 4096;
-int tc_pick_split(int M, int K, int N, size_t partial_floats, int max_split) {
+// ctas = CTAs of one split (column tiles x row-tile groups of the chosen tile shape)
+int tc_pick_split(int ctas, int M, int K, int N, size_t partial_floats, int max_split) {
 	const int k_blocks = K / TC_BK;
-	const int ctas = (N / TC_BN) * (((M + TC_BM - 1) / TC_BM + TC_MT - 1) / TC_MT);
 	// accumulation chains are kept to <= 24 K-blocks; a CTA keeps two accumulators per tile (first / second half of
 	// its K range), so it can take up to 48 K-blocks
 	// split only while every split still fits one wave (ctas * splits <= SMs): a second, partly filled wave
 	// costs as much as the split saves
-	const int want = std::max(env_int("TG_GEMM_SPLIT_CEIL", 0) ? (g_num_sms + ctas - 1) / ctas : std::max(1, g_num_sms / ctas), (k_blocks + 47) / 48);
+	const int fit = std::max(1, env_int("TG_GEMM_SPLIT_CEIL", 0) ? (g_num_sms + ctas - 1) / ctas : g_num_sms / ctas);
+	const int need = (k_blocks + 47) / 48;
+	// the largest divisor of the K-block count that still fits one wave; if the chain limit asks for more,
+	// the smallest divisor that satisfies it
 	int best = 1;
 	for (int ns = 1; ns <= std::min(k_blocks, max_split); ns++) {
 		if (k_blocks % ns) continue;
 		if (ns > 1 && size_t(ns) * M * N > partial_floats) break;
+		if (ns > fit && best >= need) break;
 		best = ns;
-		if (ns >= want) break;
 	}
 	return best;
 }
@@ -1078,11 +1081,16 @@ int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStre
 int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const int *ldcs, int M, const TcScratch &sc,
                          cudaStream_t st, int max_split = 1 << 30, int *raw_nsplit = nullptr) {
 	static bool configured = false;
-	const size_t smem = size_t(TC_STAGES) * TC_STAGE_BYTES + 1024;
 	if (!configured) {
-		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<2, 128>::SMEM));
+		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<1, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<1, 256>::SMEM));
 		configured = true;
 	}
+	// tile shape: beyond one row tile the wide shape (one row tile x 256 columns) wins: a 256-column MMA
+	// keeps the tensor pipe busier than two of 128 and every fetched A tile is used twice as often
+	const int m_tiles_all = (M + TC_BM - 1) / TC_BM;
+	const bool wide = M >= env_int("TG_GEMM_WIDE_MIN_M", 129);
+	const int bn = wide ? 256 : 128, mt_cta = wide ? 1 : 2;
 	CUtensorMap wmap[3];
 	GemmTcArgs a{};
 	ReduceGroups rg{};
@@ -1091,14 +1099,15 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 	for (int g = 0; g < 3; g++) {
 		const int gg = std::min(g, ng - 1);  // unused slots repeat the last matrix (never selected)
 		if (ws[gg]->K != K) return fail(TG_ESHAPE, "grouped GEMM: the matrices must share K");
-		TG_TRY(make_tmap(&wmap[g], ws[gg]->q, K, ws[gg]->N, TC_BN, TC_BK));
+		TG_TRY(make_tmap(&wmap[g], ws[gg]->q, K, ws[gg]->N, bn, TC_BK));
 		if (g < ng) {
 			a.col0[g] = ntot;
+			a.ncols[g] = ws[g]->N;
 			a.scales[g] = ws[g]->s;
 			a.C[g] = Cs[g];
 			a.ldc[g] = (ldcs && ldcs[g] > 0) ? ldcs[g] : ws[g]->N;
 			ntot += ws[g]->N;
-			tiles += ws[g]->N / TC_BN;
+			tiles += (ws[g]->N + bn - 1) / bn;
 			a.tile_end[g] = tiles;
 			rg.col0[g] = a.col0[g];
 			rg.scales[g] = a.scales[g];
@@ -1107,6 +1116,7 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 		} else {
 			a.col0[g] = ntot;
 			a.tile_end[g] = INT_MAX;
+			a.ncols[g] = 0;
 			a.scales[g] = a.scales[ng - 1];
 			a.C[g] = a.C[ng - 1];
 			a.ldc[g] = a.ldc[ng - 1];
@@ -1120,11 +1130,11 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 	a.M = M;
 	a.N = ntot;
 	a.K = K;
-	a.m_tiles = (M + TC_BM - 1) / TC_BM;
-	a.nsplit = tc_pick_split(M, K, ntot, sc.partial_floats, std::min(max_split, env_int("TG_GEMM_MAX_SPLIT", sc.max_split)));
+	a.m_tiles = m_tiles_all;
+	a.nsplit = tc_pick_split(tiles * ((m_tiles_all + mt_cta - 1) / mt_cta), M, K, ntot, sc.partial_floats, std::min(max_split, env_int("TG_GEMM_MAX_SPLIT", sc.max_split)));
 	a.partial = sc.partial;
 	a.err = sc.err;
-	dim3 grid(tiles, (a.m_tiles + TC_MT - 1) / TC_MT, a.nsplit);
+	dim3 grid(tiles, (a.m_tiles + mt_cta - 1) / mt_cta, a.nsplit);
 	const bool fused = !raw_nsplit && sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
 	a.tickets = fused ? sc.tickets : nullptr;
 	a.raw = raw_nsplit ? 1 : 0;
@@ -1133,7 +1143,10 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 		if (size_t(a.nsplit) * M * ntot > sc.partial_floats) return fail(TG_ENOMEM, "tensor-core GEMM partial-sum scratch too small");
 		*raw_nsplit = a.nsplit;
 	}
-	qgemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(wmap[0], wmap[1], wmap[2], a);
+	if (wide)
+		qgemm_tc_kernel<1, 256><<<grid, TC_THREADS, TcShape<1, 256>::SMEM, st>>>(wmap[0], wmap[1], wmap[2], a);
+	else
+		qgemm_tc_kernel<2, 128><<<grid, TC_THREADS, TcShape<2, 128>::SMEM, st>>>(wmap[0], wmap[1], wmap[2], a);
 	count_launch();
 	TG_TRY(check_launch("qgemm_tc"));
 	if (a.nsplit > 1 && !fused && !raw_nsplit) {
