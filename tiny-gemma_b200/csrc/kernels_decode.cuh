@@ -488,12 +488,32 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
 	}
 	const float *row = a.qkv + size_t(b) * (AT_NH * AT_HD + 2 * AT_HD);
 	if (a.qkv_nsplit > 0) {
-		__shared__ float rowbuf[AT_NH * AT_HD + 2 * AT_HD];
+		__shared__ __align__(16) float rowbuf[AT_NH * AT_HD + 2 * AT_HD];
 		constexpr int NQ = AT_NH * AT_HD + 2 * AT_HD;
-		for (int n = tid; n < NQ; n += AT_THREADS) {
-			const float acc = sum_splits(a.qkv + size_t(b) * NQ + n, size_t(a.qkv_B) * NQ, a.qkv_nsplit);
-			const float sc = n < AT_NH * AT_HD ? a.sq[n] : (n < AT_NH * AT_HD + AT_HD ? a.sk[n - AT_NH * AT_HD] : a.sv[n - AT_NH * AT_HD - AT_HD]);
-			rowbuf[n] = acc * sc;
+		// four consecutive columns x up to eight splits are requested together; the splits are added in
+		// ascending order (the order of the reduce kernel)
+		const size_t sstride = size_t(a.qkv_B) * NQ;
+		for (int n = 4 * tid; n < NQ; n += 4 * AT_THREADS) {
+			const float *p = a.qkv + size_t(b) * NQ + n;
+			float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+			for (int s0 = 0; s0 < a.qkv_nsplit; s0 += 8) {
+				float4 v[8];
+#pragma unroll
+				for (int q = 0; q < 8; q++) {
+					v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+					if (s0 + q < a.qkv_nsplit) v[q] = *reinterpret_cast<const float4 *>(p + size_t(s0 + q) * sstride);
+				}
+#pragma unroll
+				for (int q = 0; q < 8; q++) {
+					acc.x += v[q].x;
+					acc.y += v[q].y;
+					acc.z += v[q].z;
+					acc.w += v[q].w;
+				}
+			}
+			const float *sc = n < AT_NH * AT_HD ? a.sq + n : (n < AT_NH * AT_HD + AT_HD ? a.sk + (n - AT_NH * AT_HD) : a.sv + (n - AT_NH * AT_HD - AT_HD));
+			const float4 s4 = *reinterpret_cast<const float4 *>(sc);
+			*reinterpret_cast<float4 *>(&rowbuf[n]) = make_float4(acc.x * s4.x, acc.y * s4.y, acc.z * s4.z, acc.w * s4.w);
 		}
 		__syncthreads();
 		row = rowbuf;
