@@ -137,7 +137,11 @@ int tg_logits_read(tg_state *s, float *logits_host);
  * + sampler, n_steps times) run on the device without a host round trip per
  * token. first_ids_host[batch] is fed to the first step. minp >= 1 selects
  * argmax (transformer.hpp:229); else randf_host holds [n_steps, batch]
- * uniforms. toks_host receives [n_steps, batch]. */
+ * uniforms. toks_host receives [n_steps, batch]. Calls of up to 4096 tokens
+ * (n_steps * batch) move ids, uniforms and tokens through the state's pinned
+ * staging buffer and synchronise once, so n_steps = 1 per call is a per-token
+ * loop with one launch and one synchronisation per token. An id outside the
+ * vocabulary is TG_EINVAL. */
 int tg_generate(tg_state *s, const int *first_ids_host, int n_steps, float minp, float temp, const float *randf_host,
                 int *toks_host);
 

@@ -296,6 +296,17 @@ def test_device_loop_equals_stepwise(capi, model_270m, golden):
         feed = b.sample_minp(0.1, 0.7, rf[i:i + 1]).astype(np.int32)
         tb.append(int(feed[0]))
     assert list(ta) == tb
+    # one tg_generate call per token (ids and uniform through the pinned staging buffer, one
+    # synchronisation) continues both sequences identically
+    rf2 = np.random.default_rng(2).random(8, dtype=np.float32)
+    feed_a = np.array([tb[-1]], np.int32)
+    for i in range(8):
+        feed_a = a.generate(feed_a, 1, 0.1, 0.7, rf2[i:i + 1])[0]
+        b.decode(feed, want_logits=False)
+        feed = b.sample_minp(0.1, 0.7, rf2[i:i + 1]).astype(np.int32)
+        assert int(feed_a[0]) == int(feed[0])
+    with pytest.raises(capi.TgError):
+        a.generate(np.array([262144], np.int32), 1)
     a.close()
     b.close()
 

@@ -1926,14 +1926,34 @@ int tg_generate(tg_state *s, const int *first_ids, int n_steps, float minp, floa
                 int *toks_host) {
 	if (!s || !first_ids || n_steps < 1) return fail(TG_EINVAL, "bad argument");
 	TG_CUDA(cudaSetDevice(s->m->device));
+	// Short runs (a step at a time from a host loop) go through the pinned staging buffer with one
+	// synchronisation at the end: ids and uniforms in, the launch, tokens out.
+	const size_t nbytes = size_t(n_steps) * s->B * 4;
+	const bool lean = nbytes <= 16384;
+	TG_TRY(staging_acquire(s));
 	if (minp < 1.0f) {
 		if (!randf_host) return fail(TG_EINVAL, "min-p sampling needs uniforms");
-		TG_TRY(tg_state_set_randf(s, randf_host, n_steps));
+		if (lean && s->randf_cap >= n_steps) {
+			float *stage = reinterpret_cast<float *>(s->host_pin + 4096);
+			std::memcpy(stage, randf_host, nbytes);
+			TG_CUDA(cudaMemcpyAsync(s->randf, stage, nbytes, cudaMemcpyHostToDevice, s->stream));
+			TG_CUDA(cudaMemsetAsync(s->randf_count, 0, 4 * s->B, s->stream));
+		} else {
+			TG_TRY(tg_state_set_randf(s, randf_host, n_steps));
+		}
 	}
-	TG_TRY(staging_acquire(s));
+	for (int b = 0; b < s->B; b++)
+		if (first_ids[b] < 0 || first_ids[b] >= s->m->cfg.n_vocab) return fail(TG_EINVAL, "token id out of range");
 	std::memcpy(s->host_pin, first_ids, 4 * s->B);
 	TG_CUDA(cudaMemcpyAsync(s->tok, s->host_pin, 4 * s->B, cudaMemcpyHostToDevice, s->stream));
 	TG_TRY(tg_generate_async(s, n_steps, minp, temp));
+	if (toks_host && lean) {
+		// (stream order: the ids above were consumed by their copy before this one writes the buffer)
+		TG_CUDA(cudaMemcpyAsync(s->host_pin, s->tok_log, nbytes, cudaMemcpyDeviceToHost, s->stream));
+		TG_TRY(check_err_flag(s));  // synchronises
+		std::memcpy(toks_host, s->host_pin, nbytes);
+		return TG_OK;
+	}
 	if (toks_host) return tg_state_tokens(s, n_steps, toks_host);
 	TG_CUDA(cudaStreamSynchronize(s->stream));
 	return TG_OK;
