@@ -137,22 +137,23 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 		__shared__ float t_s[2048];
 		float ss = 0.0f;
 		if (nsplit > 0) {
-			// Thread tid owns d = tid, tid + 256, ... (at most 8 values). The partial sums of three splits for
-			// all of them are requested together: a row costs ceil(nsplit / 3) L2 round trips, not nsplit * 8.
+			// Thread tid owns d = tid, tid + 256, ... (at most 8 values). The partial sums of up to nine splits
+			// (the deepest split in use) for all of them are requested together: a row costs one L2 round
+			// trip, not nsplit * 8. The splits are added in ascending order.
 			float acc[8];
 #pragma unroll
 			for (int j = 0; j < 8; j++) acc[j] = 0.0f;
 			const size_t sstride = size_t(M) * ldp;
 			const float *base = t + size_t(row) * ldp + tid;
-			for (int s0 = 0; s0 < nsplit; s0 += 3) {
-				float a[3][8];
+			for (int s0 = 0; s0 < nsplit; s0 += 9) {
+				float a[9][8];
 #pragma unroll
-				for (int q = 0; q < 3; q++)
+				for (int q = 0; q < 9; q++)
 #pragma unroll
 					for (int j = 0; j < 8; j++)
 						a[q][j] = (s0 + q < nsplit && tid + 256 * j < dim) ? base[size_t(s0 + q) * sstride + 256 * j] : 0.0f;
 #pragma unroll
-				for (int q = 0; q < 3; q++)
+				for (int q = 0; q < 9; q++)
 #pragma unroll
 					for (int j = 0; j < 8; j++) acc[j] += a[q][j];
 			}
