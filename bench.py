@@ -636,8 +636,12 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the matvec sweep and the CPU baseline sample")
     ap.add_argument("--model", default=MODEL, choices=["270m", "1B"],
                     help="architecture; 1B is the benchmark configuration, 270m is the small case used for profiling")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                    help="prompt tokens; 178 is the benchmark configuration, 16384 the long-context one "
+                         "(use --no-extras: the CPU baseline sample would prefill the same prompt)")
     args = ap.parse_args()
     globals()["MODEL"] = args.model
+    globals()["PROMPT_LEN"] = args.prompt_len
     if args.impl == "reference":
         return run_reference(args)
     if args.batch > 1:

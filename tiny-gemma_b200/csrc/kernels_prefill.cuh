@@ -382,6 +382,185 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float
 	}
 }
 
+// Long prompts (the O(S^2) regime): the same CTA shape as attn_prefill_kernel (8 queries, a warp per
+// query with its four heads, 16-key tiles in shared memory), but a warp takes FOUR keys at a time:
+//  * the 16 partial dot products of a lane (4 keys x 4 heads) are reduced over the warp with a
+//    reduce-scatter butterfly (16 shuffles instead of 80): afterwards lane L holds the finished score
+//    of key (L >> 3), head (L >> 1) & 3;
+//  * the softmax state (running max, denominator) of a head lives on the lanes that own it; each lane
+//    evaluates ONE probability and one rescale factor per block (2 exp instead of 32 per lane), and
+//    the 16 probabilities and 4 rescale factors are then broadcast by index shuffles;
+//  * the output is rescaled once per block of four keys.
+// The running max advances per block instead of per key; the result equals the per-key recurrence of
+// the reference (ops.hpp:465-480) up to fp32 rounding.
+__global__ void __launch_bounds__(256) attn_prefill_blk_kernel(float *o, const float *q, const float *k, const float *v, int S,
+                                                               int is_local, int window) {
+	__shared__ __align__(16) float ks[AP_TILE][256];
+	__shared__ __align__(16) float vs[AP_TILE][256];
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	const int s0 = blockIdx.x * AP_QPB;
+	const int s = s0 + warp;              // this warp's query (may be >= S: then it only helps loading)
+	const int s_last = min(S - 1, s0 + AP_QPB - 1);
+	int cta_j0 = 0;
+	if (is_local) cta_j0 = (s0 >= window) ? s0 - window : 0;
+	int my_j0 = 0;
+	if (is_local) my_j0 = (s >= window) ? s - window : 0;
+	float4 q0[4], q1[4], o0[4], o1[4];
+#pragma unroll
+	for (int h = 0; h < 4; h++) {
+		if (s < S) {
+			const float *qr = q + size_t(s) * 1024 + h * 256;
+			q0[h] = *reinterpret_cast<const float4 *>(qr + 4 * lane);
+			q1[h] = *reinterpret_cast<const float4 *>(qr + 128 + 4 * lane);
+		} else {
+			q0[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+			q1[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+		}
+		// 1/16 = 1/sqrt(256): a power of two, exact on q (the reference scales the score, ops.hpp:463)
+		q0[h].x *= 0.0625f; q0[h].y *= 0.0625f; q0[h].z *= 0.0625f; q0[h].w *= 0.0625f;
+		q1[h].x *= 0.0625f; q1[h].y *= 0.0625f; q1[h].z *= 0.0625f; q1[h].w *= 0.0625f;
+		o0[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+		o1[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+	}
+	const int own_kk = lane >> 3;        // key of the block whose score this lane holds after the butterfly
+	float m_own = -INFINITY, l_own = 0.0f;  // softmax state of head (lane >> 1) & 3
+	float4 pk[4], pv[4];
+	auto fetch = [&](int jt) {
+#pragma unroll
+		for (int u = 0; u < 4; u++) {
+			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
+			const int j = jt + r;
+			if (j <= s_last) {
+				pk[u] = *reinterpret_cast<const float4 *>(k + size_t(j) * 256 + 4 * c4);
+				pv[u] = *reinterpret_cast<const float4 *>(v + size_t(j) * 256 + 4 * c4);
+			} else {
+				pk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+				pv[u] = pk[u];
+			}
+		}
+	};
+	fetch(cta_j0);
+	for (int jt = cta_j0; jt <= s_last; jt += AP_TILE) {
+		__syncthreads();  // previous tile fully consumed
+#pragma unroll
+		for (int u = 0; u < 4; u++) {
+			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
+			*reinterpret_cast<float4 *>(&ks[r][4 * c4]) = pk[u];
+			*reinterpret_cast<float4 *>(&vs[r][4 * c4]) = pv[u];
+		}
+		__syncthreads();
+		if (jt + AP_TILE <= s_last) fetch(jt + AP_TILE);
+		if (s >= S) continue;
+#pragma unroll 1
+		for (int r0 = 0; r0 < AP_TILE; r0 += 4) {
+			const int jb0 = jt + r0;  // first key of the block
+			if (jb0 > s || jb0 + 3 < my_j0) continue;  // no key of the block is visible to this query
+			// ---- 16 partial scores: x[kk * 4 + h]
+			float x[16];
+#pragma unroll
+			for (int kk = 0; kk < 4; kk++) {
+				const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r0 + kk][4 * lane]);
+				const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r0 + kk][128 + 4 * lane]);
+#pragma unroll
+				for (int h = 0; h < 4; h++) {
+					float t = q0[h].x * k0v.x;
+					t = fmaf(q0[h].y, k0v.y, t);
+					t = fmaf(q0[h].z, k0v.z, t);
+					t = fmaf(q0[h].w, k0v.w, t);
+					t = fmaf(q1[h].x, k1v.x, t);
+					t = fmaf(q1[h].y, k1v.y, t);
+					t = fmaf(q1[h].z, k1v.z, t);
+					t = fmaf(q1[h].w, k1v.w, t);
+					x[kk * 4 + h] = t;
+				}
+			}
+			// ---- reduce-scatter over the warp: every round halves the values a lane carries
+			float y8[8], y4[4], y2[2];
+			{
+				const bool up = lane & 16;
+#pragma unroll
+				for (int i = 0; i < 8; i++) {
+					const float send = up ? x[i] : x[i + 8], keep = up ? x[i + 8] : x[i];
+					y8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+				}
+			}
+			{
+				const bool up = lane & 8;
+#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					const float send = up ? y8[i] : y8[i + 4], keep = up ? y8[i + 4] : y8[i];
+					y4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+				}
+			}
+			{
+				const bool up = lane & 4;
+#pragma unroll
+				for (int i = 0; i < 2; i++) {
+					const float send = up ? y4[i] : y4[i + 2], keep = up ? y4[i + 2] : y4[i];
+					y2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+				}
+			}
+			float sc;
+			{
+				const bool up = lane & 2;
+				const float send = up ? y2[0] : y2[1], keep = up ? y2[1] : y2[0];
+				sc = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+			}
+			sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+			// lane L now holds the score of key jb0 + (L >> 3) for head (L >> 1) & 3
+			const int j_own = jb0 + own_kk;
+			if (j_own > s || j_own < my_j0) sc = -INFINITY;  // outside the causal / sliding window
+			// ---- softmax step of the block on the owning lanes
+			float mb = fmaxf(sc, __shfl_xor_sync(0xffffffffu, sc, 8));
+			mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+			const float mn = fmaxf(m_own, mb);            // finite: at least one key of the block is visible
+			const float corr = expf(m_own - mn);          // exp(-inf) = 0 on the first block
+			const float pr = expf(sc - mn);               // 0 for a masked key
+			float ps = pr + __shfl_xor_sync(0xffffffffu, pr, 8);
+			ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+			l_own = fmaf(l_own, corr, ps);
+			m_own = mn;
+			// ---- everyone needs the 4 rescale factors and the 16 probabilities
+			float cf[4], pa[16];
+#pragma unroll
+			for (int h = 0; h < 4; h++) cf[h] = __shfl_sync(0xffffffffu, corr, 2 * h);
+#pragma unroll
+			for (int i = 0; i < 16; i++) pa[i] = __shfl_sync(0xffffffffu, pr, 2 * i);
+#pragma unroll
+			for (int h = 0; h < 4; h++) {
+				o0[h].x *= cf[h]; o0[h].y *= cf[h]; o0[h].z *= cf[h]; o0[h].w *= cf[h];
+				o1[h].x *= cf[h]; o1[h].y *= cf[h]; o1[h].z *= cf[h]; o1[h].w *= cf[h];
+			}
+#pragma unroll
+			for (int kk = 0; kk < 4; kk++) {
+				const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r0 + kk][4 * lane]);
+				const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r0 + kk][128 + 4 * lane]);
+#pragma unroll
+				for (int h = 0; h < 4; h++) {
+					const float pp = pa[kk * 4 + h];
+					o0[h].x = fmaf(pp, v0v.x, o0[h].x);
+					o0[h].y = fmaf(pp, v0v.y, o0[h].y);
+					o0[h].z = fmaf(pp, v0v.z, o0[h].z);
+					o0[h].w = fmaf(pp, v0v.w, o0[h].w);
+					o1[h].x = fmaf(pp, v1v.x, o1[h].x);
+					o1[h].y = fmaf(pp, v1v.y, o1[h].y);
+					o1[h].z = fmaf(pp, v1v.z, o1[h].z);
+					o1[h].w = fmaf(pp, v1v.w, o1[h].w);
+				}
+			}
+		}
+	}
+	if (s >= S) return;
+#pragma unroll
+	for (int h = 0; h < 4; h++) {
+		const float inv = 1.0f / __shfl_sync(0xffffffffu, l_own, 2 * h);
+		float *orow = o + size_t(s) * 1024 + h * 256;
+		*reinterpret_cast<float4 *>(orow + 4 * lane) = make_float4(o0[h].x * inv, o0[h].y * inv, o0[h].z * inv, o0[h].w * inv);
+		*reinterpret_cast<float4 *>(orow + 128 + 4 * lane) =
+		    make_float4(o1[h].x * inv, o1[h].y * inv, o1[h].z * inv, o1[h].w * inv);
+	}
+}
+
 // Short prompts: the kernel above gives a warp one query and all four heads and walks the keys one
 // at a time, which is a long dependent chain (dot, five shuffle rounds, exp) per key on only S/8
 // CTAs. Here a warp owns one (query, head), a CTA two queries (S/2 CTAs), and four keys are scored
