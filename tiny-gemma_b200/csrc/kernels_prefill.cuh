@@ -265,6 +265,7 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
 // a key row is paid once per tile instead of once per key.
 constexpr int AP_QPB = 8;     // queries per CTA
 constexpr int AP_TILE = 16;   // keys per shared-memory tile
+constexpr int AP_BLK_SMEM = 4 * AP_TILE * 256 * 4;  // attn_prefill_blk_kernel: two K and two V tiles (dynamic shared memory)
 
 __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float *q, const float *k, const float *v, int S,
                                                            int is_local, int window) {
@@ -393,10 +394,12 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float
 //  * the output is rescaled once per block of four keys.
 // The running max advances per block instead of per key; the result equals the per-key recurrence of
 // the reference (ops.hpp:465-480) up to fp32 rounding.
-__global__ void __launch_bounds__(256) attn_prefill_blk_kernel(float *o, const float *q, const float *k, const float *v, int S,
+__global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, const float *q, const float *k, const float *v, int S,
                                                                int is_local, int window) {
-	__shared__ __align__(16) float ks[AP_TILE][256];
-	__shared__ __align__(16) float vs[AP_TILE][256];
+	// two K tiles and two V tiles (64 KiB): the next tile is copied asynchronously while this one is consumed
+	extern __shared__ __align__(16) float ap_smem[];
+	float (*ksb)[AP_TILE][256] = reinterpret_cast<float (*)[AP_TILE][256]>(ap_smem);
+	float (*vsb)[AP_TILE][256] = reinterpret_cast<float (*)[AP_TILE][256]>(ap_smem + 2 * AP_TILE * 256);
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int s0 = blockIdx.x * AP_QPB;
 	const int s = s0 + warp;              // this warp's query (may be >= S: then it only helps loading)
@@ -424,33 +427,34 @@ __global__ void __launch_bounds__(256) attn_prefill_blk_kernel(float *o, const f
 	}
 	const int own_kk = lane >> 3;        // key of the block whose score this lane holds after the butterfly
 	float m_own = -INFINITY, l_own = 0.0f;  // softmax state of head (lane >> 1) & 3
-	float4 pk[4], pv[4];
-	auto fetch = [&](int jt) {
+	// tile copy: 16 rows x 256 floats x {K, V} = 2048 x 16 bytes, 8 per thread; rows past the CTA's last
+	// key are zero-filled (source size 0 at a clamped address)
+	auto issue = [&](int jt, int buf) {
 #pragma unroll
 		for (int u = 0; u < 4; u++) {
 			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
 			const int j = jt + r;
-			if (j <= s_last) {
-				pk[u] = *reinterpret_cast<const float4 *>(k + size_t(j) * 256 + 4 * c4);
-				pv[u] = *reinterpret_cast<const float4 *>(v + size_t(j) * 256 + 4 * c4);
-			} else {
-				pk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-				pv[u] = pk[u];
-			}
+			const unsigned nbytes = (j <= s_last) ? 16u : 0u;
+			const size_t src = size_t(min(j, s_last)) * 256 + 4 * c4;
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&ksb[buf][r][4 * c4])), "l"(k + src), "r"(nbytes) : "memory");
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&vsb[buf][r][4 * c4])), "l"(v + src), "r"(nbytes) : "memory");
 		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
 	};
-	fetch(cta_j0);
-	for (int jt = cta_j0; jt <= s_last; jt += AP_TILE) {
-		__syncthreads();  // previous tile fully consumed
-#pragma unroll
-		for (int u = 0; u < 4; u++) {
-			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
-			*reinterpret_cast<float4 *>(&ks[r][4 * c4]) = pk[u];
-			*reinterpret_cast<float4 *>(&vs[r][4 * c4]) = pv[u];
+	issue(cta_j0, 0);
+	int buf = 0;
+	for (int jt = cta_j0; jt <= s_last; jt += AP_TILE, buf ^= 1) {
+		// (every thread has passed the barrier that ends the previous iteration: buffer buf ^ 1 is free)
+		if (jt + AP_TILE <= s_last) {
+			issue(jt + AP_TILE, buf ^ 1);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's copies of this thread are done
+		} else {
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
 		}
-		__syncthreads();
-		if (jt + AP_TILE <= s_last) fetch(jt + AP_TILE);
-		if (s >= S) continue;
+		__syncthreads();  // ... and everyone else's
+		float (*ks)[256] = ksb[buf];
+		float (*vs)[256] = vsb[buf];
+		if (s < S) {
 #pragma unroll 1
 		for (int r0 = 0; r0 < AP_TILE; r0 += 4) {
 			const int jb0 = jt + r0;  // first key of the block
@@ -549,6 +553,8 @@ __global__ void __launch_bounds__(256) attn_prefill_blk_kernel(float *o, const f
 				}
 			}
 		}
+		}
+		__syncthreads();  // the tile is consumed: the next iteration may overwrite the other buffer's partner
 	}
 	if (s >= S) return;
 #pragma unroll

@@ -1388,9 +1388,14 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		if (S <= env_int("TG_ATTN_SMALL_MAX", 1024))  // short prompts: one (query, head) per warp, S/2 CTAs
 			attn_prefill_small_kernel<<<(S + 1) / 2, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		else
-			if (env_int("TG_ATTN_BLOCK4", 1))  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
-				attn_prefill_blk_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
-			else
+			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
+				static bool configured = false;
+				if (!configured) {
+					TG_CUDA(cudaFuncSetAttribute(attn_prefill_blk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_BLK_SMEM));
+					configured = true;
+				}
+				attn_prefill_blk_kernel<<<(S + 7) / 8, 256, AP_BLK_SMEM, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+			} else
 				attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
 		TG_TRY(check_launch("attn_prefill"));
