@@ -1385,7 +1385,7 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		                                               s->vcache[l] + size_t(b) * slots * AT_HD, S, slots, tc.partial, ns_qkv,
 		                                               w.Q.s, w.K.s, w.V.s);
 		count_launch();
-		if (S <= env_int("TG_ATTN_SMALL_MAX", 1024))  // short prompts: one (query, head) per warp, S/2 CTAs
+		if (S <= env_int("TG_ATTN_SMALL_MAX", 384))  // short prompts: one (query, head) per warp, S/2 CTAs
 			attn_prefill_small_kernel<<<(S + 1) / 2, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
