@@ -567,11 +567,12 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 	}
 }
 
-// Short prompts: the kernel above gives a warp one query and all four heads and walks the keys one
-// at a time, which is a long dependent chain (dot, five shuffle rounds, exp) per key on only S/8
-// CTAs. Here a warp owns one (query, head), a CTA two queries (S/2 CTAs), and four keys are scored
-// together so that their shuffle chains overlap; the softmax update then runs over the four in key
-// order. Per (query, head) the arithmetic and its order are those of attn_prefill_kernel.
+// Short prompts: with one query per warp the kernels above run on only S/8 CTAs. Here a warp owns one
+// (query, head), a CTA two queries (S/2 CTAs), and four keys are taken per step as in
+// attn_prefill_blk_kernel: the four partial scores of a lane are reduce-scattered over the warp, the
+// running max advances once per block, every lane evaluates one probability, and the four
+// probabilities are broadcast. The dependent chain per step is five shuffle rounds, two for the max
+// and one exp, instead of five rounds and four sequential (max, exp, exp) updates.
 __global__ void __launch_bounds__(256) attn_prefill_small_kernel(float *o, const float *q, const float *k, const float *v,
                                                                  int S, int is_local, int window) {
 	__shared__ __align__(16) float ks[AP_TILE][256];
@@ -638,31 +639,45 @@ __global__ void __launch_bounds__(256) attn_prefill_small_kernel(float *o, const
 					t = fmaf(q1.w, k1v.w, t);
 					sc[u] = t;
 				}
-#pragma unroll
-				for (int of = 16; of > 0; of >>= 1) {
-#pragma unroll
-					for (int u = 0; u < 4; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], of);
+				// reduce-scatter over the warp (6 shuffles instead of 20): afterwards lane L holds the finished
+				// score of key j4 + (L >> 3)
+				float z;
+				{
+					const bool up = lane & 16, up8 = lane & 8;
+					const float y0 = (up ? sc[2] : sc[0]) + __shfl_xor_sync(0xffffffffu, up ? sc[0] : sc[2], 16);
+					const float y1 = (up ? sc[3] : sc[1]) + __shfl_xor_sync(0xffffffffu, up ? sc[1] : sc[3], 16);
+					z = (up8 ? y1 : y0) + __shfl_xor_sync(0xffffffffu, up8 ? y0 : y1, 8);
 				}
+				z += __shfl_xor_sync(0xffffffffu, z, 4);
+				z += __shfl_xor_sync(0xffffffffu, z, 2);
+				z += __shfl_xor_sync(0xffffffffu, z, 1);
+				if (j4 + (lane >> 3) > jb) z = -INFINITY;  // past this query's last key
+				// one softmax step for the block of four keys: the running max advances per block
+				float mb = fmaxf(z, __shfl_xor_sync(0xffffffffu, z, 8));
+				mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+				const float mn = fmaxf(m, mb);      // finite: key j4 is visible
+				const float corr = expf(m - mn);    // exp(-inf) = 0 on the first block
+				const float pr = expf(z - mn);      // this lane's key; 0 past the end
+				float p[4];
+#pragma unroll
+				for (int u = 0; u < 4; u++) p[u] = __shfl_sync(0xffffffffu, pr, 8 * u);
+				l = fmaf(l, corr, (p[0] + p[1]) + (p[2] + p[3]));
+				m = mn;
+				o0.x *= corr; o0.y *= corr; o0.z *= corr; o0.w *= corr;
+				o1.x *= corr; o1.y *= corr; o1.z *= corr; o1.w *= corr;
 #pragma unroll
 				for (int u = 0; u < 4; u++) {
-					if (j4 + u <= jb) {
-						const int r = j4 + u - jt;
-						const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r][4 * lane]);
-						const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r][128 + 4 * lane]);
-						const float mn = fmaxf(m, sc[u]);
-						const float corr = expf(m - mn);
-						const float p = expf(sc[u] - mn);
-						l = fmaf(l, corr, p);
-						o0.x = fmaf(p, v0v.x, o0.x * corr);
-						o0.y = fmaf(p, v0v.y, o0.y * corr);
-						o0.z = fmaf(p, v0v.z, o0.z * corr);
-						o0.w = fmaf(p, v0v.w, o0.w * corr);
-						o1.x = fmaf(p, v1v.x, o1.x * corr);
-						o1.y = fmaf(p, v1v.y, o1.y * corr);
-						o1.z = fmaf(p, v1v.z, o1.z * corr);
-						o1.w = fmaf(p, v1v.w, o1.w * corr);
-						m = mn;
-					}
+					const int r = min(j4 + u, jb) - jt;  // (past jb: p is 0)
+					const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r][4 * lane]);
+					const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r][128 + 4 * lane]);
+					o0.x = fmaf(p[u], v0v.x, o0.x);
+					o0.y = fmaf(p[u], v0v.y, o0.y);
+					o0.z = fmaf(p[u], v0v.z, o0.z);
+					o0.w = fmaf(p[u], v0v.w, o0.w);
+					o1.x = fmaf(p[u], v1v.x, o1.x);
+					o1.y = fmaf(p[u], v1v.y, o1.y);
+					o1.z = fmaf(p[u], v1v.z, o1.z);
+					o1.w = fmaf(p[u], v1v.w, o1.w);
 				}
 			}
 		}
