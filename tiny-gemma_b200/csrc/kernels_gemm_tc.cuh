@@ -15,11 +15,13 @@
 //                       copy.
 //   qgemm_tc_kernel     one CTA = one BN-column tile of W x MT 128-row tiles of A,
 //                       <MT, BN> = <2, 128> or <1, 256> (more rows -> grid.y). Warp
-//                       roles: warp 0 producer (bulk copies of A tiles, TMA of
-//                       the int8 W tile), warp 1 MMA issuer, warps 2-5 convert
+//                       roles: warp 0 producer of the A stages (bulk copies),
+//                       warp 6 producer of the int8 W tiles (TMA; its own,
+//                       deeper ring), warp 1 MMA issuer, warps 2-5 convert
 //                       W int8 -> bf16 into the operand layout and run the
-//                       epilogue (TMEM -> registers -> x scale -> C).
-//                       3- or 4-stage ring over K in blocks of 32. K may be split over
+//                       epilogue (TMEM -> registers -> shared memory -> x scale
+//                       -> C in row-contiguous stores).
+//                       Rings over K in blocks of 32. K may be split over
 //                       gridDim.z CTAs (raw partial sums, added in split order
 //                       and scaled by qgemm_splitk_reduce_kernel): it fills the
 //                       GPU when N/128 is small and keeps the accumulation
