@@ -408,11 +408,15 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 	if (is_local) cta_j0 = (s0 >= window) ? s0 - window : 0;
 	int my_j0 = 0;
 	if (is_local) my_j0 = (s >= window) ? s - window : 0;
+	// Slot order: a lane keeps its heads and the keys of a block in a lane-dependent order (slot ^ hperm,
+	// slot ^ kperm), chosen so that every round of the reduce-scatter below keeps the lower half of the
+	// slots and sends the upper half on every lane, without selects.
+	const int hperm = (lane >> 1) & 3, kperm = (lane >> 3) & 3;
 	float4 q0[4], q1[4], o0[4], o1[4];
 #pragma unroll
-	for (int h = 0; h < 4; h++) {
+	for (int h = 0; h < 4; h++) {  // h: head slot; the head is h ^ hperm
 		if (s < S) {
-			const float *qr = q + size_t(s) * 1024 + h * 256;
+			const float *qr = q + size_t(s) * 1024 + (h ^ hperm) * 256;
 			q0[h] = *reinterpret_cast<const float4 *>(qr + 4 * lane);
 			q1[h] = *reinterpret_cast<const float4 *>(qr + 128 + 4 * lane);
 		} else {
@@ -459,12 +463,12 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 		for (int r0 = 0; r0 < AP_TILE; r0 += 4) {
 			const int jb0 = jt + r0;  // first key of the block
 			if (jb0 > s || jb0 + 3 < my_j0) continue;  // no key of the block is visible to this query
-			// ---- 16 partial scores: x[kk * 4 + h]
+			// ---- 16 partial scores: x[key slot * 4 + head slot]
 			float x[16];
 #pragma unroll
 			for (int kk = 0; kk < 4; kk++) {
-				const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r0 + kk][4 * lane]);
-				const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r0 + kk][128 + 4 * lane]);
+				const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r0 + (kk ^ kperm)][4 * lane]);
+				const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r0 + (kk ^ kperm)][128 + 4 * lane]);
 #pragma unroll
 				for (int h = 0; h < 4; h++) {
 					float t = q0[h].x * k0v.x;
@@ -478,38 +482,17 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 					x[kk * 4 + h] = t;
 				}
 			}
-			// ---- reduce-scatter over the warp: every round halves the values a lane carries
+			// ---- reduce-scatter over the warp: every round halves the values a lane carries. The partner of a
+			// round differs in exactly the permutation bit that the round splits on, so its upper-half slot
+			// holds the same (key, head) as this lane's lower-half slot.
 			float y8[8], y4[4], y2[2];
-			{
-				const bool up = lane & 16;
 #pragma unroll
-				for (int i = 0; i < 8; i++) {
-					const float send = up ? x[i] : x[i + 8], keep = up ? x[i + 8] : x[i];
-					y8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-				}
-			}
-			{
-				const bool up = lane & 8;
+			for (int i = 0; i < 8; i++) y8[i] = x[i] + __shfl_xor_sync(0xffffffffu, x[i + 8], 16);
 #pragma unroll
-				for (int i = 0; i < 4; i++) {
-					const float send = up ? y8[i] : y8[i + 4], keep = up ? y8[i + 4] : y8[i];
-					y4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-				}
-			}
-			{
-				const bool up = lane & 4;
+			for (int i = 0; i < 4; i++) y4[i] = y8[i] + __shfl_xor_sync(0xffffffffu, y8[i + 4], 8);
 #pragma unroll
-				for (int i = 0; i < 2; i++) {
-					const float send = up ? y4[i] : y4[i + 2], keep = up ? y4[i + 2] : y4[i];
-					y2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-				}
-			}
-			float sc;
-			{
-				const bool up = lane & 2;
-				const float send = up ? y2[0] : y2[1], keep = up ? y2[1] : y2[0];
-				sc = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-			}
+			for (int i = 0; i < 2; i++) y2[i] = y4[i] + __shfl_xor_sync(0xffffffffu, y4[i + 2], 4);
+			float sc = y2[0] + __shfl_xor_sync(0xffffffffu, y2[1], 2);
 			sc += __shfl_xor_sync(0xffffffffu, sc, 1);
 			// lane L now holds the score of key jb0 + (L >> 3) for head (L >> 1) & 3
 			const int j_own = jb0 + own_kk;
@@ -527,9 +510,9 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 			// ---- everyone needs the 4 rescale factors and the 16 probabilities
 			float cf[4], pa[16];
 #pragma unroll
-			for (int h = 0; h < 4; h++) cf[h] = __shfl_sync(0xffffffffu, corr, 2 * h);
+			for (int h = 0; h < 4; h++) cf[h] = __shfl_sync(0xffffffffu, corr, 2 * (h ^ hperm));
 #pragma unroll
-			for (int i = 0; i < 16; i++) pa[i] = __shfl_sync(0xffffffffu, pr, 2 * i);
+			for (int i = 0; i < 16; i++) pa[i] = __shfl_sync(0xffffffffu, pr, 2 * (i ^ hperm));  // [key][head slot]
 #pragma unroll
 			for (int h = 0; h < 4; h++) {
 				o0[h].x *= cf[h]; o0[h].y *= cf[h]; o0[h].z *= cf[h]; o0[h].w *= cf[h];
@@ -559,8 +542,8 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 	if (s >= S) return;
 #pragma unroll
 	for (int h = 0; h < 4; h++) {
-		const float inv = 1.0f / __shfl_sync(0xffffffffu, l_own, 2 * h);
-		float *orow = o + size_t(s) * 1024 + h * 256;
+		const float inv = 1.0f / __shfl_sync(0xffffffffu, l_own, 2 * (h ^ hperm));
+		float *orow = o + size_t(s) * 1024 + (h ^ hperm) * 256;
 		*reinterpret_cast<float4 *>(orow + 4 * lane) = make_float4(o0[h].x * inv, o0[h].y * inv, o0[h].z * inv, o0[h].w * inv);
 		*reinterpret_cast<float4 *>(orow + 128 + 4 * lane) =
 		    make_float4(o1[h].x * inv, o1[h].y * inv, o1[h].z * inv, o1[h].w * inv);
