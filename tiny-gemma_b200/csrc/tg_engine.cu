@@ -11,12 +11,14 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <ctime>
 #include <string>
 #include <vector>
 
 #include "../../include/tiny_gemma_b200.h"
 #include "kernels_decode.cuh"
 #include "kernels_mega.cuh"
+#include "kernels_persist.cuh"
 #include "kernels_gemm_tc.cuh"
 #include "kernels_prefill.cuh"
 #include "kernels_sampler.cuh"
@@ -87,6 +89,11 @@ struct tg_model {
 	size_t dec_tiled_bytes = 0;
 	long dec_tiled_version = -1;
 	int dec_tiled_key[12] = {0};
+	// the same for the dp4a decode kernel: layer units as 4 x 4 pieces, and the lm_head in ring-stage order
+	int8_t *ps_tiled = nullptr, *ps_lm = nullptr;
+	size_t ps_tiled_bytes = 0, ps_lm_bytes = 0;
+	long ps_tiled_version = -1;
+	int ps_tiled_key[20] = {0};
 	uint8_t *blob = nullptr;
 	size_t nbytes = 0;
 	const int8_t *wte = nullptr;
@@ -331,6 +338,12 @@ struct tg_state {
 	unsigned *mg_bar = nullptr;
 	int mega_grid = 0;
 	long long *mg_dbg = nullptr;
+	// dp4a persistent decode kernel
+	bool ps_ok = false;
+	PsArgs ps{};
+	PsLayer *d_pslayers = nullptr;
+	float *ps_ll = nullptr;
+	size_t ps_ll_bytes = 0;
 	size_t mega_smem = 0;
 };
 
@@ -920,8 +933,315 @@ int ensure_decode_tiles(tg_state *s) {
 	return TG_OK;
 }
 
+
+// ---------------------------------------------------------------- dp4a persistent decode kernel
+// Plan of one phase: column groups per unit, K-splits across CTAs and warps per group, chosen by an
+// estimate of the phase's time in clocks: the tile product (measured: about 650 clk fixed + 1 clk per
+// 55 bytes, 65 with two matrices that share the activations) plus the bytes the phase makes CTAs poll
+// (measured: about 76 clk per KB and CTA). `poll_kb(nsplit)` gives those KB for a split.
+template <class F>
+bool ps_plan(PsPhase *out, int K, int N, int nmat, int G, int max_bytes, const std::vector<int> &splits,
+             const std::vector<int> &col_blocks, int max_nq, F poll_kb) {
+	double best = 1e30;
+	for (int ns : splits) {
+		if ((K / 4) % ns) continue;
+		const int nq = K / 4 / ns;
+		if (nq > max_nq) continue;
+		for (int ng = 1; ng <= PS_NW; ng++) {
+			bool ok = (N / 4) % ng == 0;
+			for (int cb : col_blocks) ok = ok && (cb / 4) % ng == 0;  // a tile never straddles two matrices
+			if (!ok) continue;
+			const int ntiles = N / 4 / ng, units = ntiles * ns;
+			if (units > G) continue;
+			const int bytes = nmat * ng * nq * 16;
+			if (bytes > max_bytes) continue;
+			const int kp = std::max(1, std::min(PS_NW / ng, (nq + 31) / 32));
+			const double cost = 650.0 + double(bytes) / (nmat == 2 ? 65.0 : 55.0) + 76.0 * poll_kb(ns);
+			if (cost < best) {
+				best = cost;
+				*out = PsPhase{ng, nq, ns, ntiles, units, kp, (nq + kp - 1) / kp, bytes, 0};
+			}
+		}
+	}
+	return best < 1e30;
+}
+
+int persist_setup(tg_state *s) {
+	tg_model *m = s->m;
+	const tg_config &c = m->cfg;
+	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab, L = c.n_layers;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	int smem_max = 0;
+	TG_CUDA(cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
+	const int G = s->mega_grid;
+	PsArgs &a = s->ps;
+	a = PsArgs{};
+	if (c.n_head != AT_NH || c.head_dim != AT_HD || c.n_kv != 1 || D % 4 || I % 4 || D > 4 * PS_THREADS || L > PS_MAX_LAYERS)
+		return fail(TG_ESHAPE, "persistent kernel: unsupported shape");
+	const int budget = smem_max - 48 * 1024;
+	const double dkb = D * 4 / 1024.0;
+	const int csplit = env_int("TG_PS_C_SPLIT", 0), esplit = env_int("TG_PS_E_SPLIT", 0);
+	if (!ps_plan(&a.A, D, qd + 2 * kd, 1, G, budget / 6, {1, 2, 3, 4}, {qd, kd}, 1 << 20,
+	             [&](int ns) { return 3.0 * ns; }) ||
+	    !ps_plan(&a.C, qd, D, 1, G, budget / 8, csplit ? std::vector<int>{csplit} : std::vector<int>{1, 2, 4}, {}, 1 << 20,
+	             [&](int ns) { return 8.0 * (AT_NH / ns) + dkb * ns; }) ||
+	    !ps_plan(&a.Dp, D, I, 2, G, budget, {1}, {}, 1 << 20, [&](int) { return 0.0; }) ||
+	    !ps_plan(&a.E, I, D, 1, G, budget / 2, esplit ? std::vector<int>{esplit} : std::vector<int>{1, 2, 3, 4, 6, 8}, {},
+	             5 * PS_THREADS, [&](int ns) { return I * 4 / 1024.0 / ns + dkb * ns; }))
+		return fail(TG_ESHAPE, "persistent kernel: no phase plan fits");
+	a.A.cta0 = G - a.A.units;  // the attention CTAs (low indices) hold no Q|K|V unit where possible
+	// cache chunks per head; at least 8 CTAs must stay out of the attention phase (they wipe the hand-off arena)
+	const int chmax = std::max(1, std::min(PS_MAX_CH, (G - 8) / AT_NH));
+	a.nch_local = std::min(chmax, env_int("TG_PS_NCH_LOCAL", 8));
+	a.nch_mid = std::min(chmax, env_int("TG_PS_NCH_MID", 16));
+	a.nch_long = std::min(chmax, env_int("TG_PS_NCH_LONG", 32));
+	const int npres = G - a.E.units;
+	if (D / 4 + npres > PS_THREADS || G < 16) return fail(TG_ESHAPE, "persistent kernel: grid too small for the down-projection plan");
+	// lm_head: tiles of 24 column groups (two per warp); ring stages of at most ~40 KB
+	a.lm_groups = 2 * PS_NW;
+	a.lm_cq = D / 4;
+	for (int n = 1; n <= 16; n++)
+		if ((D / 4) % n == 0 && a.lm_groups * (D / 4 / n) * 16 <= 40 * 1024) {
+			a.lm_cq = D / 4 / n;
+			break;
+		}
+	a.lm_nchunk = D / 4 / a.lm_cq;
+	a.lm_ntiles = (V + a.lm_groups * 4 - 1) / (a.lm_groups * 4);
+	a.lm_stage_bytes = a.lm_groups * a.lm_cq * 16;
+	auto up = [](int v) { return (v + 127) & ~127; };
+	int off = 0;
+	a.off_A = off;
+	off = up(off + a.A.bytes);
+	a.off_C = off;
+	off = up(off + a.C.bytes);
+	a.off_D = off;
+	a.off_E = off + a.Dp.bytes;  // contiguous with the up/gate region: the lm_head ring and the sampler staging overlay both
+	const int region = std::max(std::max(a.Dp.bytes + a.E.bytes, 3072 * 4), std::min(3 * a.lm_stage_bytes, smem_max / 2));
+	off = up(off + region);
+	a.lm_stages = std::min(8, region / a.lm_stage_bytes);
+	if (a.lm_stages < 2) return fail(TG_ESHAPE, "persistent kernel: lm_head ring does not fit");
+	a.off_h = off;
+	off = up(off + D * 4);
+	a.xd_words = std::max(std::max(D / 4, a.E.nq), qd / 4);
+	a.off_xd = off;
+	off = up(off + 3 * a.xd_words * 4);
+	a.off_att = off;
+	off = up(off + (PS_NW * AT_HD + 4 * AT_HD) * 4);
+	a.smem_total = off + 128;
+	{
+		const int region_floats = region / 4;
+		a.samp_ch = std::min(region_floats, 24576) / 3072 * 3072;
+		if (a.samp_ch < 3072) return fail(TG_ESHAPE, "persistent kernel: sampler staging does not fit");
+	}
+	cudaFuncAttributes fa{};
+	TG_CUDA(cudaFuncGetAttributes(&fa, decode_persist_kernel<true>));
+	if (a.smem_total + int(fa.sharedSizeBytes) > smem_max) return fail(TG_ESHAPE, "persistent kernel does not fit in shared memory");
+
+	std::vector<PsLayer> lys(L);
+	for (int l = 0; l < L; l++) {
+		const LayerW &w = m->layers[l];
+		PsLayer &ly = lys[l];
+		ly.sq = w.Q.s;
+		ly.sk = w.K.s;
+		ly.sv = w.V.s;
+		ly.so = w.O.s;
+		ly.su = w.U.s;
+		ly.sg = w.G.s;
+		ly.sd = w.Dn.s;
+		ly.rmsq = w.rmsq;
+		ly.rmsk = w.rmsk;
+		ly.attn_pre = w.attn_pre;
+		ly.attn_post = w.attn_post;
+		ly.mlp_pre = w.mlp_pre;
+		ly.mlp_post = w.mlp_post;
+		ly.kcache = s->kcache[l];
+		ly.vcache = s->vcache[l];
+		ly.slots = s->slots[l];
+		ly.is_local = w.is_local ? 1 : 0;
+	}
+	TG_CUDA(cudaMalloc(&s->d_pslayers, lys.size() * sizeof(PsLayer)));
+	TG_CUDA(cudaMemcpy(s->d_pslayers, lys.data(), lys.size() * sizeof(PsLayer), cudaMemcpyHostToDevice));
+	a.tl_A = 0;
+	a.tl_C = a.tl_A + size_t(a.A.units) * a.A.bytes;
+	a.tl_D = a.tl_C + size_t(a.C.units) * a.C.bytes;
+	a.tl_E = a.tl_D + size_t(a.Dp.units) * a.Dp.bytes;
+	a.tl_layer = a.tl_E + size_t(a.E.units) * a.E.bytes;
+	auto up4 = [](int n) { return (n + 3) & ~3; };
+	a.ll_qkv = 0;
+	a.ll_att = up4(qd + 2 * kd);
+	a.ll_op = a.ll_att + AT_NH * PS_MAX_CH * PS_ATT_ROW;
+	a.ll_act = a.ll_op + a.C.nsplit * D;
+	a.ll_dn = a.ll_act + I;
+	a.ll_pres = a.ll_dn + a.E.nsplit * D;
+	a.ll_stride = up4(a.ll_pres + npres + 4);
+	s->ps_ll_bytes = size_t(3) * a.ll_stride * 4;
+	TG_CUDA(cudaMalloc(&s->ps_ll, s->ps_ll_bytes));
+	TG_CUDA(cudaMemset(s->ps_ll, 0xFF, s->ps_ll_bytes));
+	a.layers = s->d_pslayers;
+	a.L = L;
+	a.D = D;
+	a.I = I;
+	a.V = V;
+	a.QD = qd;
+	a.KD = kd;
+	a.lm_scale = m->lm_head.s;
+	a.final_norm = m->final_norm;
+	a.wte = m->wte;
+	a.wte_s = m->wte_s;
+	a.sqrtD = float(std::sqrt(double(D)));
+	a.ll = s->ps_ll;
+	a.logits = s->logits;
+	a.probs = s->mg_probs;
+	a.samp_f = s->mg_samp_f;
+	a.samp_i = s->mg_samp_i;
+	a.xnorm_out = s->xnorm;
+	a.bar = s->mg_bar;
+	a.err = s->err_flag;
+	a.tok = s->tok;
+	a.next_pos = s->next_pos;
+	a.ring_base = s->ring_base;
+	a.log_count = s->log_count;
+	a.randf_count = s->randf_count;
+	TG_CUDA(cudaFuncSetAttribute(decode_persist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, a.smem_total));
+	TG_CUDA(cudaFuncSetAttribute(decode_persist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, a.smem_total));
+	int per_sm = 0;
+	TG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_persist_kernel<true>, PS_THREADS, a.smem_total));
+	if (per_sm < 1 || G > per_sm * g_num_sms) return fail(TG_ESHAPE, "persistent kernel cannot be co-resident");
+	s->ps_ok = true;
+	if (env_int("TG_MEGA_VERBOSE", 0))
+		fprintf(stderr,
+		        "[tg] persist plan: A %dg x%d nq%d kp%d (%d units)  C %dg x%d nq%d kp%d (%d)  D %dg nq%d kp%d (%d)  E %dg x%d nq%d kp%d (%d)  "
+		        "lm cq %d x%d stages %d  smem %d + %d B  grid %d\n",
+		        a.A.ngroups, a.A.nsplit, a.A.nq, a.A.kp, a.A.units, a.C.ngroups, a.C.nsplit, a.C.nq, a.C.kp, a.C.units, a.Dp.ngroups,
+		        a.Dp.nq, a.Dp.kp, a.Dp.units, a.E.ngroups, a.E.nsplit, a.E.nq, a.E.kp, a.E.units, a.lm_cq, a.lm_nchunk, a.lm_stages,
+		        a.smem_total, int(fa.sharedSizeBytes), G);
+	return TG_OK;
+}
+
+// Build (or refresh after a reload of the weights) the model's copies in the kernel's unit order:
+// per layer the units of phase A (q|k|v), C (O projection), D (up pieces followed by the gate pieces of
+// the same columns) and E (down projection), and the lm_head in ring-stage order.
+int ensure_persist_tiles(tg_state *s) {
+	tg_model *m = s->m;
+	const PsArgs &a = s->ps;
+	const tg_config &c = m->cfg;
+	const int L = c.n_layers, V = c.n_vocab;
+	const int qd = c.n_head * c.head_dim, kd = c.n_kv * c.head_dim;
+	const int key[20] = {a.A.ngroups, a.A.nsplit, a.A.nq, a.C.ngroups, a.C.nsplit, a.C.nq, a.Dp.ngroups, a.Dp.nq, a.E.ngroups, a.E.nsplit,
+	                     a.E.nq,      a.lm_groups, a.lm_cq, a.lm_ntiles, L, a.D, a.I, V, 0, 0};
+	if (m->ps_tiled && m->ps_tiled_version == m->weights_version && std::memcmp(key, m->ps_tiled_key, sizeof key) == 0) return TG_OK;
+	const size_t bytes = a.tl_layer * L;
+	const size_t lm_bytes = size_t(a.lm_ntiles) * a.lm_nchunk * a.lm_stage_bytes;
+	if (m->ps_tiled_bytes != bytes) {
+		cudaFree(m->ps_tiled);
+		m->ps_tiled = nullptr;
+		TG_CUDA(cudaMalloc(&m->ps_tiled, bytes));
+		m->ps_tiled_bytes = bytes;
+	}
+	if (m->ps_lm_bytes != lm_bytes) {
+		cudaFree(m->ps_lm);
+		m->ps_lm = nullptr;
+		TG_CUDA(cudaMalloc(&m->ps_lm, lm_bytes));
+		m->ps_lm_bytes = lm_bytes;
+	}
+	cudaStream_t st = s->stream;
+	auto run = [&](int8_t *dst, const QW &w, const PsPhase &ph, int tile0, size_t dst_off) {
+		retile_quads_kernel<<<4 * g_num_sms, 256, 0, st>>>(dst, w.q, w.N, ph.ngroups, ph.nq, ph.nsplit, ph.ntiles, tile0,
+		                                                   w.N / 4 / ph.ngroups, size_t(ph.bytes), dst_off);
+		count_launch();
+	};
+	for (int l = 0; l < L; l++) {
+		const LayerW &w = m->layers[l];
+		int8_t *base = m->ps_tiled + size_t(l) * a.tl_layer;
+		run(base + a.tl_A, w.Q, a.A, 0, 0);
+		run(base + a.tl_A, w.K, a.A, qd / 4 / a.A.ngroups, 0);
+		run(base + a.tl_A, w.V, a.A, (qd + kd) / 4 / a.A.ngroups, 0);
+		run(base + a.tl_C, w.O, a.C, 0, 0);
+		run(base + a.tl_D, w.U, a.Dp, 0, 0);
+		run(base + a.tl_D, w.G, a.Dp, 0, size_t(a.Dp.ngroups) * a.Dp.nq * 16);
+		run(base + a.tl_E, w.Dn, a.E, 0, 0);
+	}
+	retile_lm_kernel<<<8 * g_num_sms, 256, 0, st>>>(m->ps_lm, m->lm_head.q, V, a.lm_groups, a.lm_cq, a.lm_nchunk, a.lm_ntiles);
+	count_launch();
+	TG_TRY(check_launch("retile"));
+	std::memcpy(m->ps_tiled_key, key, sizeof key);
+	m->ps_tiled_version = m->weights_version;
+	return TG_OK;
+}
+
+int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, bool log_tokens) {
+	tg_model *m = s->m;
+	TG_TRY(ensure_persist_tiles(s));
+	PsArgs a = s->ps;
+	a.tiled = m->ps_tiled;
+	a.lm_tiled = m->ps_lm;
+	a.rope[0][0] = m->rope[0][0];
+	a.rope[0][1] = m->rope[0][1];
+	a.rope[1][0] = m->rope[1][0];
+	a.rope[1][1] = m->rope[1][1];
+	a.lut = make_lut(m);
+	a.n_steps = n_steps;
+	a.sampler = sampler;
+	a.minp = minp;
+	a.temp = temp;
+	a.randf = s->randf;
+	a.randf_cap = s->randf_cap;
+	a.tok_log = log_tokens ? s->tok_log : nullptr;
+	a.log_cap = s->log_cap;
+	a.dbg = s->mg_dbg;
+	a.dbg_cap = s->mg_dbg ? 4096 : 0;
+	a.dbg_cta = std::min(std::max(env_int("TG_MEGA_DBG_CTA", 0), 0), s->mega_grid - 1);
+	a.wait_clocks = (long long)(std::max(1, env_int("TG_PS_WAIT_MS", 100))) * 2000000ll;  // ~2 GHz
+	a.fault_cta = env_int("TG_PS_WITHHOLD_CTA", -1);
+	a.poll_ns = std::max(0, env_int("TG_PS_POLL_NS", 20));
+	a.sched = env_int("TG_PS_SCHED", 0);
+	a.dbg_flags = env_int("TG_PS_DBG_FLAGS", 0);
+	// every word of the hand-off arena starts as "empty" (all ones)
+	TG_CUDA(cudaMemsetAsync(s->ps_ll, 0xFF, s->ps_ll_bytes, s->stream));
+	TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
+	// TG_PS_BEACON=1: every warp leaves progress marks in mapped host memory; if the launch has not finished
+	// after two seconds the marks are printed (where each CTA's slowest and fastest warp stand)
+	static int *beacon_host = nullptr, *beacon_dev = nullptr;
+	const bool beacon = env_int("TG_PS_BEACON", 0) != 0;
+	if (beacon && !beacon_host) {
+		TG_CUDA(cudaHostAlloc(&beacon_host, 1024 * 16 * 4, cudaHostAllocMapped));
+		TG_CUDA(cudaHostGetDevicePointer(&beacon_dev, beacon_host, 0));
+	}
+	if (beacon) std::memset(beacon_host, 0, 1024 * 16 * 4);
+	a.beacon = beacon ? beacon_dev : nullptr;
+	void *params[] = {&a};
+	// the instrumented instantiation runs only while the phase-clock recorder or the progress marks are armed
+	const void *fn = (a.dbg || a.beacon) ? (const void *)decode_persist_kernel<true> : (const void *)decode_persist_kernel<false>;
+	TG_CUDA(cudaLaunchCooperativeKernel(fn, dim3(s->mega_grid), dim3(PS_THREADS), params, size_t(a.smem_total), s->stream));
+	count_launch();
+	TG_TRY(check_launch("decode_persist"));
+	if (beacon) {
+		for (int ms = 0; ms < 2000 && cudaStreamQuery(s->stream) == cudaErrorNotReady; ms++) {
+			struct timespec ts = {0, 1000000};
+			nanosleep(&ts, nullptr);
+		}
+		if (cudaStreamQuery(s->stream) == cudaErrorNotReady) {
+			fprintf(stderr, "[tg] persistent kernel still running after 2 s; marks (layer count : phase mark) per CTA, min..max over its warps:\n");
+			for (int c = 0; c < s->mega_grid; c++) {
+				int lo = INT_MAX, hi = 0;
+				for (int w = 0; w < PS_NW; w++) {
+					lo = std::min(lo, beacon_host[c * 16 + w]);
+					hi = std::max(hi, beacon_host[c * 16 + w]);
+				}
+				fprintf(stderr, " %d=%d:%02x..%d:%02x", c, lo >> 8, lo & 0xFF, hi >> 8, hi & 0xFF);
+				if (c % 8 == 7) fprintf(stderr, "\n");
+			}
+			fprintf(stderr, "\n");
+			fflush(stderr);
+		}
+		cudaGetLastError();
+	}
+	return TG_OK;
+}
+
 // one cooperative launch: n_steps tokens; sampler 0 none / 1 argmax / 2 min-p
 int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, bool log_tokens) {
+	if (s->ps_ok) return persist_launch(s, n_steps, sampler, minp, temp, log_tokens);
 	tg_model *m = s->m;
 	TG_TRY(ensure_decode_tiles(s));
 	MgArgs a = s->mega;
@@ -1016,6 +1336,12 @@ int check_err_flag(tg_state *s) {
 	flag = s->host_pin[8192];
 	if (flag) {
 		cudaMemsetAsync(s->err_flag, 0, 4, s->stream);
+		if (flag > 0xFF) {  // the persistent kernel reports where it gave up above the code
+			const int where = flag >> 8;
+			const char *what = (flag & 0xFF) == 3 ? "bulk-copy" : ((flag & 0xFF) == 4 ? "grid-barrier" : "hand-off");
+			return fail(TG_ECUDA, std::string("persistent kernel: a ") + what + " wait ran out (layer " + std::to_string(where >> 4) +
+			                          ", phase " + std::to_string(where & 15) + ")");
+		}
 		if (flag == 1) return fail(TG_EINVAL, "token id out of range");
 		if (flag == 2) return fail(TG_ESTATE, "global KV cache full (max_pos_global reached)");
 		if (flag == 6) return fail(TG_ECUDA, "tensor-core GEMM: a pipeline wait ran out");
@@ -1528,6 +1854,8 @@ int tg_model_free(tg_model *m) {
 	cudaSetDevice(m->device);
 	cudaFree(m->blob);
 	cudaFree(m->dec_tiled);
+	cudaFree(m->ps_tiled);
+	cudaFree(m->ps_lm);
 	for (int i = 0; i < 2; i++)
 		for (int j = 0; j < 2; j++) cudaFree(m->rope[i][j]);
 	cudaFree(m->gelu);
@@ -1675,6 +2003,12 @@ int tg_state_create(tg_model *m, int batch, int max_pos_global, tg_state **out) 
 		if (mrc != TG_OK) {
 			if (env_int("TG_MEGA", 1) == 2) rc = mrc;  // 2 = required
 			s->mega_ok = false;
+		} else if (env_int("TG_PERSIST", 0)) {
+			int prc = persist_setup(s);
+			if (prc != TG_OK) {
+				if (env_int("TG_PERSIST", 0) == 2) rc = prc;  // 2 = required
+				s->ps_ok = false;
+			}
 		}
 	}
 	if (rc != TG_OK) {
@@ -1731,6 +2065,8 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->mg_samp_i);
 	cudaFree(s->mg_bar);
 	cudaFree(s->mg_dbg);
+	cudaFree(s->d_pslayers);
+	cudaFree(s->ps_ll);
 	if (s->host_pin) cudaFreeHost(s->host_pin);
 	if (s->stream) cudaStreamDestroy(s->stream);
 	delete s;
