@@ -127,6 +127,7 @@ struct PsArgs {
 	long long wait_clocks;  // SM clocks before a wait gives up
 	int poll_ns;            // sleep between two rounds of a hand-off poll
 	int sched;              // 0: up/gate and down units of layer l+1 requested in phase E of layer l; 1: units of layer l requested after the Q|K|V product of layer l
+	long long *gt;  // optional: [CTA][12] global-timer marks of one layer (DBG instantiation)
 	int dbg_flags;  // DBG instantiation: bit 0 = run the up/gate product twice (stamps both: cold vs warm code)
 	int *beacon;    // optional (mapped host memory): [CTA][16] progress marks of every warp, for diagnosing a stall
 	int fault_cta;  // test hook: this CTA withholds its down-projection hand-off (-1: none); the waits then run out
@@ -166,6 +167,23 @@ __device__ __forceinline__ void ps_bulk(void *dst, const void *src, uint32_t byt
 	    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(ps_smem(dst)),
 	    "l"(src), "r"(bytes), "r"(ps_smem(bar)), "l"(pol)
 	    : "memory");
+}
+// Small vectors that every token reads again (column scales, norm weights, RoPE rows): kept in the L2
+// (evict-last) so that they are L2 hits while the weight stream (evict-first) passes through.
+__device__ __forceinline__ uint64_t ps_evict_last() {
+	uint64_t pol;
+	asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+	return pol;
+}
+__device__ __forceinline__ float ps_ldk(const float *p, uint64_t keep) {
+	float v;
+	asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(keep));
+	return v;
+}
+__device__ __forceinline__ float4 ps_ldk4(const float *p, uint64_t keep) {
+	float4 v;
+	asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(keep));
+	return v;
 }
 __device__ __forceinline__ void ps_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void ps_prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
@@ -291,6 +309,7 @@ __device__ __forceinline__ int ps_exponent(float bound) {
 }
 __device__ __forceinline__ float ps_pow2(int e) { return __uint_as_float(uint32_t(e + 127) << 23); }
 __device__ __noinline__ void ps_quantise(float4 y, float qs, uint32_t *xd, int stride, int q) {
+	__builtin_assume(__isShared(xd));
 	int v[4];
 	v[0] = __float2int_rn(y.x * qs);
 	v[1] = __float2int_rn(y.y * qs);
@@ -383,6 +402,43 @@ __device__ __forceinline__ float ps_ldsf(uint32_t addr) {
 	return v;
 }
 __device__ __forceinline__ void ps_stsf(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+// Two groups at once: the two reductions' shuffles overlap. Lanes 0..3: (r0, r1) of column `lane`.
+__device__ __noinline__ float2 ps_finish2(const PsAcc a, const PsAcc b) {
+	const int lane = threadIdx.x & 31;
+	float v[4], u[4];
+#pragma unroll
+	for (int c = 0; c < 4; c++) {
+		const float f0 = __int_as_float(0x4B400000 + a.v[3 * c]) - 12582912.0f;
+		const float f1 = __int_as_float(0x4B400000 + a.v[3 * c + 1]) - 12582912.0f;
+		const float f2 = __int_as_float(0x4B400000 + a.v[3 * c + 2]) - 12582912.0f;
+		v[c] = fmaf(f2, 65536.0f, fmaf(f1, 256.0f, f0));
+		const float g0 = __int_as_float(0x4B400000 + b.v[3 * c]) - 12582912.0f;
+		const float g1 = __int_as_float(0x4B400000 + b.v[3 * c + 1]) - 12582912.0f;
+		const float g2 = __int_as_float(0x4B400000 + b.v[3 * c + 2]) - 12582912.0f;
+		u[c] = fmaf(g2, 65536.0f, fmaf(g1, 256.0f, g0));
+	}
+	{
+		const bool up = lane & 16;
+		const float s0 = up ? v[0] : v[2], s1 = up ? v[1] : v[3], t0 = up ? u[0] : u[2], t1 = up ? u[1] : u[3];
+		const float k0 = up ? v[2] : v[0], k1 = up ? v[3] : v[1], m0 = up ? u[2] : u[0], m1 = up ? u[3] : u[1];
+		v[0] = k0 + __shfl_xor_sync(0xffffffffu, s0, 16);
+		v[1] = k1 + __shfl_xor_sync(0xffffffffu, s1, 16);
+		u[0] = m0 + __shfl_xor_sync(0xffffffffu, t0, 16);
+		u[1] = m1 + __shfl_xor_sync(0xffffffffu, t1, 16);
+	}
+	{
+		const bool up = lane & 8;
+		const float s = up ? v[0] : v[1], k = up ? v[1] : v[0], t = up ? u[0] : u[1], m = up ? u[1] : u[0];
+		v[0] = k + __shfl_xor_sync(0xffffffffu, s, 8);
+		u[0] = m + __shfl_xor_sync(0xffffffffu, t, 8);
+	}
+#pragma unroll
+	for (int o = 4; o > 0; o >>= 1) {
+		v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+		u[0] += __shfl_xor_sync(0xffffffffu, u[0], o);
+	}
+	return make_float2(__shfl_sync(0xffffffffu, v[0], (lane & 3) * 8), __shfl_sync(0xffffffffu, u[0], (lane & 3) * 8));
+}
 // The warp that completes a count: every warp calls this once per round after its work; the one
 // that makes the count reach `total` gets true (and resets the counter for the next round).
 __device__ __forceinline__ bool ps_last(uint32_t cnt_s, int total) {
@@ -422,7 +478,8 @@ __device__ __noinline__ PsOut ps_product(uint32_t tile_s, int ngroups, int nq, i
 	for (int i = 0; i < 12; i++) a0.v[i] = a1.v[i] = 0;
 	const uint32_t t0 = tile_s + uint32_t(group * nq) * 16u, t1 = tile_s + uint32_t((ngroups + group) * nq) * 16u;
 	int q = part * wq + lane;
-	// two quads per round: the second round's loads are in flight while the first one's products issue
+	// two quads per round: the second quad's loads are in flight while the first one's products issue
+	// (requesting the next round's operands a round ahead was measured slower: more registers, no gain)
 #pragma unroll 1
 	for (; q + 32 < q1; q += 64) {
 		const uint32_t xa = xd_s + 4u * q;
@@ -445,8 +502,13 @@ __device__ __noinline__ PsOut ps_product(uint32_t tile_s, int ngroups, int nq, i
 		if (two) ps_mac(a1, ps_lds128(t1 + 16u * q), x0, x1, x2);
 	}
 	if (trace && lane == 0) trace[warp * 4 + 1] = clock64();
-	o.r0 = ps_finish(a0);
-	if (two) o.r1 = ps_finish(a1);
+	if (two) {
+		const float2 r = ps_finish2(a0, a1);
+		o.r0 = r.x;
+		o.r1 = r.y;
+	} else {
+		o.r0 = ps_finish(a0);
+	}
 	if (trace && lane == 0) trace[warp * 4 + 2] = clock64();
 	bool pub = true;
 	if (kp > 1) {
@@ -530,9 +592,18 @@ __device__ __forceinline__ float ps_inv_rms(float sumsq, float inv_dim) {
 // D/4) with *s_xscale = 2^(e - 23). Every CTA computes the same bits. D <= 4 * PS_THREADS. Thread t
 // owns elements 4t..4t+3, which are quad t. bred: 3 * PS_NW floats.
 __device__ __noinline__ void ps_resnorm(const PsW w, int where, int D, float *h, uint32_t *xd, float *bred, float *s_xscale,
-                                        const float *part, int nsplit, const float *pres, int npres, float4 wpost, float4 wpre,
-                                        float *x_out, long long *trace = nullptr) {
+                                        const float *part, int nsplit, const float *pres, int npres, const float *w_post,
+                                        const float *w_pre, uint64_t keep, float *x_out, long long *trace = nullptr) {
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	__builtin_assume(__isShared(h));
+	__builtin_assume(__isShared(xd));
+	__builtin_assume(__isShared(s_xscale));
+	// the norm weights are L2-resident (evict-last): requested together with the first poll loads
+	float4 wpost = make_float4(0.f, 0.f, 0.f, 0.f), wpre = wpost;
+	if (4 * tid < D) {
+		if (part) wpost = ps_ldk4(w_post + 4 * tid, keep);
+		wpre = ps_ldk4(w_pre + 4 * tid, keep);
+	}
 	const uint32_t bred_s = ps_smem(bred);
 	const float invD = 1.0f / float(D);
 	if (trace && lane == 0) trace[warp * 5] = clock64();
@@ -614,14 +685,14 @@ __device__ __noinline__ void ps_resnorm(const PsW w, int where, int D, float *h,
 struct PsRope {
 	float4 w0, w1, c0, c1, s0, s1;
 };
-__device__ __forceinline__ void ps_load_rope(PsRope &r, const float *w, const float *cosr, const float *sinr) {
+__device__ __forceinline__ void ps_load_rope(PsRope &r, const float *w, const float *cosr, const float *sinr, uint64_t keep) {
 	const int lane = threadIdx.x & 31;
-	r.w0 = __ldg(reinterpret_cast<const float4 *>(w) + lane);
-	r.w1 = __ldg(reinterpret_cast<const float4 *>(w + 128) + lane);
-	r.c0 = __ldg(reinterpret_cast<const float4 *>(cosr) + lane);
-	r.c1 = __ldg(reinterpret_cast<const float4 *>(cosr + 128) + lane);
-	r.s0 = __ldg(reinterpret_cast<const float4 *>(sinr) + lane);
-	r.s1 = __ldg(reinterpret_cast<const float4 *>(sinr + 128) + lane);
+	r.w0 = ps_ldk4(w + 4 * lane, keep);
+	r.w1 = ps_ldk4(w + 128 + 4 * lane, keep);
+	r.c0 = ps_ldk4(cosr + 4 * lane, keep);
+	r.c1 = ps_ldk4(cosr + 128 + 4 * lane, keep);
+	r.s0 = ps_ldk4(sinr + 4 * lane, keep);
+	r.s1 = ps_ldk4(sinr + 128 + 4 * lane, keep);
 }
 __device__ __forceinline__ void ps_norm_rope(const float *x, const PsRope &r, float scale, float *dst) {
 	const int lane = threadIdx.x & 31;
@@ -658,6 +729,10 @@ __device__ __forceinline__ void ps_norm_rope(const float *x, const PsRope &r, fl
 __device__ __noinline__ void ps_attn_merge(const PsW w, int where, const float *att_ll, int h0, int hp, int nch, float *scr, uint32_t *xd,
                                            float *bred, float *s_xscale) {
 	const int tid = threadIdx.x;
+	__builtin_assume(__isShared(scr));
+	__builtin_assume(__isShared(xd));
+	__builtin_assume(__isShared(bred));
+	__builtin_assume(__isShared(s_xscale));
 	const int items = hp * (AT_HD / 4);  // float4 columns
 	const int ncg = PS_THREADS / items;  // chunk groups
 	const int cg = tid / items, it = tid - cg * items;
@@ -730,6 +805,9 @@ __device__ __noinline__ void ps_attn_merge(const PsW w, int where, const float *
 // complete, quantised into xd (stride nq). nq <= 5 * PS_THREADS.
 __device__ __noinline__ void ps_act_quant(const PsW w, int where, const float *act, int nq, uint32_t *xd, float *bred, float *s_xscale) {
 	const int tid = threadIdx.x;
+	__builtin_assume(__isShared(xd));
+	__builtin_assume(__isShared(bred));
+	__builtin_assume(__isShared(s_xscale));
 	float4 v[5];
 	int spins = 0;
 	long long t0 = 0;
@@ -758,6 +836,387 @@ __device__ __noinline__ void ps_act_quant(const PsW w, int where, const float *a
 	__syncthreads();
 }
 
+// Phase B of one attention CTA = (head hh, cache slots j0 .. j1): q|k|v of this token from the hand-off
+// vector (polled), q/k norm + RoPE, append of the new row (head 0's CTA of the chunk that holds `slot`),
+// running-max softmax over the chunk (warp -> slots j0 + warp, + 12, ...; lane owns dims 4 lane.. and
+// 128 + 4 lane..), merge of the 12 warps, (o[256], m, l) published to prow. att: 16 KB of scratch,
+// wml: 3 * PS_NW floats. Reference: ops.hpp:224-370 (attention_decode), decode.hpp:203-211 (RoPE).
+__device__ __noinline__ void ps_attention(const PsW w, int where, float *kcache, float *vcache, const float *rmsq, const float *rmsk,
+                                          const float *cosr, const float *sinr, const float *qkv_ll, int QD, int hh, float *prow, int j0,
+                                          int j1, int slot, float *att, float *wml, uint64_t keep) {
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	__builtin_assume(__isShared(att));
+	__builtin_assume(__isShared(wml));
+	float *wo = att, *qraw = att + PS_NW * AT_HD, *qs = qraw + 3 * AT_HD;
+	float *wm = wml, *wl = wml + PS_NW, *we = wml + 2 * PS_NW;
+	PsRope rr;
+	if (warp < 2) ps_load_rope(rr, warp == 0 ? rmsq : rmsk, cosr, sinr, keep);
+	// The cache rows do not depend on this token's q|k|v: a warp's first two rows are requested before
+	// the poll (the new token's own row comes from shared memory later).
+	float4 kv[2][4];
+	auto load_keys = [&](int jb) {
+#pragma unroll
+		for (int u = 0; u < 2; u++) {
+			const int j = jb + PS_NW * u;
+			if (j < j1 && j != slot) {
+				const float *kr = kcache + size_t(j) * AT_HD, *vr = vcache + size_t(j) * AT_HD;
+				kv[u][0] = __ldcg(reinterpret_cast<const float4 *>(kr + 4 * lane));
+				kv[u][1] = __ldcg(reinterpret_cast<const float4 *>(kr + 128 + 4 * lane));
+				kv[u][2] = __ldcg(reinterpret_cast<const float4 *>(vr + 4 * lane));
+				kv[u][3] = __ldcg(reinterpret_cast<const float4 *>(vr + 128 + 4 * lane));
+			}
+		}
+	};
+	load_keys(j0 + warp);
+	if (tid < 3 * (AT_HD / 4)) {
+		const float *src = qkv_ll + (tid < AT_HD / 4 ? hh * AT_HD + 4 * tid : QD + 4 * (tid - AT_HD / 4));
+		float4 v;
+		int spins = 0;
+		long long t0 = 0;
+		do {
+			v = ps_ld4(src);
+		} while (!ps_ok(v) && ps_retry(w, where, spins, t0));
+		*reinterpret_cast<float4 *>(qraw + 4 * tid) = v;
+	}
+	__syncthreads();
+	float *ks = qraw + AT_HD, *vs = qraw + 2 * AT_HD;
+	// the reference scales q by 1/sqrt(256) before the dot products (ops.hpp:262,283); k is normed in place
+	if (warp < 2) ps_norm_rope(qraw + warp * AT_HD, rr, warp == 0 ? 0.0625f : 1.0f, warp == 0 ? qs : ks);
+	__syncthreads();
+	if (hh == 0 && slot >= j0 && slot < j1 && tid < 2 * (AT_HD / 4)) {
+		float *dst = (tid < AT_HD / 4 ? kcache : vcache) + size_t(slot) * AT_HD;
+		const int j = tid & (AT_HD / 4 - 1);
+		*reinterpret_cast<float4 *>(dst + 4 * j) = *reinterpret_cast<const float4 *>((tid < AT_HD / 4 ? ks : vs) + 4 * j);
+	}
+	const float4 q0 = *reinterpret_cast<const float4 *>(qs + 4 * lane);
+	const float4 q1 = *reinterpret_cast<const float4 *>(qs + 128 + 4 * lane);
+	float4 o0 = make_float4(0.f, 0.f, 0.f, 0.f), o1 = make_float4(0.f, 0.f, 0.f, 0.f);
+	float m = -INFINITY, lsum = 0.0f;
+#pragma unroll 1
+	for (int jb = j0 + warp; jb < j1; jb += 2 * PS_NW) {
+#pragma unroll
+		for (int u = 0; u < 2; u++) {
+			const int j = jb + PS_NW * u;
+			if (j >= j1) continue;
+			if (j == slot) {  // the new row: not in the cache yet for the other heads' CTAs
+				kv[u][0] = *reinterpret_cast<const float4 *>(ks + 4 * lane);
+				kv[u][1] = *reinterpret_cast<const float4 *>(ks + 128 + 4 * lane);
+				kv[u][2] = *reinterpret_cast<const float4 *>(vs + 4 * lane);
+				kv[u][3] = *reinterpret_cast<const float4 *>(vs + 128 + 4 * lane);
+			}
+			float t = q0.x * kv[u][0].x;
+			t = fmaf(q0.y, kv[u][0].y, t);
+			t = fmaf(q0.z, kv[u][0].z, t);
+			t = fmaf(q0.w, kv[u][0].w, t);
+			t = fmaf(q1.x, kv[u][1].x, t);
+			t = fmaf(q1.y, kv[u][1].y, t);
+			t = fmaf(q1.z, kv[u][1].z, t);
+			t = fmaf(q1.w, kv[u][1].w, t);
+			t = warp_sum(t);
+			const float mn = fmaxf(m, t);
+			const float corr = expf(m - mn);
+			const float pp = expf(t - mn);
+			lsum = fmaf(lsum, corr, pp);
+			o0.x = fmaf(pp, kv[u][2].x, o0.x * corr);
+			o0.y = fmaf(pp, kv[u][2].y, o0.y * corr);
+			o0.z = fmaf(pp, kv[u][2].z, o0.z * corr);
+			o0.w = fmaf(pp, kv[u][2].w, o0.w * corr);
+			o1.x = fmaf(pp, kv[u][3].x, o1.x * corr);
+			o1.y = fmaf(pp, kv[u][3].y, o1.y * corr);
+			o1.z = fmaf(pp, kv[u][3].z, o1.z * corr);
+			o1.w = fmaf(pp, kv[u][3].w, o1.w * corr);
+			m = mn;
+		}
+		load_keys(jb + 2 * PS_NW);
+	}
+	if (lane == 0) {
+		wm[warp] = m;
+		wl[warp] = lsum;
+	}
+	*reinterpret_cast<float4 *>(wo + warp * AT_HD + 4 * lane) = o0;
+	*reinterpret_cast<float4 *>(wo + warp * AT_HD + 128 + 4 * lane) = o1;
+	__syncthreads();
+	float M = -INFINITY;
+#pragma unroll
+	for (int i = 0; i < PS_NW; i++) M = fmaxf(M, wm[i]);
+	if (tid < PS_NW) we[tid] = (wm[tid] == -INFINITY) ? 0.0f : expf(wm[tid] - M);
+	__syncthreads();
+	if (tid < AT_HD) {
+		float O = 0.0f;
+#pragma unroll
+		for (int i = 0; i < PS_NW; i++) O = fmaf(wo[i * AT_HD + tid], we[i], O);
+		ps_st(prow + tid, O);
+	} else if (tid == AT_HD) {
+		float Ls = 0.0f;
+#pragma unroll
+		for (int i = 0; i < PS_NW; i++) Ls = fmaf(wl[i], we[i], Ls);
+		ps_st(prow + AT_HD, M);
+		ps_st(prow + AT_HD + 1, Ls);
+	}
+	__syncthreads();  // the scratch is reused by phase C
+}
+
+// lm_head of one token: logits[v] = lm_scale[v] * sum_k x[k] W[k,v]; this CTA takes column tiles cta, cta + G, ...;
+// a tile arrives as lm_nchunk ring stages in `ring`; warp w owns column groups 2w and 2w + 1 of every tile over
+// all of its rows. Returns this lane's best (temperature-scaled) logit and the ring's barrier parities.
+struct PsLmOut {
+	float best;
+	int best_i;
+	uint32_t plm, pemp;
+};
+__device__ __noinline__ PsLmOut ps_lm_head(const PsArgs &a, const PsW pw, uint8_t *ring, const uint32_t *xd, float xs, uint64_t *bar_lm,
+                                           uint64_t *emp_lm, uint32_t plm, uint32_t pemp, uint64_t pol, uint64_t keep) {
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int cta = blockIdx.x, G = gridDim.x, D = a.D, L = a.L;
+	__builtin_assume(__isShared(ring));
+	__builtin_assume(__isShared(xd));
+	__builtin_assume(__isShared(bar_lm));
+	__builtin_assume(__isShared(emp_lm));
+float best = -INFINITY;  // running max of this lane's (temperature-scaled) logits, lanes 0..7
+int best_i = -1;
+{
+	const int nst = a.lm_stages, nchunk = a.lm_nchunk, cq = a.lm_cq;
+	const int my_tiles = (a.lm_ntiles - cta + G - 1) / G;
+	const int total = my_tiles * nchunk;
+	const uint32_t sbytes = uint32_t(a.lm_stage_bytes);
+			auto issue_stage = [&](int q, int stg) {  // one lane
+		const int t = cta + (q / nchunk) * G, c = q % nchunk;
+		ps_issue(ring + size_t(stg) * sbytes, a.lm_tiled + (size_t(t) * nchunk + c) * sbytes, sbytes, &bar_lm[stg], pol, pw.s_abort);
+	};
+	if (tid == PS_THREADS - 32) {
+#pragma unroll 1
+		for (int s = 0; s < nst && s < total; s++) issue_stage(s, s);
+	}
+	PsAcc a0, a1;
+	float sc = 0.0f;
+	int stg = 0, c = 0, tile = cta;
+	bool lm_rdy = false;
+	const bool wact = 2 * warp < a.lm_groups;
+#pragma unroll 1
+	for (int q = 0; q < total; q++) {
+		if (c == 0) {
+#pragma unroll
+			for (int i = 0; i < 12; i++) a0.v[i] = a1.v[i] = 0;
+			const int v0 = tile * a.lm_groups * 4 + 8 * warp + lane;  // lanes 0..3: group 2w, lanes 4..7: group 2w+1
+			sc = (wact && lane < 8 && v0 < a.V) ? ps_ldk(a.lm_scale + v0, keep) : 0.0f;
+		}
+		if (!lm_rdy) ps_wait_bulk(pw, (L << 4) | 6, &bar_lm[stg], (plm >> stg) & 1u);
+		plm ^= (1u << stg);
+		{  // the next stage's barrier is tested now; its result is needed only after this stage's products
+			const int ns = (stg + 1 == nst) ? 0 : stg + 1;
+			lm_rdy = (q + 1 < total) && ps_mbar_test(&bar_lm[ns], (plm >> ns) & 1u);
+		}
+		if (wact) {
+			const uint4 *t0 = reinterpret_cast<const uint4 *>(ring + size_t(stg) * sbytes) + 2 * warp * cq;
+			const uint32_t *x = xd + c * cq;
+#pragma unroll 1
+			for (int qq = lane; qq < cq; qq += 32) {
+				const uint32_t x0 = x[qq], x1 = x[D / 4 + qq], x2 = x[2 * (D / 4) + qq];
+				ps_mac(a0, t0[qq], x0, x1, x2);
+				ps_mac(a1, t0[cq + qq], x0, x1, x2);
+			}
+		}
+		__syncwarp();
+		if (lane == 0) ps_mbar_arrive(&emp_lm[stg]);
+		if (tid == PS_THREADS - 32) {
+			const int nq = q + nst;
+			if (nq < total) {
+				ps_wait_bulk(pw, (L << 4) | 6, &emp_lm[stg], (pemp >> stg) & 1u);  // all 12 warps have left the stage
+				issue_stage(nq, stg);
+			}
+		}
+		__syncwarp();
+		pemp ^= (1u << stg);
+		if (c == nchunk - 1 && wact) {
+			const float2 r01 = ps_finish2(a0, a1);  // lanes 0..3
+			const float r1s = __shfl_sync(0xffffffffu, r01.y, lane & 3);  // every lane takes part in the shuffle
+			const float r = (lane < 4) ? r01.x : r1s;
+			const int v = tile * a.lm_groups * 4 + 8 * warp + lane;
+			if (lane < 8 && v < a.V) {
+				const float lg = (r * xs) * sc;
+				__stcg(a.logits + v, lg);
+				const float z = (a.sampler == 2) ? lg / a.temp : lg;
+				if (z > best) {  // tiles ascend, so the first maximum keeps the lowest index
+					best = z;
+					best_i = v;
+				}
+			}
+		}
+		if (++stg == nst) stg = 0;
+		if (++c == nchunk) {
+			c = 0;
+			tile += G;
+		}
+	}
+}
+	return PsLmOut{best, best_i, plm, pemp};
+}
+
+// Sampler of one token (0: none, 1: argmax, 2: min-p) over the logits row; `best`, `best_i` are this lane's
+// candidates from the lm_head. Returns the sampled token (every thread) and the grid-barrier count.
+struct PsSampOut {
+	int tok;
+	unsigned epoch;
+};
+__device__ __noinline__ PsSampOut ps_sampler(const PsArgs &a, const PsW pw, float best, int best_i, unsigned epoch, int n_logged, float *wm,
+                                             int *s_cdf, float *s_f, int *s_i, float *bred, float *cbuf) {
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int cta = blockIdx.x, G = gridDim.x, L = a.L;
+	// these are shared-memory pointers: tell the compiler, or every access through them is a generic load
+	__builtin_assume(__isShared(wm));
+	__builtin_assume(__isShared(s_cdf));
+	__builtin_assume(__isShared(s_f));
+	__builtin_assume(__isShared(s_i));
+	__builtin_assume(__isShared(bred));
+	__builtin_assume(__isShared(cbuf));
+const int wh = (L << 4) | 7;
+int next_tok = 0;
+if (a.sampler == 0) {
+	ps_grid_sync(pw, wh, a.bar, ++epoch * G);  // logits complete
+} else {
+	// CTA-local (max, argmax): value descending, index ascending; index -1 never beats a real one
+	auto better = [](float v1, int i1, float v2, int i2) {
+		if (v1 > v2) return true;
+		if (v1 < v2) return false;
+		if (i2 < 0) return i1 >= 0;
+		if (i1 < 0) return false;
+		return i1 < i2;
+	};
+#pragma unroll
+	for (int o = 16; o > 0; o >>= 1) {
+		float ov = __shfl_xor_sync(0xffffffffu, best, o);
+		int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+		if (better(ov, oi, best, best_i)) {
+			best = ov;
+			best_i = oi;
+		}
+	}
+	if (lane == 0) {
+		wm[warp] = best;
+		s_cdf[warp] = best_i;
+	}
+	__syncthreads();
+	if (tid == 0) {
+		for (int i = 1; i < PS_NW; i++)
+			if (better(wm[i], s_cdf[i], best, best_i)) {
+				best = wm[i];
+				best_i = s_cdf[i];
+			}
+		__stcg(a.samp_f + cta, best);
+		__stcg(a.samp_i + cta, best_i);
+	}
+	ps_grid_sync(pw, wh, a.bar, ++epoch * G);
+	// every CTA reduces the per-CTA results the same way (warp 0)
+	if (warp == 0) {
+		float gmax = -INFINITY;
+		int gidx = -1;
+#pragma unroll 1
+		for (int c = lane; c < G; c += 32) {
+			float v = __ldcg(a.samp_f + c);
+			int ix = __ldcg(a.samp_i + c);
+			if (better(v, ix, gmax, gidx)) {
+				gmax = v;
+				gidx = ix;
+			}
+		}
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) {
+			float ov = __shfl_xor_sync(0xffffffffu, gmax, o);
+			int oi = __shfl_xor_sync(0xffffffffu, gidx, o);
+			if (better(ov, oi, gmax, gidx)) {
+				gmax = ov;
+				gidx = oi;
+			}
+		}
+		if (lane == 0) {
+			s_f[4] = gmax;
+			s_i[0] = gidx;
+		}
+	}
+	__syncthreads();
+	const float gmax = s_f[4];
+	const int gidx = s_i[0];
+	if (a.sampler == 1) {
+		next_tok = gidx;  // ops::argmax_logits (reference ops.hpp:744-760)
+	} else {
+		// ops::minp_logits (reference ops.hpp:762-859). z = logit / temp; rowmax = gmax;
+		// p = exp(z - rowmax); maxp = exp(0) = 1 so cut = minp * 1; denom = sum of p >= cut.
+		const float cut = a.minp * expf(gmax - gmax);
+		float ds = 0.0f;
+		{
+			const int ntile = a.V / PS_SAMP_TILE;
+			const int my_tiles = (ntile - cta + G - 1) / G;
+#pragma unroll 1
+			for (int j = tid; j < my_tiles * PS_SAMP_TILE; j += PS_THREADS) {
+				const int v = (cta + (j / PS_SAMP_TILE) * G) * PS_SAMP_TILE + (j % PS_SAMP_TILE);
+				const float pv = expf(__ldcg(a.logits + v) / a.temp - gmax);
+				__stcg(a.probs + v, pv);
+				ds += (pv < cut) ? 0.0f : pv;
+			}
+		}
+		ds = block_sum<PS_NW>(ds, bred);
+		if (tid == 0) __stcg(a.samp_f + G + cta, ds);
+		ps_grid_sync(pw, wh, a.bar, ++epoch * G);
+		if (cta == 0) {
+			// denominator: per-CTA sums added in a fixed tree by warp 0
+			if (warp == 0) {
+				float dv = 0.0f;
+#pragma unroll 1
+				for (int c = lane; c < G; c += 32) dv += __ldcg(a.samp_f + G + c);
+				dv = warp_sum(dv);
+				if (lane == 0) s_f[6] = 1.0f / dv;
+			}
+			float randf = 0.0f;
+			const int rc = __ldcg(a.randf_count);
+			if (rc < a.randf_cap) randf = __ldg(a.randf + rc);
+			__syncthreads();
+			const float inv = s_f[6];
+			// inverse CDF: the first index whose sequential fp32 running sum reaches randf,
+			// evaluated exactly and in parallel (cdf_cross_block) over chunks of probabilities
+			// p = exp(z - max) * inv staged in the idle weight ring
+			const int CH = a.samp_ch;
+			if (tid == 0) {
+				s_i[1] = -1;
+				s_f[5] = 0.0f;
+			}
+			__syncthreads();
+#pragma unroll 1
+			for (int c0 = 0; c0 < a.V; c0 += CH) {
+				const int n = min(CH, a.V - c0);
+#pragma unroll 4
+				for (int i = tid * 4; i < n; i += PS_THREADS * 4) {
+					float4 v = __ldcg(reinterpret_cast<const float4 *>(a.probs + c0 + i));
+					v.x *= inv;
+					v.y *= inv;
+					v.z *= inv;
+					v.w *= inv;
+					*reinterpret_cast<float4 *>(cbuf + i) = v;
+				}
+				__syncthreads();
+				const int r = cdf_cross_block<PS_NW>(cbuf, n, &s_f[5], randf, s_cdf, c0 == 0 ? 1024 : 0);
+				if (r >= 0) {
+					if (tid == 0) s_i[1] = c0 + r;
+					break;
+				}
+			}
+			__syncthreads();
+			if (tid == 0) {
+				__stcg(a.samp_i + G, s_i[1] < 0 ? 0 : s_i[1]);
+				*a.randf_count = rc + 1;
+			}
+		}
+		ps_grid_sync(pw, wh, a.bar, ++epoch * G);
+		next_tok = __ldcg(a.samp_i + G);
+	}
+	if (cta == 0 && tid == 0) {
+		if (a.tok_log && n_logged < a.log_cap) a.tok_log[n_logged] = next_tok;
+		*a.tok = next_tok;
+	}
+	n_logged++;
+}
+	return PsSampOut{next_tok, epoch};
+}
+
 // Instrumentation of the DBG instantiation only: SM-clock stamps of one CTA along the last token,
 // and progress marks of every warp in mapped host memory (for diagnosing a stall).
 #define PS_BEACON(x)                                                                               \
@@ -765,6 +1224,26 @@ __device__ __noinline__ void ps_act_quant(const PsW w, int where, const float *a
 		if constexpr (DBG) {                                                                       \
 			if (a.beacon && lane == 0) *(volatile int *)(a.beacon + cta * 16 + warp) = (lc << 8) | (x); \
 		}                                                                                          \
+	} while (0)
+#define PS_GT(k)                                                                                        \
+	do {                                                                                                \
+		if constexpr (DBG) {                                                                            \
+			if (a.gt && tid == 0 && !more && l == L / 2) {                                              \
+				unsigned long long t_;                                                                  \
+				asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+				a.gt[cta * 12 + (k)] = (long long)t_;                                                   \
+			}                                                                                           \
+		}                                                                                               \
+	} while (0)
+#define PS_GT_WARP(k)                                                                                   \
+	do {                                                                                                \
+		if constexpr (DBG) {                                                                            \
+			if (a.gt && lane == 0 && !more && l == L / 2) {                                             \
+				unsigned long long t_;                                                                  \
+				asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+				a.gt[cta * 12 + (k)] = (long long)t_;                                                   \
+			}                                                                                           \
+		}                                                                                               \
 	} while (0)
 #define PS_STAMP()                                                       \
 	do {                                                                 \
@@ -786,14 +1265,13 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	__shared__ float s_f[8];
 	__shared__ int s_i[4];
 	__shared__ int s_cdf[2 * PS_NW + 8];
-	__shared__ float wm[PS_NW], wl[PS_NW], we[PS_NW];
+	__shared__ float wm[3 * PS_NW];  // per-warp (m, l, weight) of the attention merge; also the sampler's per-warp maxima
 	__shared__ PsLayer s_ly[PS_MAX_LAYERS];
 
 	uint8_t *R_A = smem + a.off_A, *R_C = smem + a.off_C, *R_D = smem + a.off_D, *R_E = smem + a.off_E;
 	float *h = reinterpret_cast<float *>(smem + a.off_h);
 	uint32_t *xd = reinterpret_cast<uint32_t *>(smem + a.off_xd);
 	float *att = reinterpret_cast<float *>(smem + a.off_att);  // wo[12][256] | qraw[768] (q_h, k, v) | qs[256]
-	float *wo = att, *qraw = att + PS_NW * AT_HD, *qs = qraw + 3 * AT_HD;
 	const uint32_t xd_s = ps_smem(xd), part_s = ps_smem(s_part), cnt_s = ps_smem(s_cnt);
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -824,7 +1302,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	const PsW pw{&s_abort, a.err, a.wait_clocks, unsigned(a.poll_ns)};
 	unsigned epoch = 0;  // grid barriers passed
 	uint32_t pA = 0, pC = 0, pD = 0, pE = 0, plm = 0, pemp = 0;
-	const uint64_t pol = ps_evict_first();
+	const uint64_t pol = ps_evict_first(), keep = ps_evict_last();
 
 	const int uA = cta - a.A.cta0, uC = cta - a.C.cta0, uD = cta - a.Dp.cta0, uE = cta - a.E.cta0;
 	const bool hasA = uA >= 0 && uA < a.A.units, hasC = uC >= 0 && uC < a.C.units;
@@ -832,7 +1310,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	const int tileA = hasA ? uA % a.A.ntiles : 0;
 	const int tileC = hasC ? uC % a.C.ntiles : 0, splitC = hasC ? uC / a.C.ntiles : 0;
 	const int tileE = hasE ? uE % a.E.ntiles : 0, splitE = hasE ? uE / a.E.ntiles : 0;
-	const int npres = G - a.E.units;  // CTAs without a down unit report with a presence word
 	const int presE = uE < 0 ? cta : cta - a.E.units;  // index of this CTA's presence word (if !hasE)
 	// the unit this CTA fetches for a phase of layer l (one lane issues the copy)
 	const int8_t *srcA = a.tiled + a.tl_A + size_t(hasA ? uA : 0) * a.A.bytes, *srcC = a.tiled + a.tl_C + size_t(hasC ? uC : 0) * a.C.bytes;
@@ -850,8 +1327,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	const int rbase = __ldcg(a.ring_base);
 	int n_logged = 0;
 	int dbg_n = 0;
-	float4 vA_post = make_float4(0.f, 0.f, 0.f, 0.f), vA_pre = vA_post;  // norm weights of the next A prologue (thread t: elements 4t..)
-	if (4 * tid < D) vA_pre = __ldg(reinterpret_cast<const float4 *>(s_ly[0].attn_pre) + tid);
 	// this lane's column in a product: group = warp / kp, column 4 * group + lane (lanes 0..3); active = the warp has a group
 	const bool actA = hasA && warp / a.A.kp < a.A.ngroups, actC = hasC && warp / a.C.kp < a.C.ngroups;
 	const bool actD = hasD && warp / a.Dp.kp < a.Dp.ngroups, actE = hasE && warp / a.E.kp < a.E.ngroups;
@@ -897,19 +1372,35 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 			float *const llb = a.ll + size_t(lc % 3) * a.ll_stride;
 			float *const llprev = a.ll + size_t((lc + 2) % 3) * a.ll_stride;
 			PS_BEACON(0x10);
+			PS_GT(0);
 			// ============================================================ A: QKV
-			{
-				float scA = 0.0f;  // scale of this lane's q|k|v column
-				if (actA && lane < 4) {
+			// Cold data of the whole layer (this lane's column scales, the norm weights of phase D) is requested
+			// here, a phase or more before its use: a DRAM or L2 access issued while a burst of weight copies
+			// lands can take microseconds, and a publishing warp that waits for its scale delays every consumer.
+			float scA = 0.0f, scC = 0.0f, su_r = 0.0f, sg_r = 0.0f, scE = 0.0f;
+			if (lane < 4) {
+				if (actA) {
 					const int n = colA;
-					scA = __ldg(n < a.QD ? ly.sq + n : (n < a.QD + a.KD ? ly.sk + (n - a.QD) : ly.sv + (n - a.QD - a.KD)));
+					scA = ps_ldk(n < a.QD ? ly.sq + n : (n < a.QD + a.KD ? ly.sk + (n - a.QD) : ly.sv + (n - a.QD - a.KD)), keep);
 				}
+				if (actC) scC = ps_ldk(ly.so + colC, keep);
+				if (actD) {
+					su_r = ps_ldk(ly.su + colD, keep);
+					sg_r = ps_ldk(ly.sg + colD, keep);
+				}
+				if (actE) scE = ps_ldk(ly.sd + colE, keep);
+			}
+			// The units were requested a layer ago: test their barriers early, so that the (long) latency of the
+			// test hides behind the hand-off polls instead of following them.
+			const bool rdyA = actA && ps_mbar_test(&bar_A, pA), rdyC = actC && ps_mbar_test(&bar_C, pC);
+			{
 				ps_resnorm(pw, (l << 4) | 1, D, h, xd, bred, &s_xscale, l > 0 ? llprev + a.ll_dn : nullptr, a.E.nsplit, llprev + a.ll_pres,
-				           npres, vA_post, vA_pre, nullptr);
+				           G - a.E.units, l > 0 ? s_ly[l - 1].mlp_post : nullptr, ly.attn_pre, keep, nullptr);
 				PS_STAMP();
+				PS_GT(1);
 				PS_BEACON(0x11);
 				if (actA) {
-					ps_wait_bulk(pw, (l << 4) | 1, &bar_A, pA);
+					if (!rdyA) ps_wait_bulk(pw, (l << 4) | 1, &bar_A, pA);
 					PS_STAMP();
 					const PsOut o = ps_product(ps_smem(R_A), a.A.ngroups, a.A.nq, a.A.kp, a.A.wq, false, xd_s, D / 4, part_s, cnt_s);
 					if ((o.flags & 1) && lane < 4) ps_st(llb + a.ll_qkv + colA, (o.r0 * s_xscale) * scA);
@@ -925,6 +1416,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 					if (hasE) ps_issue(R_E, srcE + size_t(l) * a.tl_layer, a.E.bytes, &bar_E, pol, &s_abort);
 				}
 				PS_STAMP();
+				PS_GT(2);
 				PS_BEACON(0x12);
 				// Wipe the arena copy of the NEXT layer. It was last used two layers ago; every CTA has
 				// finished with it: this CTA got past the prologue above, which needs the down-projection
@@ -945,158 +1437,29 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 			}
 			// ============================================================ B: attention
 			if (cta < nsA) {
-				const int hh = cta & 3, ch = cta >> 2;
 				const int chunk = (valid + nch - 1) / nch;
-				const int j0 = ch * chunk, j1 = min(valid, j0 + chunk);
-				PS_BEACON(0x20);
-				PsRope rr;
-				if (warp < 2)
-					ps_load_rope(rr, warp == 0 ? ly.rmsq : ly.rmsk, a.rope[ly.is_local][0] + size_t(p) * AT_HD,
-					             a.rope[ly.is_local][1] + size_t(p) * AT_HD);
-				// this CTA's cache rows: 1 KiB per row = 8 lines, K and V
-#pragma unroll 1
-				for (int i = tid; i < (j1 - j0) * 8; i += PS_THREADS) {
-					ps_prefetch_l2(ly.kcache + size_t(j0) * AT_HD + 32 * i);
-					ps_prefetch_l2(ly.vcache + size_t(j0) * AT_HD + 32 * i);
-				}
-				// The cache rows do not depend on this token's q|k|v: a warp's first two rows are requested before
-				// the poll (the new token's own row comes from shared memory later).
-				float4 kv[2][4];
-				auto load_keys = [&](int jb) {
-#pragma unroll
-					for (int u = 0; u < 2; u++) {
-						const int j = jb + PS_NW * u;
-						if (j < j1 && j != slot) {
-							const float *kr = ly.kcache + size_t(j) * AT_HD, *vr = ly.vcache + size_t(j) * AT_HD;
-							kv[u][0] = __ldcg(reinterpret_cast<const float4 *>(kr + 4 * lane));
-							kv[u][1] = __ldcg(reinterpret_cast<const float4 *>(kr + 128 + 4 * lane));
-							kv[u][2] = __ldcg(reinterpret_cast<const float4 *>(vr + 4 * lane));
-							kv[u][3] = __ldcg(reinterpret_cast<const float4 *>(vr + 128 + 4 * lane));
-						}
-					}
-				};
-				load_keys(j0 + warp);
-				if (tid < 3 * (AT_HD / 4)) {
-					const float *src = llb + a.ll_qkv + (tid < AT_HD / 4 ? hh * AT_HD + 4 * tid : a.QD + 4 * (tid - AT_HD / 4));
-					float4 v;
-					int spins = 0;
-					long long t0 = 0;
-					do {
-						v = ps_ld4(src);
-					} while (!ps_ok(v) && ps_retry(pw, (l << 4) | 2, spins, t0));
-					*reinterpret_cast<float4 *>(qraw + 4 * tid) = v;
-				}
-				__syncthreads();
-				PS_STAMP();
-				PS_BEACON(0x21);
-				float *ks = qraw + AT_HD, *vs = qraw + 2 * AT_HD;
-				// the reference scales q by 1/sqrt(256) before the dot products (ops.hpp:262,283); k is normed in place
-				if (warp < 2) ps_norm_rope(qraw + warp * AT_HD, rr, warp == 0 ? 0.0625f : 1.0f, warp == 0 ? qs : ks);
-				__syncthreads();
-				if (hh == 0 && slot >= j0 && slot < j1 && tid < 2 * (AT_HD / 4)) {
-					float *dst = (tid < AT_HD / 4 ? ly.kcache : ly.vcache) + size_t(slot) * AT_HD;
-					const int j = tid & (AT_HD / 4 - 1);
-					*reinterpret_cast<float4 *>(dst + 4 * j) = *reinterpret_cast<const float4 *>((tid < AT_HD / 4 ? ks : vs) + 4 * j);
-				}
-				// warp -> keys j0 + warp, + 12, ...; lane owns dims 4 lane.. and 128 + 4 lane..
-				const float4 q0 = *reinterpret_cast<const float4 *>(qs + 4 * lane);
-				const float4 q1 = *reinterpret_cast<const float4 *>(qs + 128 + 4 * lane);
-				float4 o0 = make_float4(0.f, 0.f, 0.f, 0.f), o1 = make_float4(0.f, 0.f, 0.f, 0.f);
-				float m = -INFINITY, lsum = 0.0f;
-#pragma unroll 1
-				for (int jb = j0 + warp; jb < j1; jb += 2 * PS_NW) {
-#pragma unroll
-					for (int u = 0; u < 2; u++) {
-						const int j = jb + PS_NW * u;
-						if (j >= j1) continue;
-						if (j == slot) {  // the new row: not in the cache yet for the other heads' CTAs
-							kv[u][0] = *reinterpret_cast<const float4 *>(ks + 4 * lane);
-							kv[u][1] = *reinterpret_cast<const float4 *>(ks + 128 + 4 * lane);
-							kv[u][2] = *reinterpret_cast<const float4 *>(vs + 4 * lane);
-							kv[u][3] = *reinterpret_cast<const float4 *>(vs + 128 + 4 * lane);
-						}
-						float t = q0.x * kv[u][0].x;
-						t = fmaf(q0.y, kv[u][0].y, t);
-						t = fmaf(q0.z, kv[u][0].z, t);
-						t = fmaf(q0.w, kv[u][0].w, t);
-						t = fmaf(q1.x, kv[u][1].x, t);
-						t = fmaf(q1.y, kv[u][1].y, t);
-						t = fmaf(q1.z, kv[u][1].z, t);
-						t = fmaf(q1.w, kv[u][1].w, t);
-						t = warp_sum(t);
-						const float mn = fmaxf(m, t);
-						const float corr = expf(m - mn);
-						const float pp = expf(t - mn);
-						lsum = fmaf(lsum, corr, pp);
-						o0.x = fmaf(pp, kv[u][2].x, o0.x * corr);
-						o0.y = fmaf(pp, kv[u][2].y, o0.y * corr);
-						o0.z = fmaf(pp, kv[u][2].z, o0.z * corr);
-						o0.w = fmaf(pp, kv[u][2].w, o0.w * corr);
-						o1.x = fmaf(pp, kv[u][3].x, o1.x * corr);
-						o1.y = fmaf(pp, kv[u][3].y, o1.y * corr);
-						o1.z = fmaf(pp, kv[u][3].z, o1.z * corr);
-						o1.w = fmaf(pp, kv[u][3].w, o1.w * corr);
-						m = mn;
-					}
-					load_keys(jb + 2 * PS_NW);
-				}
-				PS_STAMP();
-				PS_BEACON(0x23);
-				if (lane == 0) {
-					wm[warp] = m;
-					wl[warp] = lsum;
-				}
-				*reinterpret_cast<float4 *>(wo + warp * AT_HD + 4 * lane) = o0;
-				*reinterpret_cast<float4 *>(wo + warp * AT_HD + 128 + 4 * lane) = o1;
-				__syncthreads();
-				float M = -INFINITY;
-#pragma unroll
-				for (int i = 0; i < PS_NW; i++) M = fmaxf(M, wm[i]);
-				if (tid < PS_NW) we[tid] = (wm[tid] == -INFINITY) ? 0.0f : expf(wm[tid] - M);
-				__syncthreads();
-				float *prow = llb + a.ll_att + (size_t(hh) * PS_MAX_CH + ch) * PS_ATT_ROW;
-				if (tid < AT_HD) {
-					float O = 0.0f;
-#pragma unroll
-					for (int i = 0; i < PS_NW; i++) O = fmaf(wo[i * AT_HD + tid], we[i], O);
-					ps_st(prow + tid, O);
-				} else if (tid == AT_HD) {
-					float Ls = 0.0f;
-#pragma unroll
-					for (int i = 0; i < PS_NW; i++) Ls = fmaf(wl[i], we[i], Ls);
-					ps_st(prow + AT_HD, M);
-					ps_st(prow + AT_HD + 1, Ls);
-				}
-				__syncthreads();  // the scratch is reused by phase C
-			} else {
-				PS_STAMP();
-				PS_STAMP();
+				const int j0 = (cta >> 2) * chunk;
+				ps_attention(pw, (l << 4) | 2, ly.kcache, ly.vcache, ly.rmsq, ly.rmsk, a.rope[ly.is_local][0] + size_t(p) * AT_HD,
+				             a.rope[ly.is_local][1] + size_t(p) * AT_HD, llb + a.ll_qkv, a.QD, cta & 3,
+				             llb + a.ll_att + (size_t(cta & 3) * PS_MAX_CH + (cta >> 2)) * PS_ATT_ROW, j0, min(valid, j0 + chunk), slot, att, wm,
+				             keep);
 			}
 			PS_BEACON(0x24);
+			PS_GT(3);
 			PS_STAMP();
 			// ============================================================ C: O projection
-			float4 vD_post = make_float4(0.f, 0.f, 0.f, 0.f), vD_pre = vD_post;
-			float su_r = 0.0f, sg_r = 0.0f;
 			{
-				float scC = 0.0f;
-				if (actC && lane < 4) scC = __ldg(ly.so + colC);
-				if (4 * tid < D) {
-					vD_post = __ldg(reinterpret_cast<const float4 *>(ly.attn_post) + tid);
-					vD_pre = __ldg(reinterpret_cast<const float4 *>(ly.mlp_pre) + tid);
-				}
-				if (actD && lane < 4) {
-					su_r = __ldg(ly.su + colD);
-					sg_r = __ldg(ly.sg + colD);
-				}
 				if (hasC) {
 					const int hp = AT_NH / a.C.nsplit;
 					ps_attn_merge(pw, (l << 4) | 3, llb + a.ll_att, splitC * hp, hp, nch, att, xd, bred, &s_xscale);
 					PS_STAMP();
+					PS_GT(4);
 					PS_BEACON(0x31);
-					if (actC) ps_wait_bulk(pw, (l << 4) | 3, &bar_C, pC);
+					if (actC && !rdyC) ps_wait_bulk(pw, (l << 4) | 3, &bar_C, pC);
 					PS_STAMP();
 					const PsOut o = ps_product(ps_smem(R_C), a.C.ngroups, a.C.nq, a.C.kp, a.C.wq, false, xd_s, hp * (AT_HD / 4), part_s, cnt_s);
 					if ((o.flags & 1) && lane < 4) ps_st(llb + a.ll_op + size_t(splitC) * D + colC, (o.r0 * s_xscale) * scC);
+					if (o.flags & 2) PS_GT_WARP(10);
 					PS_STAMP();
 					if ((o.flags & 2) && nl >= 0 && lane == 0) ps_issue(R_C, srcC + size_t(nl) * a.tl_layer, a.C.bytes, &bar_C, pol, &s_abort);
 				} else {
@@ -1106,15 +1469,18 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				}
 				pC ^= 1;
 				PS_STAMP();
+				PS_GT(5);
 				PS_BEACON(0x32);
 			}
 			// ============================================================ D: up & gate + GeGLU
 			{
-				ps_resnorm(pw, (l << 4) | 4, D, h, xd, bred, &s_xscale, llb + a.ll_op, a.C.nsplit, nullptr, 0, vD_post, vD_pre, nullptr,
+				const bool rdyD = actD && ps_mbar_test(&bar_D, pD);
+				ps_resnorm(pw, (l << 4) | 4, D, h, xd, bred, &s_xscale, llb + a.ll_op, a.C.nsplit, nullptr, 0, ly.attn_post, ly.mlp_pre, keep, nullptr,
 				           (DBG && a.dbg && cta == a.dbg_cta && !more && l == L / 2) ? a.dbg + 3930 : nullptr);
 				PS_STAMP();
+				PS_GT(6);
 				PS_BEACON(0x41);
-				if (actD) ps_wait_bulk(pw, (l << 4) | 4, &bar_D, pD);
+				if (actD && !rdyD) ps_wait_bulk(pw, (l << 4) | 4, &bar_D, pD);
 				PS_STAMP();
 				if constexpr (DBG) {
 					if ((a.dbg_flags & 2) && a.dbg && cta == a.dbg_cta && !more && l == L / 2) {
@@ -1154,16 +1520,12 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				}
 				pD ^= 1;
 				PS_STAMP();
+				PS_GT(7);
 				PS_BEACON(0x42);
 			}
 			// ============================================================ E: down projection
 			{
-				float scE = 0.0f;
-				if (actE && lane < 4) scE = __ldg(ly.sd + colE);
-				if (4 * tid < D) {
-					vA_post = __ldg(reinterpret_cast<const float4 *>(ly.mlp_post) + tid);
-					vA_pre = __ldg(reinterpret_cast<const float4 *>(l + 1 < L ? s_ly[l + 1].attn_pre : a.final_norm) + tid);
-				}
+				const bool rdyE = actE && ps_mbar_test(&bar_E, pE);
 				if (hasE) {
 					ps_act_quant(pw, (l << 4) | 5, llb + a.ll_act + size_t(splitE) * a.E.nq * 4, a.E.nq, xd, bred, &s_xscale);
 				} else {
@@ -1172,12 +1534,14 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				// the up/gate region is free: request the next layer's unit now that the hand-off loads are done
 				if (a.sched == 0 && tid == 32 && hasD && l + 1 < L) ps_issue(R_D, srcD + size_t(l + 1) * a.tl_layer, a.Dp.bytes, &bar_D, pol, &s_abort);
 				PS_STAMP();
+				PS_GT(8);
 				PS_BEACON(0x51);
 				if (hasE) {
-					if (actE) ps_wait_bulk(pw, (l << 4) | 5, &bar_E, pE);
+					if (actE && !rdyE) ps_wait_bulk(pw, (l << 4) | 5, &bar_E, pE);
 					PS_STAMP();
 					const PsOut o = ps_product(ps_smem(R_E), a.E.ngroups, a.E.nq, a.E.kp, a.E.wq, false, xd_s, a.E.nq, part_s, cnt_s);
 					if ((o.flags & 1) && lane < 4 && cta != a.fault_cta) ps_st(llb + a.ll_dn + size_t(splitE) * D + colE, (o.r0 * s_xscale) * scE);
+					if (o.flags & 2) PS_GT_WARP(11);
 					PS_STAMP();
 					if (a.sched == 0 && (o.flags & 2) && l + 1 < L && lane == 0) ps_issue(R_E, srcE + size_t(l + 1) * a.tl_layer, a.E.bytes, &bar_E, pol, &s_abort);
 				} else {
@@ -1187,6 +1551,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				}
 				pE ^= 1;
 				PS_STAMP();
+				PS_GT(9);
 				PS_BEACON(0x52);
 			}
 		}
@@ -1198,236 +1563,23 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 		const int lc = step * L + L;
 		{
 			float *const lllast = a.ll + size_t((lc + 2) % 3) * a.ll_stride;
-			ps_resnorm(pw, (L << 4) | 6, D, h, xd, bred, &s_xscale, lllast + a.ll_dn, a.E.nsplit, lllast + a.ll_pres, npres, vA_post,
-			           vA_pre, cta == 0 ? a.xnorm_out : nullptr);
+			ps_resnorm(pw, (L << 4) | 6, D, h, xd, bred, &s_xscale, lllast + a.ll_dn, a.E.nsplit, lllast + a.ll_pres, G - a.E.units,
+			           s_ly[L - 1].mlp_post, a.final_norm, keep, cta == 0 ? a.xnorm_out : nullptr);
 		}
 		PS_STAMP();
 		PS_BEACON(0x61);
-		float best = -INFINITY;  // running max of this lane's (temperature-scaled) logits, lanes 0..7
-		int best_i = -1;
-		{
-			const int nst = a.lm_stages, nchunk = a.lm_nchunk, cq = a.lm_cq;
-			const int my_tiles = (a.lm_ntiles - cta + G - 1) / G;
-			const int total = my_tiles * nchunk;
-			const uint32_t sbytes = uint32_t(a.lm_stage_bytes);
-			uint8_t *ring = R_D;
-			const float xs = s_xscale;
-			auto issue_stage = [&](int q, int stg) {  // one lane
-				const int t = cta + (q / nchunk) * G, c = q % nchunk;
-				ps_issue(ring + size_t(stg) * sbytes, a.lm_tiled + (size_t(t) * nchunk + c) * sbytes, sbytes, &bar_lm[stg], pol, &s_abort);
-			};
-			if (tid == PS_THREADS - 32) {
-#pragma unroll 1
-				for (int s = 0; s < nst && s < total; s++) issue_stage(s, s);
-			}
-			PsAcc a0, a1;
-			float sc = 0.0f;
-			int stg = 0, c = 0, tile = cta;
-			const bool wact = 2 * warp < a.lm_groups;
-#pragma unroll 1
-			for (int q = 0; q < total; q++) {
-				if (c == 0) {
-#pragma unroll
-					for (int i = 0; i < 12; i++) a0.v[i] = a1.v[i] = 0;
-					const int v0 = tile * a.lm_groups * 4 + 8 * warp + lane;  // lanes 0..3: group 2w, lanes 4..7: group 2w+1
-					sc = (wact && lane < 8 && v0 < a.V) ? __ldg(a.lm_scale + v0) : 0.0f;
-				}
-				ps_wait_bulk(pw, (L << 4) | 6, &bar_lm[stg], (plm >> stg) & 1u);
-				plm ^= (1u << stg);
-				if (wact) {
-					const uint4 *t0 = reinterpret_cast<const uint4 *>(ring + size_t(stg) * sbytes) + 2 * warp * cq;
-					const uint32_t *x = xd + c * cq;
-#pragma unroll 1
-					for (int qq = lane; qq < cq; qq += 32) {
-						const uint32_t x0 = x[qq], x1 = x[D / 4 + qq], x2 = x[2 * (D / 4) + qq];
-						ps_mac(a0, t0[qq], x0, x1, x2);
-						ps_mac(a1, t0[cq + qq], x0, x1, x2);
-					}
-				}
-				__syncwarp();
-				if (lane == 0) ps_mbar_arrive(&emp_lm[stg]);
-				if (tid == PS_THREADS - 32) {
-					const int nq = q + nst;
-					if (nq < total) {
-						ps_wait_bulk(pw, (L << 4) | 6, &emp_lm[stg], (pemp >> stg) & 1u);  // all 12 warps have left the stage
-						issue_stage(nq, stg);
-					}
-				}
-				__syncwarp();
-				pemp ^= (1u << stg);
-				if (c == nchunk - 1 && wact) {
-					const float r0 = ps_finish(a0), r1 = ps_finish(a1);  // lanes 0..3
-					const float r1s = __shfl_sync(0xffffffffu, r1, lane & 3);  // every lane takes part in the shuffle
-					const float r = (lane < 4) ? r0 : r1s;
-					const int v = tile * a.lm_groups * 4 + 8 * warp + lane;
-					if (lane < 8 && v < a.V) {
-						const float lg = (r * xs) * sc;
-						__stcg(a.logits + v, lg);
-						const float z = (a.sampler == 2) ? lg / a.temp : lg;
-						if (z > best) {  // tiles ascend, so the first maximum keeps the lowest index
-							best = z;
-							best_i = v;
-						}
-					}
-				}
-				if (++stg == nst) stg = 0;
-				if (++c == nchunk) {
-					c = 0;
-					tile += G;
-				}
-			}
-		}
+		const PsLmOut lo = ps_lm_head(a, pw, R_D, xd, s_xscale, bar_lm, emp_lm, plm, pemp, pol, keep);
+		plm = lo.plm;
+		pemp = lo.pemp;
 		__syncthreads();
 
 		// ================================================================ sampler
 		PS_STAMP();
 		PS_BEACON(0x70);
-		const int wh = (L << 4) | 7;
-		int next_tok = 0;
-		if (a.sampler == 0) {
-			ps_grid_sync(pw, wh, a.bar, ++epoch * G);  // logits complete
-		} else {
-			// CTA-local (max, argmax): value descending, index ascending; index -1 never beats a real one
-			auto better = [](float v1, int i1, float v2, int i2) {
-				if (v1 > v2) return true;
-				if (v1 < v2) return false;
-				if (i2 < 0) return i1 >= 0;
-				if (i1 < 0) return false;
-				return i1 < i2;
-			};
-#pragma unroll
-			for (int o = 16; o > 0; o >>= 1) {
-				float ov = __shfl_xor_sync(0xffffffffu, best, o);
-				int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-				if (better(ov, oi, best, best_i)) {
-					best = ov;
-					best_i = oi;
-				}
-			}
-			if (lane == 0) {
-				wm[warp] = best;
-				s_cdf[warp] = best_i;
-			}
-			__syncthreads();
-			if (tid == 0) {
-				for (int i = 1; i < PS_NW; i++)
-					if (better(wm[i], s_cdf[i], best, best_i)) {
-						best = wm[i];
-						best_i = s_cdf[i];
-					}
-				__stcg(a.samp_f + cta, best);
-				__stcg(a.samp_i + cta, best_i);
-			}
-			ps_grid_sync(pw, wh, a.bar, ++epoch * G);
-			// every CTA reduces the per-CTA results the same way (warp 0)
-			if (warp == 0) {
-				float gmax = -INFINITY;
-				int gidx = -1;
-#pragma unroll 1
-				for (int c = lane; c < G; c += 32) {
-					float v = __ldcg(a.samp_f + c);
-					int ix = __ldcg(a.samp_i + c);
-					if (better(v, ix, gmax, gidx)) {
-						gmax = v;
-						gidx = ix;
-					}
-				}
-#pragma unroll
-				for (int o = 16; o > 0; o >>= 1) {
-					float ov = __shfl_xor_sync(0xffffffffu, gmax, o);
-					int oi = __shfl_xor_sync(0xffffffffu, gidx, o);
-					if (better(ov, oi, gmax, gidx)) {
-						gmax = ov;
-						gidx = oi;
-					}
-				}
-				if (lane == 0) {
-					s_f[4] = gmax;
-					s_i[0] = gidx;
-				}
-			}
-			__syncthreads();
-			const float gmax = s_f[4];
-			const int gidx = s_i[0];
-			if (a.sampler == 1) {
-				next_tok = gidx;  // ops::argmax_logits (reference ops.hpp:744-760)
-			} else {
-				// ops::minp_logits (reference ops.hpp:762-859). z = logit / temp; rowmax = gmax;
-				// p = exp(z - rowmax); maxp = exp(0) = 1 so cut = minp * 1; denom = sum of p >= cut.
-				const float cut = a.minp * expf(gmax - gmax);
-				float ds = 0.0f;
-				{
-					const int ntile = a.V / PS_SAMP_TILE;
-					const int my_tiles = (ntile - cta + G - 1) / G;
-#pragma unroll 1
-					for (int j = tid; j < my_tiles * PS_SAMP_TILE; j += PS_THREADS) {
-						const int v = (cta + (j / PS_SAMP_TILE) * G) * PS_SAMP_TILE + (j % PS_SAMP_TILE);
-						const float pv = expf(__ldcg(a.logits + v) / a.temp - gmax);
-						__stcg(a.probs + v, pv);
-						ds += (pv < cut) ? 0.0f : pv;
-					}
-				}
-				ds = block_sum<PS_NW>(ds, bred);
-				if (tid == 0) __stcg(a.samp_f + G + cta, ds);
-				ps_grid_sync(pw, wh, a.bar, ++epoch * G);
-				if (cta == 0) {
-					// denominator: per-CTA sums added in a fixed tree by warp 0
-					if (warp == 0) {
-						float dv = 0.0f;
-#pragma unroll 1
-						for (int c = lane; c < G; c += 32) dv += __ldcg(a.samp_f + G + c);
-						dv = warp_sum(dv);
-						if (lane == 0) s_f[6] = 1.0f / dv;
-					}
-					float randf = 0.0f;
-					const int rc = __ldcg(a.randf_count);
-					if (rc < a.randf_cap) randf = __ldg(a.randf + rc);
-					__syncthreads();
-					const float inv = s_f[6];
-					// inverse CDF: the first index whose sequential fp32 running sum reaches randf,
-					// evaluated exactly and in parallel (cdf_cross_block) over chunks of probabilities
-					// p = exp(z - max) * inv staged in the idle weight ring
-					float *cbuf = reinterpret_cast<float *>(R_D);
-					const int CH = a.samp_ch;
-					if (tid == 0) {
-						s_i[1] = -1;
-						s_f[5] = 0.0f;
-					}
-					__syncthreads();
-#pragma unroll 1
-					for (int c0 = 0; c0 < a.V; c0 += CH) {
-						const int n = min(CH, a.V - c0);
-#pragma unroll 4
-						for (int i = tid * 4; i < n; i += PS_THREADS * 4) {
-							float4 v = __ldcg(reinterpret_cast<const float4 *>(a.probs + c0 + i));
-							v.x *= inv;
-							v.y *= inv;
-							v.z *= inv;
-							v.w *= inv;
-							*reinterpret_cast<float4 *>(cbuf + i) = v;
-						}
-						__syncthreads();
-						const int r = cdf_cross_block<PS_NW>(cbuf, n, &s_f[5], randf, s_cdf, c0 == 0 ? 1024 : 0);
-						if (r >= 0) {
-							if (tid == 0) s_i[1] = c0 + r;
-							break;
-						}
-					}
-					__syncthreads();
-					if (tid == 0) {
-						__stcg(a.samp_i + G, s_i[1] < 0 ? 0 : s_i[1]);
-						*a.randf_count = rc + 1;
-					}
-				}
-				ps_grid_sync(pw, wh, a.bar, ++epoch * G);
-				next_tok = __ldcg(a.samp_i + G);
-			}
-			if (cta == 0 && tid == 0) {
-				if (a.tok_log && n_logged < a.log_cap) a.tok_log[n_logged] = next_tok;
-				*a.tok = next_tok;
-			}
-			n_logged++;
-		}
+		const PsSampOut so = ps_sampler(a, pw, lo.best, lo.best_i, epoch, n_logged, wm, s_cdf, s_f, s_i, bred, reinterpret_cast<float *>(R_D));
+		const int next_tok = so.tok;
+		epoch = so.epoch;
+		if (a.sampler != 0) n_logged++;
 		PS_STAMP();
 		PS_BEACON(0x7F);
 		pos += 1;
@@ -1436,10 +1588,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 		if (tid == 0 && more && a.sched == 0) {
 			if (hasD) ps_issue(R_D, srcD, a.Dp.bytes, &bar_D, pol, &s_abort);
 			if (hasE) ps_issue(R_E, srcE, a.E.bytes, &bar_E, pol, &s_abort);
-		}
-		if (more && 4 * tid < D) {
-			vA_post = make_float4(0.f, 0.f, 0.f, 0.f);
-			vA_pre = __ldg(reinterpret_cast<const float4 *>(s_ly[0].attn_pre) + tid);
 		}
 		tok = next_tok;
 		if (__syncthreads_or(*(volatile int *)&s_abort)) break;  // the whole CTA leaves together
