@@ -89,7 +89,8 @@ int tg_model_file_bytes(const tg_config *cfg, size_t *nbytes);
 
 /* decode::RoPE(Config*, is_sw), decode.hpp:118-134,176-201: the cos/sin tables
  * [n_pos, head_dim] are built by host code and handed over. is_local selects the
- * sliding-window (theta_local) table. */
+ * sliding-window (theta_local) table. n_pos must be at least the config's n_pos (the
+ * reference always builds that many rows; the kernels read row `position`), else TG_EINVAL. */
 int tg_model_set_rope(tg_model *m, int is_local, const float *cos_host, const float *sin_host, int n_pos);
 /* lut::GeLUTable{min,max,size}, ops.hpp:22-51: table built on the host. */
 int tg_model_set_gelu_table(tg_model *m, float min, float max, const float *table_host, int size);
@@ -121,6 +122,14 @@ int tg_prefill(tg_state *s, const int *ids_host, int n_tokens, float *logits_hos
  * ids_host NULL = feed the token the last tg_sample_* call produced (it is
  * still on the device). logits_host may be NULL. */
 int tg_decode(tg_state *s, const int *ids_host, float *logits_host);
+
+/* Continuation of a non-empty context (a further turn of a conversation): the n tokens of ids_host
+ * are fed one after the other through the decode path, each seeing the cache the earlier ones left, so
+ * the result equals n calls of forward_decode (transformer.hpp:75-97) on those tokens. The reference
+ * cannot do this with its prefill — KVCache::update_prefill asserts an empty cache (decode.hpp:78-79,
+ * listed as a limitation in README.md:96). One sequence per state; logits_host may be NULL, otherwise it
+ * receives the logits after the last token. */
+int tg_append(tg_state *s, const int *ids_host, int n, float *logits_host);
 
 /* ops::argmax_logits, ops.hpp:744-760, on the logits of the last forward
  * (still in HBM): lowest index wins ties, NaN never wins, -1 if no logit is

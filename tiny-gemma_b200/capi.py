@@ -51,6 +51,7 @@ SIGNATURES = {
     "tg_state_position": (C.c_int, [_P, C.c_int, C.POINTER(C.c_int)]),
     "tg_prefill": (C.c_int, [_P, _P, C.c_int, _P]),
     "tg_decode": (C.c_int, [_P, _P, _P]),
+    "tg_append": (C.c_int, [_P, _P, C.c_int, _P]),
     "tg_sample_argmax": (C.c_int, [_P, _P]),
     "tg_sample_minp": (C.c_int, [_P, C.c_float, C.c_float, _P, _P]),
     "tg_logits_read": (C.c_int, [_P, _P]),
@@ -258,6 +259,13 @@ class State:
             ids = np.ascontiguousarray(ids, np.int32).reshape(self.B)
         logits = np.empty((self.B, self.V), np.float32) if want_logits else None
         _ck(self.lib.tg_decode(self.h, _ptr(ids), _ptr(logits)))
+        return logits
+
+    def append(self, ids, want_logits: bool = True):
+        """continue a non-empty context with the given tokens (one sequence per state)"""
+        ids = np.ascontiguousarray(ids, np.int32).reshape(-1)
+        logits = np.empty((1, self.V), np.float32) if want_logits else None
+        _ck(self.lib.tg_append(self.h, _ptr(ids), ids.size, _ptr(logits)))
         return logits
 
     def sample_argmax(self) -> np.ndarray:

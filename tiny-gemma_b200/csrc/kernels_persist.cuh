@@ -118,6 +118,7 @@ struct PsArgs {
 	int *err;
 	int *tok, *next_pos, *ring_base, *tok_log, *log_count;
 	int log_cap, n_steps, sampler;
+	const int *force_ids;  // optional [n_steps]: the token of every step is given (continuation of a context), not sampled
 	float minp, temp;
 	const float *randf;
 	int *randf_count;
@@ -577,6 +578,16 @@ __global__ void retile_lm_kernel(int8_t *dst, const int8_t *src, int V, int ngro
 		if (gc * 4 < size_t(V)) v = ps_piece(src, size_t(V), size_t(row_q) * 4, gc * 4);
 		*reinterpret_cast<uint4 *>(dst + ((size_t(t) * nchunk + ch) * ngroups * cq + size_t(g) * cq + q) * 16) = v;
 	}
+}
+
+// lut::GeLUTable::lookup (reference ops.hpp:41-51) with the table kept L2-resident
+__device__ __forceinline__ float ps_gelu(const GeluLut &t, float x, uint64_t keep) {
+	const float q = (x - t.mn) / t.eps;
+	if (!(q < 2147483648.0f) || q < -2147483648.0f) return 0.0f;  // (x86 cvttss2si: INT_MIN, a negative index)
+	const int idx = int(q);
+	if (idx < 0) return 0.0f;
+	if (idx >= t.size) return x;
+	return ps_ldk(t.table + idx, keep);
 }
 
 // ------------------------------------------------------------------ prologues
@@ -1341,6 +1352,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 		const bool dbg_on = DBG && (a.dbg != nullptr) && cta == a.dbg_cta && tid == 0 && !more;
 		PS_STAMP();
 		// ---------------------------------------------------------------- embedding
+		if (a.force_ids) tok = __ldg(a.force_ids + step);
 		if (tok < 0 || tok >= a.V) {
 			if (tid == 0 && cta == 0) atomicExch(a.err, 1);
 			tok = 0;
@@ -1515,7 +1527,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 					const PsOut o = ps_product(ps_smem(R_D), a.Dp.ngroups, a.Dp.nq, a.Dp.kp, a.Dp.wq, true, xd_s, D / 4, part_s, cnt_s);
 					if ((o.flags & 1) && lane < 4) {
 						const float xs = s_xscale;
-						ps_st(llb + a.ll_act + colD, a.lut((o.r1 * xs) * sg_r) * ((o.r0 * xs) * su_r));
+						ps_st(llb + a.ll_act + colD, ps_gelu(a.lut, (o.r1 * xs) * sg_r, keep) * ((o.r0 * xs) * su_r));
 					}
 				}
 				pD ^= 1;

@@ -65,6 +65,14 @@ int env_int(const char *name, int dflt) {
 
 int g_num_sms = 148;
 
+// cudaFuncSetAttribute is per device: "configured once" flags are kept per device index
+constexpr int TG_MAX_DEVICES = 64;
+inline int current_device_slot() {
+	int d = 0;
+	cudaGetDevice(&d);
+	return (d >= 0 && d < TG_MAX_DEVICES) ? d : 0;
+}
+
 }  // namespace
 
 // ===================================================================== model
@@ -216,10 +224,11 @@ size_t mv_smem_bytes(int MB, int pro, int epi, int K, int kc) {
 
 template <int MB, int PRO, int EPI>
 int launch_mv_t(const MvArgs &a, dim3 grid, size_t smem, cudaStream_t st) {
-	static size_t configured = 0;
-	if (smem > 48 * 1024 && smem > configured) {
+	static size_t configured[TG_MAX_DEVICES] = {0};
+	const int dev = current_device_slot();
+	if (smem > 48 * 1024 && smem > configured[dev]) {
 		TG_CUDA(cudaFuncSetAttribute(qmatvec_kernel<MB, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-		configured = smem;
+		configured[dev] = smem;
 	}
 	qmatvec_kernel<MB, PRO, EPI><<<grid, MV_THREADS, smem, st>>>(a);
 	count_launch();
@@ -300,6 +309,8 @@ struct tg_state {
 	int *step_pos = nullptr, *next_pos = nullptr, *ring_base = nullptr;  // [B]
 	int *tok = nullptr;                // [B]
 	int *tok_log = nullptr;            // [log_cap][B]
+	int *force_ids = nullptr;          // [force_cap] tokens of tg_append (batch 1)
+	int force_cap = 0;
 	int log_cap = 0;
 	int *log_count = nullptr;          // [B]
 	float *randf = nullptr;            // [randf_cap][B]
@@ -752,8 +763,10 @@ int mega_setup(tg_state *s) {
 	const int G = env_int("TG_MEGA_GRID", g_num_sms);
 	MgArgs &a = s->mega;
 	a = MgArgs{};
-	a.att_local = std::min(std::min(env_int("TG_MEGA_ATT_LOCAL", 32), MG_MAX_ATT), G);
-	a.att_global = std::min(std::min(env_int("TG_MEGA_ATT_GLOBAL", 32), MG_MAX_ATT), G);
+	// (the CTAs that idle through the attention phase wipe the hand-off arena: at least 8 must remain)
+	if (G < 16) return fail(TG_ESHAPE, "persistent kernel: grid too small");
+	a.att_local = std::min(std::min(env_int("TG_MEGA_ATT_LOCAL", 32), MG_MAX_ATT), G - 8);
+	a.att_global = std::min(std::min(env_int("TG_MEGA_ATT_GLOBAL", 32), MG_MAX_ATT), G - 8);
 	const int budget = smem_max - 40 * 1024;  // room for h, xs, reduction scratch, attention scratch, static shared
 	if (!plan_phase(&a.A, D, {qd, kd, kd}, 1, true, G, budget / 8) || !plan_phase(&a.C, qd, {D}, 1, true, G, budget / 8) ||
 	    !plan_phase(&a.Dp, D, {I}, 2, false, G, budget) || !plan_phase(&a.E, I, {D}, 1, true, G, budget / 2))
@@ -1169,7 +1182,7 @@ int ensure_persist_tiles(tg_state *s) {
 	return TG_OK;
 }
 
-int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, bool log_tokens) {
+int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, bool log_tokens, const int *force_ids = nullptr) {
 	tg_model *m = s->m;
 	TG_TRY(ensure_persist_tiles(s));
 	PsArgs a = s->ps;
@@ -1182,6 +1195,7 @@ int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp
 	a.lut = make_lut(m);
 	a.n_steps = n_steps;
 	a.sampler = sampler;
+	a.force_ids = force_ids;
 	a.minp = minp;
 	a.temp = temp;
 	a.randf = s->randf;
@@ -1264,7 +1278,7 @@ int mega_launch(tg_state *s, int n_steps, int sampler, float minp, float temp, b
 	s->mg_seq += unsigned(n_steps) * unsigned(m->cfg.n_layers);
 	// CTAs per global-attention layer follow the context: 32 up to ~1K positions, 64 beyond (measured at 16K
 	// positions: 937 -> 1049 tok/s; at 200-700 positions 64 is no gain). TG_MEGA_ATT_GLOBAL fixes the number.
-	if (!std::getenv("TG_MEGA_ATT_GLOBAL") && s->host_pos[0] >= 1024) a.att_global = std::min(MG_MAX_ATT, s->mega_grid);
+	if (!std::getenv("TG_MEGA_ATT_GLOBAL") && s->host_pos[0] >= 1024) a.att_global = std::min(MG_MAX_ATT, s->mega_grid - 8);
 	// every word of the hand-off arena starts as "empty" (all ones)
 	TG_CUDA(cudaMemsetAsync(s->mg_ll, 0xFF, s->mg_ll_bytes, s->stream));
 	a.dbg = s->mg_dbg;
@@ -1407,11 +1421,12 @@ int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStre
 // kernel that adds the splits and scales itself; *raw_nsplit receives the split count, no reduce is launched.
 int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const int *ldcs, int M, const TcScratch &sc,
                          cudaStream_t st, int max_split = 1 << 30, int *raw_nsplit = nullptr) {
-	static bool configured = false;
-	if (!configured) {
+	static bool configured[TG_MAX_DEVICES] = {false};
+	const int dev = current_device_slot();
+	if (!configured[dev]) {
 		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<2, 128>::SMEM));
 		TG_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<1, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<1, 256>::SMEM));
-		configured = true;
+		configured[dev] = true;
 	}
 	// tile shape: beyond one row tile the wide shape (one row tile x 256 columns) wins: a 256-column MMA
 	// keeps the tensor pipe busier than two of 128 and every fetched A tile is used twice as often
@@ -1716,10 +1731,11 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 			attn_prefill_small_kernel<<<(S + 1) / 2, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
-				static bool configured = false;
-				if (!configured) {
+				static bool configured[TG_MAX_DEVICES] = {false};
+				const int dev = current_device_slot();
+				if (!configured[dev]) {
 					TG_CUDA(cudaFuncSetAttribute(attn_prefill_blk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_BLK_SMEM));
-					configured = true;
+					configured[dev] = true;
 				}
 				attn_prefill_blk_kernel<<<(S + 7) / 8, 256, AP_BLK_SMEM, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 			} else
@@ -1925,6 +1941,9 @@ int tg_model_load_file(tg_model *m, const char *path) {
 
 int tg_model_set_rope(tg_model *m, int is_local, const float *cos_host, const float *sin_host, int n_pos) {
 	if (!m || !cos_host || !sin_host || n_pos <= 0) return fail(TG_EINVAL, "bad argument");
+	// the kernels read row `position` for every position a state may reach (max_pos_global <= n_pos); the
+	// reference's decode::RoPE always builds cfg.n_pos rows (decode.hpp:118-200), so a shorter table is refused
+	if (n_pos < m->cfg.n_pos) return fail(TG_EINVAL, "RoPE table shorter than the model's n_pos");
 	TG_CUDA(cudaSetDevice(m->device));
 	const int i = is_local ? 1 : 0;
 	size_t n = size_t(n_pos) * m->cfg.head_dim * 4;
@@ -2046,6 +2065,7 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->ring_base);
 	cudaFree(s->tok);
 	cudaFree(s->tok_log);
+	cudaFree(s->force_ids);
 	cudaFree(s->log_count);
 	cudaFree(s->randf);
 	cudaFree(s->randf_count);
@@ -2175,7 +2195,7 @@ int tg_decode(tg_state *s, const int *ids, float *logits_host) {
 	else
 		TG_TRY(enqueue_decode_step(s));
 	for (int b = 0; b < s->B; b++) s->host_pos[b] += 1;
-	s->staging_busy = ids != nullptr;
+	s->staging_busy = s->staging_busy || ids != nullptr;  // (an earlier asynchronous call's copy may still be queued)
 	if (logits_host) {
 		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(s->B) * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, s->stream));
 		TG_TRY(check_err_flag(s));
@@ -2183,6 +2203,35 @@ int tg_decode(tg_state *s, const int *ids, float *logits_host) {
 	// without a host read-back the call only enqueues: the step runs while the caller prepares the sampler
 	// call, and a device-side error (a wait that ran out) is reported by the next call that synchronises
 	return TG_OK;
+}
+
+int tg_append(tg_state *s, const int *ids, int n, float *logits_host) {
+	if (!s || !ids || n < 1) return fail(TG_EINVAL, "bad argument");
+	if (s->B != 1) return fail(TG_EINVAL, "tg_append: one sequence per state");
+	tg_model *m = s->m;
+	TG_TRY(check_ready(m));
+	TG_CUDA(cudaSetDevice(m->device));
+	if (s->host_pos[0] + n > s->max_pos_global) return fail(TG_ESTATE, "global KV cache too small for the appended tokens");
+	for (int i = 0; i < n; i++)
+		if (ids[i] < 0 || ids[i] >= m->cfg.n_vocab) return fail(TG_EINVAL, "token id out of range");
+	if (s->ps_ok) {
+		// one launch of the persistent kernel: every step takes its token from the list instead of a sampler
+		if (s->force_cap < n) {
+			cudaFree(s->force_ids);
+			s->force_ids = nullptr;
+			TG_CUDA(cudaMalloc(&s->force_ids, size_t(n) * 4));
+			s->force_cap = n;
+		}
+		TG_CUDA(cudaMemcpyAsync(s->force_ids, ids, size_t(n) * 4, cudaMemcpyHostToDevice, s->stream));
+		TG_CUDA(cudaStreamSynchronize(s->stream));  // `ids` is the caller's pageable memory: consumed before returning
+		TG_TRY(persist_launch(s, n, 0, 2.0f, 1.0f, false, s->force_ids));
+		s->host_pos[0] += n;
+	} else {
+		for (int i = 0; i < n; i++) TG_TRY(tg_decode(s, ids + i, nullptr));
+	}
+	if (logits_host)
+		TG_CUDA(cudaMemcpyAsync(logits_host, s->logits, size_t(m->cfg.n_vocab) * 4, cudaMemcpyDeviceToHost, s->stream));
+	return check_err_flag(s);
 }
 
 int tg_sample_argmax(tg_state *s, int *toks_host) {
