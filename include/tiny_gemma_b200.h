@@ -210,12 +210,26 @@ int tg_dev_qgemm(float *c_dev, const float *a_dev, const int8_t *w_dev, const fl
  * (2) after the hidden states of all GPUs have been gathered, scores M of them against its own
  * column slice [col0, col0 + ncols) and returns per row the maximum logit and its global index,
  * lowest index on ties (tg_dev_lm_head_top1), and (3) after the per-slice candidates have been
- * gathered and resolved, takes the tokens of its own sequences back (tg_dev_set_tokens). The two
- * gathers are the caller's (NCCL). col0 and ncols must be multiples of 128. */
+ * gathered, resolves them (tg_dev_resolve_top1: largest maximum, lowest index among equal maxima,
+ * ops.hpp:744-760) and takes the tokens of its own sequences back (tg_dev_set_tokens). The two
+ * gathers are the caller's (NCCL). col0 and ncols must be multiples of 128.
+ *
+ * A step enqueues only: tg_decode_hidden with ids_host == NULL (tokens fed from the device),
+ * tg_dev_hidden_copy, tg_dev_set_tokens (all on the state's stream) and tg_dev_lm_head_top1 /
+ * tg_dev_resolve_top1 (on the stream given) never synchronise the host; enqueue everything of a
+ * step on the state's stream (tg_state_stream). tg_state_check synchronises that stream and reports
+ * the kernels' error word (bad token id, cache full, a wait that ran out); tg_decode_hidden with
+ * host ids does the same before it returns. tg_dev_lm_head_top1 is one tensor-core GEMM over the
+ * slice whose epilogue keeps the row maxima (no logits are written); a pipeline wait that ran out
+ * in it is reported by the next call on the same device.
+ * tg_dev_resolve_top1: cand_all_dev is [world][2][M] 32-bit words, per slice the M maxima (fp32)
+ * then the M global indices (int32, -1: no candidate); writes the tokens of rows row0..row0+nrows. */
 int tg_decode_hidden(tg_state *s, const int *ids_host);
+int tg_state_check(tg_state *s);
 int tg_dev_hidden_copy(tg_state *s, float *dst_dev);
 int tg_dev_lm_head_top1(tg_model *m, const float *hidden_dev, int M, int col0, int ncols, float *max_dev, int *idx_dev,
                         void *cuda_stream);
+int tg_dev_resolve_top1(const void *cand_all_dev, int world, int M, int row0, int nrows, int *toks_dev, void *cuda_stream);
 int tg_dev_set_tokens(tg_state *s, const int *toks_dev);
 
 /* ---- introspection for benchmarks --------------------------------------- */

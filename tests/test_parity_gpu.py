@@ -57,6 +57,22 @@ def test_qgemm_ragged_and_large_m(capi, port):
         assert rel_l2(capi.qgemm(x, w, s), port.linear_prefill(x, w, s)) <= 5e-6
 
 
+@pytest.mark.parametrize("K,N", [(1152, 6912), (6912, 1152), (1152, 1024)])
+def test_qgemm_m1024_1b_shapes_vs_oracle(capi, port, K, N):
+    """the 256-column tile shape with 8 full row tiles at the three Gemma-3-1B layer shapes (K = 6912 takes the K-split)"""
+    x, w, s = cases.linear_case(K, N, 1024, seed=11)
+    assert rel_l2(capi.qgemm(x, w, s), port.linear_prefill(x, w, s)) <= 5e-6
+
+
+def test_qgemm_lm_head_shape_m16_vs_oracle(capi, port):
+    """the lm_head shape as a GEMM (2048 column tiles, one ragged row tile): each row against the oracle's lm_head matvec"""
+    K, N = cases.LM_HEAD_SHAPE
+    x, w, s = cases.linear_case(K, N, 16, seed=12)
+    c = capi.qgemm(x, w, s)
+    for r in (0, 7, 15):
+        assert rel_l2(c[r], port.lm_head_decode(x[r], w, s)) <= 5e-6
+
+
 def test_matvec_is_linear_and_deterministic(capi):
     # size-independent properties at the full lm_head size
     K, N = cases.LM_HEAD_SHAPE
@@ -351,6 +367,49 @@ def test_batched_decode_tensor_core_step(capi, model_270m, synth):
     assert loop.shape == (4, B) and (loop >= 0).all()
     stb.close()
     model_270m.build_tables(1024)
+
+
+def test_bounded_wait_returns_an_error_and_the_context_survives(capi, synth, weights_270m, monkeypatch):
+    """The persistent decode kernel's waits are bounded by a host-settable limit (TG_PS_WAIT_MS). With one
+    producer CTA told to withhold its down-projection hand-off (TG_PS_WITHHOLD_CTA, a debug argument of the
+    launch), the consumers' waits run out: the kernel returns by itself, tg_generate reports TG_ECUDA with
+    the place it gave up, and a fresh state on the same model and context decodes normally afterwards."""
+    monkeypatch.setenv("TG_PERSIST", "2")
+    monkeypatch.setenv("TG_PS_WAIT_MS", "20")
+    m = capi.Model("270m").load_file(weights_270m).build_tables(1024)
+    ids = synth.random_prompt(24, 31)
+    good = m.state(1, 128)
+    good.prefill(ids, want_logits=False)
+    first = good.sample_argmax()
+    want = good.generate(first, 6)
+    good.close()
+    monkeypatch.setenv("TG_PS_WITHHOLD_CTA", "0")
+    st = m.state(1, 128)
+    st.prefill(ids, want_logits=False)
+    st.sample_argmax()
+    with pytest.raises(capi.TgError) as e:
+        st.generate(first, 2)
+    assert e.value.code == capi.TG_ECUDA and "wait ran out" in str(e.value)
+    st.close()
+    monkeypatch.delenv("TG_PS_WITHHOLD_CTA")
+    st = m.state(1, 128)
+    st.prefill(ids, want_logits=False)
+    assert np.array_equal(st.generate(st.sample_argmax(), 6), want)
+    st.close()
+    m.close()
+
+
+def test_rope_table_shorter_than_the_model_is_refused(capi, weights_270m):
+    """tg_model_set_rope must cover every position of the model: a shorter table would be read past its end"""
+    import ctypes as C
+
+    m = capi.Model("270m").load_file(weights_270m).build_tables(1024)
+    lib = capi.load()
+    short = np.zeros((1024, 128), np.float32)
+    p = short.ctypes.data_as(C.c_void_p)
+    for is_local in (0, 1):
+        assert lib.tg_model_set_rope(m.h, is_local, p, p, 1024) == capi.TG_EINVAL
+    m.close()
 
 
 def test_error_paths(capi, model_270m, synth, tmp_path):

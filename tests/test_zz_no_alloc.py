@@ -27,7 +27,7 @@ def _ptr(t):
 
 
 @pytest.mark.parametrize("K,N", [(6912, 1152), (1152, 6912), (640, 1024), (1152, 262144)])
-def test_static_scratch_matvec_matches_allocating_entry_point(capi, K, N):
+def test_static_scratch_matvec_matches_allocating_entry_point(capi, port, K, N):
     import torch
 
     lib = capi.load()
@@ -52,6 +52,9 @@ def test_static_scratch_matvec_matches_allocating_entry_point(capi, K, N):
     assert rel_l2(y1.cpu().numpy(), ref) <= 5e-6
     assert rel_l2(y2.cpu().numpy(), ref) <= 5e-6
     assert torch.equal(y1, y2)
+    # and against the oracle's restatement of the reference operator (linalg.hpp:41-204)
+    want = port.lm_head_decode(x[0], w, s) if N == 262144 else port.linear_decode(x[0], w, s)
+    assert rel_l2(y1.cpu().numpy(), want) <= 5e-6
 
 
 def test_static_scratch_rejects_sizes_beyond_its_maximum(capi):

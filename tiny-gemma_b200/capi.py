@@ -71,6 +71,8 @@ SIGNATURES = {
     "tg_dev_hidden_copy": (C.c_int, [_P, _P]),
     "tg_dev_lm_head_top1": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),
     "tg_dev_set_tokens": (C.c_int, [_P, _P]),
+    "tg_state_check": (C.c_int, [_P]),
+    "tg_dev_resolve_top1": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "tg_launch_count": (C.c_int, [C.c_int, C.POINTER(C.c_longlong)]),
     "tg_state_stream": (C.c_int, [_P, C.POINTER(_P)]),
     "tg_generate_async": (C.c_int, [_P, C.c_int, C.c_float, C.c_float]),
@@ -220,6 +222,9 @@ class Model:
         _ck(self.lib.tg_dev_lm_head_top1(self.h, C.c_void_p(hidden_ptr), M, col0, ncols, C.c_void_p(max_ptr),
                                          C.c_void_p(idx_ptr), C.c_void_p(stream)))
 
+    def resolve_top1_dev(self, cand_ptr: int, world: int, M: int, row0: int, nrows: int, toks_ptr: int, stream: int = 0):
+        _ck(self.lib.tg_dev_resolve_top1(C.c_void_p(cand_ptr), world, M, row0, nrows, C.c_void_p(toks_ptr), C.c_void_p(stream)))
+
     def state(self, batch: int = 1, max_pos_global: int = 0) -> "State":
         return State(self, batch, max_pos_global)
 
@@ -313,6 +318,10 @@ class State:
         if ids is not None:
             ids = np.ascontiguousarray(ids, np.int32).reshape(self.B)
         _ck(self.lib.tg_decode_hidden(self.h, _ptr(ids)))
+
+    def check(self):
+        """synchronises the state's stream and raises if a kernel left an error word"""
+        _ck(self.lib.tg_state_check(self.h))
 
     def hidden_copy_dev(self, dst_ptr: int):
         _ck(self.lib.tg_dev_hidden_copy(self.h, C.c_void_p(dst_ptr)))

@@ -335,8 +335,32 @@ struct GemmTcArgs {
 	                             // and applies the column scales itself, so no reduce kernel runs
 	unsigned *tickets;           // [gridDim.y * gridDim.x] zeros, or null. Non-null with nsplit > 1: the CTA that finishes
 	                             // a tile last adds the partial sums in split order, scales and writes C itself
+	unsigned long long *top1;    // non-null (nsplit == 1 only): no C is written; per row the largest scaled value and its column
+	                             // are folded into top1[row] with atomicMax on tc_top1_key (lowest column on equal values)
+	int top1_col0;               // added to a column index before it is recorded
 	int *err;
 };
+
+// (value, column) -> a 64-bit key whose unsigned order is: larger value first, then the lower column. 0 = no candidate.
+__device__ __forceinline__ unsigned long long tc_top1_key(float v, int col) {
+	const uint32_t b = __float_as_uint(v);
+	const uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+	return (static_cast<unsigned long long>(ord) << 32) | static_cast<unsigned long long>(0xFFFFFFFFu - uint32_t(col));
+}
+// keys [M] -> maximum (or -inf) and column (or -1) per row
+__global__ void top1_unpack_kernel(const unsigned long long *keys, int M, float *max_out, int *idx_out) {
+	const int r = blockIdx.x * blockDim.x + threadIdx.x;
+	if (r >= M) return;
+	const unsigned long long k = keys[r];
+	if (k == 0ull) {
+		max_out[r] = -INFINITY;
+		idx_out[r] = -1;
+		return;
+	}
+	const uint32_t ord = uint32_t(k >> 32);
+	max_out[r] = __uint_as_float((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
+	idx_out[r] = int(0xFFFFFFFFu - uint32_t(k));
+}
 
 template <int MT, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap0,
@@ -531,11 +555,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 				tc_ld32(taddr, r);
 				if (two) tc_ld32(taddr + uint32_t(MT * BN), r2);
 			};
+			float t1_best = -INFINITY;  // top-1 mode: this lane's row, running over the column blocks of one row tile
+			int t1_col = -1;
 			auto finish = [&](int e, uint32_t (&r)[32], uint32_t (&r2)[32]) {
 				const int mt = e / CH, c = e % CH;
 				if (two) {
 #pragma unroll
 					for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+				}
+				if (a.top1) {
+					// a lane holds 32 consecutive columns of one row: scan them in ascending order (strict >: the
+					// lowest column of equal values stays), one atomicMax per row when the row tile is through
+					if ((mt0 + mt) < a.m_tiles && n0 + c * 32 < ncg) {
+						const float4 *sc = reinterpret_cast<const float4 *>(scg + n0 + c * 32);
+#pragma unroll
+						for (int i4 = 0; i4 < 8; i4++) {
+							const float4 s4 = __ldg(sc + i4);
+							const float v0 = __uint_as_float(r[4 * i4]) * s4.x, v1 = __uint_as_float(r[4 * i4 + 1]) * s4.y;
+							const float v2 = __uint_as_float(r[4 * i4 + 2]) * s4.z, v3 = __uint_as_float(r[4 * i4 + 3]) * s4.w;
+							const int cb = n0 + c * 32 + 4 * i4;
+							if (v0 > t1_best) { t1_best = v0; t1_col = cb; }
+							if (v1 > t1_best) { t1_best = v1; t1_col = cb + 1; }
+							if (v2 > t1_best) { t1_best = v2; t1_col = cb + 2; }
+							if (v3 > t1_best) { t1_best = v3; t1_col = cb + 3; }
+						}
+					}
+					if (c == CH - 1) {
+						const int row = (mt0 + mt) * TC_BM + quad * 32 + lane;
+						if (row < a.M && t1_col >= 0) atomicMax(a.top1 + row, tc_top1_key(t1_best, a.top1_col0 + t1_col));
+						t1_best = -INFINITY;
+						t1_col = -1;
+					}
+					return;
 				}
 				if ((mt0 + mt) < a.m_tiles && n0 + c * 32 < ncg) {  // (a wide tile may reach past the group's last column)
 					// A lane holds 32 consecutive columns of ONE row; written from here, a store instruction would

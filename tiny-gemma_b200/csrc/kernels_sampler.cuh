@@ -70,45 +70,6 @@ __global__ void __launch_bounds__(SM_THREADS) argmax_kernel(SampleArgs a) {
 	}
 }
 
-// Row-wise (max, argmax) over a slice of the vocabulary: rows [M][ncols] hold the logits of
-// columns col0.. of M sequences; writes the maximum and its GLOBAL index (col0 + local), lowest
-// index on ties (the rule of ops::argmax_logits). One CTA per row.
-__global__ void __launch_bounds__(SM_THREADS) top1_rows_kernel(const float *logits, int ncols, int col0, float *max_out,
-                                                               int *idx_out) {
-	__shared__ float sv[SM_NWARPS];
-	__shared__ int si[SM_NWARPS];
-	const int r = blockIdx.x, tid = threadIdx.x;
-	const float *x = logits + size_t(r) * ncols;
-	float best = -INFINITY;
-	int arg = -1;
-	for (int i = tid; i < ncols; i += SM_THREADS) {
-		float v = x[i];
-		if (v > best) { best = v; arg = i; }
-	}
-	auto better = [](float v1, int i1, float v2, int i2) {
-		if (v1 > v2) return true;
-		if (v1 < v2) return false;
-		if (i2 < 0) return i1 >= 0;
-		if (i1 < 0) return false;
-		return i1 < i2;
-	};
-#pragma unroll
-	for (int o = 16; o > 0; o >>= 1) {
-		float ov = __shfl_xor_sync(0xffffffffu, best, o);
-		int oi = __shfl_xor_sync(0xffffffffu, arg, o);
-		if (better(ov, oi, best, arg)) { best = ov; arg = oi; }
-	}
-	if ((tid & 31) == 0) { sv[tid >> 5] = best; si[tid >> 5] = arg; }
-	__syncthreads();
-	if (tid == 0) {
-		for (int w = 1; w < SM_NWARPS; w++)
-			if (better(sv[w], si[w], best, arg)) { best = sv[w]; arg = si[w]; }
-		max_out[r] = best;
-		idx_out[r] = arg < 0 ? -1 : col0 + arg;
-	}
-}
-
-
 // ------------------------------------------------------------------ exact parallel inverse CDF
 // Step (6) of min-p sampling is "the first index whose running fp32 sum reaches randf", where the
 // running sum is the sequential chain cum = fl(cum + p[i]). fp32 addition is not associative, so a

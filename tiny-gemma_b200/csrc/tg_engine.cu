@@ -80,6 +80,7 @@ struct QW {
 	const int8_t *q = nullptr;
 	const float *s = nullptr;
 	int K = 0, N = 0;
+	int ld = 0;  // bytes between rows when the matrix is a column slice of a wider one; 0: N
 };
 
 struct LayerW {
@@ -280,6 +281,8 @@ struct TcScratch {
 	                              // latency-bound (measured: 9-way splits reduced in-kernel doubled the batched step time)
 	int max_split = 9;            // cap on the K-split depth: deeper splits (one or two K-blocks per CTA) cost more in partial-sum
 	                              // traffic and per-CTA fixed cost than they gain in parallelism (TG_GEMM_MAX_SPLIT overrides)
+	unsigned long long *top1 = nullptr;  // set for one launch: row-wise (max, column) keys instead of C (unsplit K)
+	int top1_col0 = 0;
 	int *err = nullptr;
 };
 
@@ -685,11 +688,11 @@ PFN_encodeTiled get_encode_fn() {
 }
 
 // 2-D uint8 map over a row-major [K, N] int8 matrix; box = TN bytes x box_rows rows, no swizzle
-int make_tmap(CUtensorMap *out, const int8_t *base, int K, int N, int TN, int box_rows) {
+int make_tmap(CUtensorMap *out, const int8_t *base, int K, int N, int TN, int box_rows, int ld = 0) {
 	PFN_encodeTiled enc = get_encode_fn();
 	if (!enc) return fail(TG_ECUDA, "cuTensorMapEncodeTiled entry point not available");
 	cuuint64_t gdim[2] = {cuuint64_t(N), cuuint64_t(K)};
-	cuuint64_t gstride[1] = {cuuint64_t(N)};
+	cuuint64_t gstride[1] = {cuuint64_t(ld > 0 ? ld : N)};
 	cuuint32_t box[2] = {cuuint32_t(TN), cuuint32_t(box_rows)};
 	cuuint32_t estr[2] = {1, 1};
 	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(base), gdim, gstride, box, estr,
@@ -1441,7 +1444,7 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 	for (int g = 0; g < 3; g++) {
 		const int gg = std::min(g, ng - 1);  // unused slots repeat the last matrix (never selected)
 		if (ws[gg]->K != K) return fail(TG_ESHAPE, "grouped GEMM: the matrices must share K");
-		TG_TRY(make_tmap(&wmap[g], ws[gg]->q, K, ws[gg]->N, bn, TC_BK));
+		TG_TRY(make_tmap(&wmap[g], ws[gg]->q, K, ws[gg]->N, bn, TC_BK, ws[gg]->ld));
 		if (g < ng) {
 			a.col0[g] = ntot;
 			a.ncols[g] = ws[g]->N;
@@ -1476,6 +1479,9 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 	a.nsplit = tc_pick_split(tiles * ((m_tiles_all + mt_cta - 1) / mt_cta), M, K, ntot, sc.partial_floats, std::min(max_split, env_int("TG_GEMM_MAX_SPLIT", sc.max_split)));
 	a.partial = sc.partial;
 	a.err = sc.err;
+	a.top1 = sc.top1;
+	a.top1_col0 = sc.top1_col0;
+	if (a.top1 && (a.nsplit != 1 || raw_nsplit)) return fail(TG_EINVAL, "top-1 epilogue needs an unsplit K");
 	dim3 grid(tiles, (a.m_tiles + mt_cta - 1) / mt_cta, a.nsplit);
 	const bool fused = !raw_nsplit && sc.tickets && a.nsplit > 1 && a.nsplit <= sc.fused_max_split && size_t(grid.x) * grid.y <= TC_TICKETS;
 	a.tickets = fused ? sc.tickets : nullptr;
@@ -2392,16 +2398,21 @@ int tg_decode_hidden(tg_state *s, const int *ids) {
 	} else {
 		for (int b0 = 0; b0 < s->B; b0 += MV_MAX_B) TG_TRY(enqueue_decode_chunk(s, b0, std::min(MV_MAX_B, s->B - b0), false));
 	}
-	TG_TRY(check_err_flag(s));
+	if (ids) TG_TRY(check_err_flag(s));  // fed from the device: enqueue only, tg_state_check reports the error word later
 	for (int b = 0; b < s->B; b++) s->host_pos[b] += 1;
 	return TG_OK;
+}
+
+int tg_state_check(tg_state *s) {
+	if (!s) return fail(TG_EINVAL, "null state");
+	TG_CUDA(cudaSetDevice(s->m->device));
+	return check_err_flag(s);
 }
 
 int tg_dev_hidden_copy(tg_state *s, float *dst_dev) {
 	if (!s || !dst_dev) return fail(TG_EINVAL, "null argument");
 	TG_CUDA(cudaSetDevice(s->m->device));
 	TG_CUDA(cudaMemcpyAsync(dst_dev, s->xnorm, size_t(s->B) * s->m->cfg.hidden_size * 4, cudaMemcpyDeviceToDevice, s->stream));
-	TG_CUDA(cudaStreamSynchronize(s->stream));
 	return TG_OK;
 }
 
@@ -2409,7 +2420,6 @@ int tg_dev_set_tokens(tg_state *s, const int *toks_dev) {
 	if (!s || !toks_dev) return fail(TG_EINVAL, "null argument");
 	TG_CUDA(cudaSetDevice(s->m->device));
 	TG_CUDA(cudaMemcpyAsync(s->tok, toks_dev, size_t(s->B) * 4, cudaMemcpyDeviceToDevice, s->stream));
-	TG_CUDA(cudaStreamSynchronize(s->stream));
 	return TG_OK;
 }
 
@@ -2421,44 +2431,88 @@ int tg_dev_lm_head_top1(tg_model *m, const float *hidden_dev, int M, int col0, i
 		return fail(TG_EINVAL, "vocabulary slice must be a multiple of 128 columns inside [0, n_vocab)");
 	TG_CUDA(cudaSetDevice(m->device));
 	cudaStream_t st = (cudaStream_t)stream;
-	// logits of up to MV_MAX_B rows at a time over the slice, then their row maxima
-	static float *scratch[64] = {nullptr};
-	static size_t scratch_floats[64] = {0};
-	static unsigned *tickets[64] = {nullptr};
-	const int dev = m->device;
-	const size_t need = size_t(MV_MAX_B) * ncols;
-	if (need > scratch_floats[dev]) {
-		if (scratch[dev]) cudaFree(scratch[dev]);
-		scratch[dev] = nullptr;
-		TG_CUDA(cudaMalloc(&scratch[dev], need * 4));
-		scratch_floats[dev] = need;
+	// One tensor-core GEMM over the slice, addressed in place through a tensor map with the full matrix's row
+	// pitch (a tile row is a 128- or 256-byte segment either way); its epilogue keeps per row the largest
+	// scaled value and its column, so no logits are written. Scratch per device, grown on demand.
+	struct Top1Scratch {
+		TcScratch tc;
+		unsigned long long *keys = nullptr;
+		int keys_cap = 0;
+		int *err_host = nullptr;
+	};
+	static Top1Scratch scr[TG_MAX_DEVICES];
+	const int slot = current_device_slot();
+	Top1Scratch &t = scr[slot];
+	const size_t need = tc_pack_bytes(M, D);
+	if (need > t.tc.apack_bytes) {
+		if (t.tc.apack) cudaFree(t.tc.apack);
+		t.tc.apack = nullptr;
+		t.tc.apack_bytes = 0;
+		TG_CUDA(cudaMalloc(&t.tc.apack, need));
+		t.tc.apack_bytes = need;
 	}
-	if (!tickets[dev]) {
-		TG_CUDA(cudaMalloc(&tickets[dev], sizeof(unsigned) * 2048));
-		TG_CUDA(cudaMemset(tickets[dev], 0, sizeof(unsigned) * 2048));
+	if (M > t.keys_cap) {
+		if (t.keys) cudaFree(t.keys);
+		t.keys = nullptr;
+		t.keys_cap = 0;
+		TG_CUDA(cudaMalloc(&t.keys, size_t(M) * 8));
+		t.keys_cap = M;
 	}
-	for (int r0 = 0; r0 < M; r0 += MV_MAX_B) {
-		const int nb = std::min(MV_MAX_B, M - r0);
-		MvArgs a{};
-		a.seg[0] = MvSeg{m->lm_head.q + col0, m->lm_head.s + col0, V, 0, 0};
-		a.nseg = 1;
-		a.ntiles = ncols / MV_TN;
-		a.K = D;
-		a.kc = D;
-		a.nsplit = 1;
-		a.B = nb;
-		a.part_stride = ncols;
-		a.out_stride = ncols;
-		a.x = hidden_dev + size_t(r0) * D;
-		a.partial = nullptr;
-		a.tickets = tickets[dev];
-		a.out = scratch[dev];
-		TG_TRY(launch_mv(a, PRO_PLAIN, EPI_SCALE, st));
-		top1_rows_kernel<<<nb, SM_THREADS, 0, st>>>(scratch[dev], ncols, col0, max_dev + r0, idx_dev + r0);
-		count_launch();
-		TG_TRY(check_launch("top1_rows"));
+	if (!t.tc.err) {
+		TG_CUDA(cudaMalloc(&t.tc.err, 4));
+		TG_CUDA(cudaMemset(t.tc.err, 0, 4));
+		TG_CUDA(cudaHostAlloc(&t.err_host, 4, cudaHostAllocDefault));
+		*t.err_host = 0;
 	}
+	// The call only enqueues. The GEMM's error word is copied out behind it and looked at by the next call on
+	// this device (a wait that ran out shows up one call late instead of costing a synchronisation per step).
+	if (*static_cast<volatile int *>(t.err_host)) {
+		*t.err_host = 0;
+		cudaMemsetAsync(t.tc.err, 0, 4, st);
+		return fail(TG_ECUDA, "tensor-core GEMM: a pipeline wait ran out in an earlier tg_dev_lm_head_top1 on this device");
+	}
+	TG_CUDA(cudaMemsetAsync(t.keys, 0, size_t(M) * 8, st));
+	TG_TRY(pack_activations(hidden_dev, M, D, t.tc, st));
+	QW slice{m->lm_head.q + col0, m->lm_head.s + col0, D, ncols, V};
+	TcScratch one = t.tc;
+	one.top1 = t.keys;
+	one.top1_col0 = col0;
+	float *Cs[1] = {nullptr};
+	const QW *ws[1] = {&slice};
+	TG_TRY(launch_gemm_tc_group(1, Cs, ws, nullptr, M, one, st, 1));
+	top1_unpack_kernel<<<(M + 127) / 128, 128, 0, st>>>(t.keys, M, max_dev, idx_dev);
+	count_launch();
+	TG_TRY(check_launch("top1_unpack"));
+	TG_CUDA(cudaMemcpyAsync(t.err_host, t.tc.err, 4, cudaMemcpyDeviceToHost, st));
 	return TG_OK;
+}
+
+// gathered candidates [world][2][M] (row 0: maxima as fp32 bits, row 1: global indices) -> tokens of rows
+// row0 .. row0 + nrows: the largest maximum, among equal maxima the lowest index (the tie rule of
+// ops::argmax_logits, reference ops.hpp:744-760); a slice without a candidate (index -1) never wins; -1 if none has one
+__global__ void resolve_top1_kernel(const int *cand, int world, int M, int row0, int nrows, int *toks) {
+	const int r = blockIdx.x * blockDim.x + threadIdx.x;
+	if (r >= nrows) return;
+	float best = -INFINITY;
+	int arg = -1;
+	for (int w = 0; w < world; w++) {
+		const float v = __int_as_float(cand[(size_t(w) * 2) * M + row0 + r]);
+		const int i = cand[(size_t(w) * 2 + 1) * M + row0 + r];
+		if (i < 0) continue;
+		if (arg < 0 || v > best || (v == best && i < arg)) {
+			best = v;
+			arg = i;
+		}
+	}
+	toks[r] = arg;
+}
+
+int tg_dev_resolve_top1(const void *cand_all_dev, int world, int M, int row0, int nrows, int *toks_dev, void *stream) {
+	if (!cand_all_dev || !toks_dev || world < 1 || M < 1 || row0 < 0 || nrows < 1 || row0 + nrows > M)
+		return fail(TG_EINVAL, "bad argument");
+	resolve_top1_kernel<<<(nrows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(static_cast<const int *>(cand_all_dev), world, M, row0, nrows, toks_dev);
+	count_launch();
+	return check_launch("resolve_top1");
 }
 
 // ---------------------------------------------------------------- isolated ops

@@ -14,7 +14,11 @@ layers for its own sequences. Per decode step
 
 Both exchanges are a few KB to ~1 MB: latency-bound NCCL all-gathers over NVLink.
 The collectives go through torch.distributed (NCCL on GPUs, gloo in the CPU
-tests of this logic); the scoring and the forward are the library's kernels.
+tests of this logic); the forward, the scoring (one tensor-core GEMM over the
+slice with a row-maximum epilogue) and the resolution of the candidates are the
+library's kernels. resolve_candidates / sharded_greedy_step below are the same
+logic in torch operations: the form the gloo tests run, and the checker of the
+device kernel.
 """
 
 from __future__ import annotations
@@ -69,7 +73,11 @@ def sharded_greedy_step(torch, dist, hidden_local, score_slice, rank: int, world
 
 
 class ShardedGreedyDecoder:
-    """Greedy decoding of this rank's sequences with the lm_head sharded over `world` GPUs."""
+    """Greedy decoding of this rank's sequences with the lm_head sharded over `world` GPUs.
+
+    A step only enqueues: the layers, both all-gathers (NCCL, ordered after the state's stream, which is
+    made torch's current stream), the slice scoring and the candidate resolution run back to back on the
+    device; nothing waits on the host until the caller reads the tokens or calls state.check()."""
 
     def __init__(self, torch, dist, model, state, rank: int, world: int):
         self.torch, self.dist = torch, dist
@@ -77,24 +85,29 @@ class ShardedGreedyDecoder:
         self.rank, self.world = rank, world
         self.V = model.cfg.n_vocab
         self.D = model.cfg.hidden_size
+        b, M = state.B, world * state.B
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.hidden = torch.empty((state.B, self.D), dtype=torch.float32, device=dev)
-        self.maxs = torch.empty(world * state.B, dtype=torch.float32, device=dev)
-        self.idxs = torch.empty(world * state.B, dtype=torch.int32, device=dev)
-        self.toks = torch.empty(state.B, dtype=torch.int32, device=dev)
-
-    def _score(self, hidden_all, col0, ncols):
-        self.torch.cuda.current_stream().synchronize()
-        self.model.lm_head_top1_dev(hidden_all.data_ptr(), hidden_all.shape[0], col0, ncols, self.maxs.data_ptr(),
-                                    self.idxs.data_ptr(), self.torch.cuda.current_stream().cuda_stream)
-        return self.maxs, self.idxs
+        self.stream = torch.cuda.ExternalStream(state.stream())
+        self.hidden = torch.empty((b, self.D), dtype=torch.float32, device=dev)
+        self.hidden_all = torch.empty((M, self.D), dtype=torch.float32, device=dev)
+        self.cand = torch.empty((2, M), dtype=torch.int32, device=dev)  # row 0: maxima (fp32 bits), row 1: global indices
+        self.cand_all = torch.empty((world * 2, M), dtype=torch.int32, device=dev)
+        self.toks = torch.empty(b, dtype=torch.int32, device=dev)
+        self.col0, self.ncols = shard_columns(self.V, rank, world)
 
     def step(self, ids=None):
-        """feed `ids` (host, [b]) or the tokens of the previous step; returns the new tokens [b] (device int32)"""
-        self.state.decode_hidden(ids)
-        self.state.hidden_copy_dev(self.hidden.data_ptr())
-        toks = sharded_greedy_step(self.torch, self.dist, self.hidden, self._score, self.rank, self.world, self.V)
-        self.toks.copy_(toks.to(self.torch.int32))
-        self.torch.cuda.current_stream().synchronize()
-        self.state.set_tokens_dev(self.toks.data_ptr())
+        """feed `ids` (host, [b]) or the tokens of the previous step; returns the new tokens [b] (device int32,
+        valid in stream order on the state's stream)"""
+        torch, st = self.torch, self.stream.cuda_stream
+        M = self.hidden_all.shape[0]
+        with torch.cuda.stream(self.stream):
+            self.state.decode_hidden(ids)
+            self.state.hidden_copy_dev(self.hidden.data_ptr())
+            self.dist.all_gather_into_tensor(self.hidden_all, self.hidden)
+            self.model.lm_head_top1_dev(self.hidden_all.data_ptr(), M, self.col0, self.ncols, self.cand[0].data_ptr(),
+                                        self.cand[1].data_ptr(), st)
+            self.dist.all_gather_into_tensor(self.cand_all, self.cand)
+            self.model.resolve_top1_dev(self.cand_all.data_ptr(), self.world, M, self.rank * self.state.B, self.state.B,
+                                        self.toks.data_ptr(), st)
+            self.state.set_tokens_dev(self.toks.data_ptr())
         return self.toks

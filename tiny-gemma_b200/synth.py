@@ -109,45 +109,55 @@ def file_size(size: str) -> int:
     return layout(size)[-1][3]
 
 
-def write_random_model(path: str, size: str, seed: int = 0, std: float = 0.02) -> str:
-    """Write seeded N(0, std) weights (norm weights included, lm_head tied to
-    wte before quantisation) to ``path``; returns ``path``. Skips the work if a
-    file of the right size is already there (callers encode size/seed in the
-    name)."""
+def random_tensors(size: str, seed: int = 0, std: float = 0.02):
+    """The seeded N(0, std) fp32 tensors of a model in file order, as (name, array): wte [V, D], final_norm,
+    then per layer q, k, v, o, q_norm, k_norm, attn_pre, attn_post, up, gate, down, mlp_pre, mlp_post
+    (names prefixed l<layer>.). The lm_head is tied: wte.T."""
     c = CONFIGS[size]
-    want = file_size(size)
-    if os.path.exists(path) and os.path.getsize(path) == want:
-        return path
     rng = np.random.default_rng(seed)
 
     def normal(*shape):
         return (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
 
+    yield "wte", normal(c.n_vocab, c.hidden_size)
+    yield "final_norm", normal(c.hidden_size)
+    for l in range(c.n_layers):
+        p = "l%d." % l
+        yield p + "q", normal(c.hidden_size, c.q_dim)
+        yield p + "k", normal(c.hidden_size, c.kv_dim)
+        yield p + "v", normal(c.hidden_size, c.kv_dim)
+        yield p + "o", normal(c.q_dim, c.hidden_size)
+        yield p + "q_norm", normal(c.head_dim)
+        yield p + "k_norm", normal(c.head_dim)
+        yield p + "attn_pre", normal(c.hidden_size)
+        yield p + "attn_post", normal(c.hidden_size)
+        yield p + "up", normal(c.hidden_size, c.intermediate_size)
+        yield p + "gate", normal(c.hidden_size, c.intermediate_size)
+        yield p + "down", normal(c.intermediate_size, c.hidden_size)
+        yield p + "mlp_pre", normal(c.hidden_size)
+        yield p + "mlp_post", normal(c.hidden_size)
+
+
+def write_random_model(path: str, size: str, seed: int = 0, std: float = 0.02) -> str:
+    """Write the tensors of random_tensors (norm weights included, lm_head tied to
+    wte before quantisation) to ``path`` in the gemma_i8.bin layout (reference
+    ``py/gemma.py:27-77``); returns ``path``. Skips the work if a file of the
+    right size is already there (callers encode size/seed in the name)."""
+    want = file_size(size)
+    if os.path.exists(path) and os.path.getsize(path) == want:
+        return path
     tmp = path + ".tmp%d" % os.getpid()
     with open(tmp, "wb") as f:
-
-        def put_q(w):
-            q, s = quantize_weight(w)
-            f.write(np.ascontiguousarray(q).data)
-            f.write(np.ascontiguousarray(s).data)
-
-        wte = normal(c.n_vocab, c.hidden_size)
-        put_q(wte)
-        f.write(normal(c.hidden_size).data)
-        for _ in range(c.n_layers):
-            put_q(normal(c.hidden_size, c.q_dim))
-            put_q(normal(c.hidden_size, c.kv_dim))
-            put_q(normal(c.hidden_size, c.kv_dim))
-            put_q(normal(c.q_dim, c.hidden_size))
-            f.write(normal(c.head_dim).data)
-            f.write(normal(c.head_dim).data)
-            f.write(normal(c.hidden_size).data)
-            f.write(normal(c.hidden_size).data)
-            put_q(normal(c.hidden_size, c.intermediate_size))
-            put_q(normal(c.hidden_size, c.intermediate_size))
-            put_q(normal(c.intermediate_size, c.hidden_size))
-            f.write(normal(c.hidden_size).data)
-            f.write(normal(c.hidden_size).data)
+        wte = None
+        for name, w in random_tensors(size, seed, std):
+            if w.ndim == 2:
+                q, s = quantize_weight(w)
+                f.write(np.ascontiguousarray(q).data)
+                f.write(np.ascontiguousarray(s).data)
+                if name == "wte":
+                    wte = w
+            else:
+                f.write(w.data)
         # tied embeddings: lm_head = wte.T as floats, quantised per vocab column
         s_v = (np.max(np.abs(wte), axis=1) / 127.0).astype(np.float32)  # [V]
         q = np.rint(wte / s_v[:, None]).astype(np.int8)  # [V, D]
