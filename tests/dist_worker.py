@@ -82,11 +82,11 @@ def run_gpu(rank, world):
     st.prefill(prompts, want_logits=False)
     dec = sharded.ShardedGreedyDecoder(torch, dist, m, st, rank, world)
     got = []
-    toks = dec.step(first)
-    got.append(toks.cpu().numpy().copy())
+    dec.step(first)
+    got.append(dec.tokens_host())
     for _ in range(steps - 1):
-        toks = dec.step(None)
-        got.append(toks.cpu().numpy().copy())
+        dec.step(None)
+        got.append(dec.tokens_host())
     got = np.stack(got)
     assert np.array_equal(got, want), (rank, got.T, want.T)
     st.close()

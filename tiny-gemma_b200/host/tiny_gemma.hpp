@@ -27,7 +27,11 @@
 #include <unordered_map>
 #include <vector>
 
+#include <chrono>
+#include <iostream>
+
 #include "../../include/tiny_gemma_b200.h"
+#include "tokenizer.hpp"
 
 namespace constants {  // reference constants.hpp:4-10
 static constexpr size_t simd{8};
@@ -124,6 +128,15 @@ inline void check(int rc) {
 }
 }  // namespace tg_detail
 
+namespace ops_detail {  // the two samplers on host logits (ops::argmax_logits / ops::minp_logits below forward to these)
+inline void argmax(tensor::tokens *toks, tensor::activation *o) {
+	tg_detail::check(tg_argmax_logits(o->data.get(), int(constants::vocab), &toks->data[0]));
+}
+inline void minp(tensor::tokens *toks, tensor::activation *o, float minp, float temp, float randf) {
+	tg_detail::check(tg_minp_logits(o->data.get(), int(constants::vocab), minp, temp, randf, &toks->data[0]));
+}
+}  // namespace ops_detail
+
 namespace lut {  // reference ops.hpp:16-51
 struct GeLUTable {
 	float min, max;
@@ -187,6 +200,7 @@ struct DecodeState {  // decode.hpp:215-276: owns the KV caches of one batch of 
 
 namespace gemma {
 using config::Config;
+using config::CONFIG_MAP;  // gemma.cpp:38 reads gemma::CONFIG_MAP
 using lut::GeLUTable;
 
 struct Transformer {  // transformer.hpp:22-47
@@ -252,6 +266,70 @@ inline std::vector<int> generate_tokens(int first_token, int n_decode, Transform
 	tg_detail::check(tg_generate(d->gpu, first.data(), n_decode, minp, temp, minp < 1 ? randf.data() : nullptr, out.data()));
 	return out;
 }
+
+// transformer.hpp:167-258: tokenize, prefill, sample, n_decode x (forward_decode + sampler), streaming the
+// decoded pieces to stdout; returns {decode steps completed, generated text, prefill seconds, decode seconds}.
+// The decode steps run on the device in chunks (the token never leaves the GPU inside a chunk); pieces are
+// printed chunk by chunk, and with terminate_on_end the first <end_of_turn> ends the text (steps the chunk ran
+// past it are dropped). The uniforms are drawn from std::mt19937 in the reference's order: one for the
+// token after the prompt, then one per step. seed == nullptr seeds from std::random_device as the reference does.
+inline std::tuple<int, std::string, float, float> generate(std::string prompt, int n_decode, sentencepiece::Tokenizer *tokenizer,
+                                                           Transformer *t, const float minp, const float temp,
+                                                           const bool terminate_on_end, const unsigned *seed = nullptr,
+                                                           int chunk = 16) {
+	auto t_prefill_s = std::chrono::high_resolution_clock::now();
+	std::random_device rd;
+	std::mt19937 gen(seed ? *seed : rd());
+	std::uniform_real_distribution<float> unif(0.0, 1.0);
+	std::vector<int> ids = tokenizer->encode(prompt);
+	const size_t prompt_len = ids.size();
+	std::string decoded;
+	decoded.reserve(size_t(n_decode > 0 ? n_decode : 0));
+	printf("Prompt length: %lu\n", (unsigned long)prompt_len);
+	std::cout << tokenizer->decode(ids);
+
+	auto tokens_data = tensor::make_unique_aligned<int>(prompt_len);
+	for (size_t i = 0; i < prompt_len; i++) tokens_data[i] = ids[i];
+	decode::RoPE rope(&(t->cfg), false);
+	decode::RoPE rope_sw(&(t->cfg), true);
+	lut::GeLUTable table{-4.0, 4.0, 1024};
+	decode::DecodeState d(1, &(t->cfg));
+	tensor::tokens tokens(tokens_data, 1, prompt_len);
+	tensor::activation o(1, 1, t->cfg.n_vocab);
+	forward_prefill(&o, &tokens, t, &d, &rope, &rope_sw, &table);
+	tensor::tokens tokens_decode(1, 1);
+	if (minp < 1)
+		ops_detail::minp(&tokens_decode, &o, minp, temp, unif(gen));
+	else
+		ops_detail::argmax(&tokens_decode, &o);
+	int prev_token = ids[ids.size() - 1];
+	std::cout << tokenizer->decode(tokens_decode.data[0], prev_token) << std::flush;
+	prev_token = tokens_decode.data[0];
+	auto t_prefill_e = std::chrono::high_resolution_clock::now();
+
+	auto t_decode_s = std::chrono::high_resolution_clock::now();
+	int done = 0;
+	bool ended = false;
+	while (done < n_decode && !ended) {
+		const int n = std::min(chunk, n_decode - done);
+		const std::vector<int> out = generate_tokens(prev_token, n, t, &d, &rope, &rope_sw, &table, minp, temp, gen);
+		for (int i = 0; i < n; i++) {
+			if (terminate_on_end && out[i] == tokenizer->get_eot_id()) {
+				ended = true;
+				break;
+			}
+			const std::string piece = tokenizer->decode(out[i], prev_token);
+			decoded.append(piece);
+			std::cout << piece << std::flush;
+			prev_token = out[i];
+			done++;
+		}
+	}
+	auto t_decode_e = std::chrono::high_resolution_clock::now();
+	const double s_prefill = (t_prefill_e - t_prefill_s).count() / 1e9;
+	const double s_decode = (t_decode_e - t_decode_s).count() / 1e9;
+	return {done, decoded, float(s_prefill), float(s_decode)};
+}
 }  // namespace gemma
 
 namespace ops {  // reference ops.hpp: host-buffer operators
@@ -259,11 +337,9 @@ using tensor::activation;
 using tensor::tokens;
 using tensor::weight;
 
-inline void argmax_logits(tokens *toks, activation *o) {  // ops.hpp:744-760
-	tg_detail::check(tg_argmax_logits(o->data.get(), int(constants::vocab), &toks->data[0]));
-}
+inline void argmax_logits(tokens *toks, activation *o) { ops_detail::argmax(toks, o); }  // ops.hpp:744-760
 inline void minp_logits(tokens *toks, activation *o, float minp, float temp, float randf) {  // ops.hpp:762-859
-	tg_detail::check(tg_minp_logits(o->data.get(), int(constants::vocab), minp, temp, randf, &toks->data[0]));
+	ops_detail::minp(toks, o, minp, temp, randf);
 }
 inline void linear_decode(activation *o, activation *a, weight<int8_t> *w) {  // ops.hpp:634-649
 	tg_detail::check(tg_qmatvec(o->data.get(), a->data.get(), w->data.get(), w->scales.get(), int(w->rows), int(w->cols)));

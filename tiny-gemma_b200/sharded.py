@@ -111,3 +111,8 @@ class ShardedGreedyDecoder:
                                         self.toks.data_ptr(), st)
             self.state.set_tokens_dev(self.toks.data_ptr())
         return self.toks
+
+    def tokens_host(self):
+        """the tokens of the last step as a numpy array (waits for the state's stream)"""
+        with self.torch.cuda.stream(self.stream):
+            return self.toks.cpu().numpy().copy()
