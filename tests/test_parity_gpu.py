@@ -369,6 +369,36 @@ def test_batched_decode_tensor_core_step(capi, model_270m, synth):
     model_270m.build_tables(1024)
 
 
+@pytest.mark.parametrize("size", ["270m", "1B"])
+def test_both_persistent_decode_kernels_agree(capi, synth, weights_270m, weights_1b, size, monkeypatch):
+    """The batch-1 decode path is the dp4a kernel (24-bit block fixed-point activations, exact integer products);
+    TG_PERSIST=0 selects the fp32-FMA kernel it replaced, which stays as the fall-back for shapes without a plan.
+    Same prompt, smooth GeLU table: logits of the last of 24 steps within 2e-5, greedy tokens equal where the top-2
+    gap is above that noise."""
+    m = capi.Model(size).load_file(weights_270m if size == "270m" else weights_1b).build_tables(1 << 20)
+    ids = synth.random_prompt(40, 17)
+    out = {}
+    for persist in ("1", "0"):
+        monkeypatch.setenv("TG_PERSIST", persist)
+        st = m.state(1, 128)
+        st.prefill(ids, want_logits=False)
+        tok = st.sample_argmax()
+        toks, gaps = [], []
+        for _ in range(24):
+            lg = st.decode(tok)[0]
+            t2 = np.partition(lg, -2)[-2:]
+            gaps.append(float(t2[1] - t2[0]))
+            tok = st.sample_argmax()
+            toks.append(int(tok[0]))
+        out[persist] = (toks, gaps, lg)
+        st.close()
+    monkeypatch.delenv("TG_PERSIST")
+    assert rel_l2(out["1"][2], out["0"][2]) <= 2e-5
+    first = next((i for i in range(24) if out["1"][0][i] != out["0"][0][i]), 24)
+    assert first == 24 or min(out["1"][1][first], out["0"][1][first]) < 1e-3, (first, out["1"][0], out["0"][0])
+    m.close()
+
+
 def test_bounded_wait_returns_an_error_and_the_context_survives(capi, synth, weights_270m, monkeypatch):
     """The persistent decode kernel's waits are bounded by a host-settable limit (TG_PS_WAIT_MS). With one
     producer CTA told to withhold its down-projection hand-off (TG_PS_WITHHOLD_CTA, a debug argument of the

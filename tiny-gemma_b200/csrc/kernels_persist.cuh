@@ -131,6 +131,8 @@ struct PsArgs {
 	long long *gt;  // optional: [CTA][12] global-timer marks of one layer (DBG instantiation)
 	int dbg_flags;  // DBG instantiation: bit 0 = run the up/gate product twice (stamps both: cold vs warm code)
 	int *beacon;    // optional (mapped host memory): [CTA][16] progress marks of every warp, for diagnosing a stall
+	int e_rows;     // 1: the down projection runs by K-parts per warp (ps_product_rows), e_wq quads per warp
+	int e_wq;
 	int fault_cta;  // test hook: this CTA withholds its down-projection hand-off (-1: none); the waits then run out
 };
 
@@ -309,7 +311,7 @@ __device__ __forceinline__ int ps_exponent(float bound) {
 	return max(-100, min(100, eb - 126));
 }
 __device__ __forceinline__ float ps_pow2(int e) { return __uint_as_float(uint32_t(e + 127) << 23); }
-__device__ __noinline__ void ps_quantise(float4 y, float qs, uint32_t *xd, int stride, int q) {
+__device__ __forceinline__ void ps_quantise(float4 y, float qs, uint32_t *xd, int stride, int q) {
 	__builtin_assume(__isShared(xd));
 	int v[4];
 	v[0] = __float2int_rn(y.x * qs);
@@ -465,6 +467,11 @@ struct PsOut {
 	float r0, r1;
 	int flags;
 };
+// what a CTA's place in the grid fixes for the whole launch (kept in shared memory, read where it is used)
+struct PsCta {
+	const int8_t *srcA, *srcC, *srcD, *srcE;
+	int tileA, tileC, splitC, tileE, splitE, presE, uD, has;
+};
 __device__ __noinline__ PsOut ps_product(uint32_t tile_s, int ngroups, int nq, int kp, int wq, bool two, uint32_t xd_s, int xs,
                                          uint32_t part_s, uint32_t cnt_s, long long *trace = nullptr) {
 	PsOut o{0.0f, 0.0f, 0};
@@ -528,6 +535,91 @@ __device__ __noinline__ PsOut ps_product(uint32_t tile_s, int ngroups, int nq, i
 		}
 	}
 	if (pub) o.flags = 1 | (ps_last(cnt_s, ngroups) ? 2 : 0);
+	if (trace && lane == 0) trace[warp * 4 + 3] = clock64();
+	return o;
+}
+
+// Down projection without a CTA-wide prologue. Warp w takes K-part w of the unit (quads w * wq .. of every
+// group; lane -> quads lane, lane + 32, lane + 64 of the part, wq <= 96): it polls ITS rows of the activation
+// vector, quantises them with a warp-local exponent into registers, multiplies them with all ngroups <= 4
+// groups of the tile and leaves scaled fp32 partial sums in part_s[w][16]. The warp that finishes last adds
+// the PS_NW parts in part order: its lanes 0 .. 4 * ngroups - 1 return the raw sums of columns
+// 4 * group + (lane & 3), group = lane / 4, in r0, with flags = 3. No warp waits for another warp's rows, so
+// a late producer delays only the part that needs it. part_s: PS_NW * 16 floats; cnt_s: one counter.
+__device__ __noinline__ PsOut ps_product_rows(const PsW w, int where, uint32_t tile_s, int ngroups, int nq, int wq, const float *act,
+                                              uint32_t part_s, uint32_t cnt_s, long long *trace = nullptr) {
+	PsOut o{0.0f, 0.0f, 0};
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	if (trace && lane == 0) trace[warp * 4] = clock64();
+	const int qb = warp * wq, qe = min(nq, qb + wq);  // this warp's quads
+	float4 v[3];
+	{
+		int spins = 0;
+		long long t0 = 0;
+		bool ok;
+		do {
+			ok = true;
+#pragma unroll
+			for (int i = 0; i < 3; i++) {
+				const int q = qb + lane + 32 * i;
+				v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+				if (q < qe) v[i] = ps_ld4(act + 4 * q);
+				ok = ok && ps_ok(v[i]);
+			}
+		} while (!ok && ps_retry(w, where, spins, t0));
+	}
+	float mx = 0.0f;
+#pragma unroll
+	for (int i = 0; i < 3; i++) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+	mx = warp_max(mx);
+	if (trace && lane == 0) trace[warp * 4 + 1] = clock64();
+	const int e = ps_exponent(mx * 1.000001f);
+	const float qs = ps_pow2(23 - e), back = ps_pow2(e - 23);
+	uint32_t x0[3], x1[3], x2[3];
+#pragma unroll
+	for (int i = 0; i < 3; i++) {
+		int d[4];
+		d[0] = __float2int_rn(v[i].x * qs);
+		d[1] = __float2int_rn(v[i].y * qs);
+		d[2] = __float2int_rn(v[i].z * qs);
+		d[3] = __float2int_rn(v[i].w * qs);
+#pragma unroll
+		for (int j = 0; j < 4; j++) d[j] = max(-8388607, min(8388607, d[j]));
+		const uint32_t p01 = __byte_perm(d[0], d[1], 0x5140), p23 = __byte_perm(d[2], d[3], 0x5140);
+		const uint32_t h01 = __byte_perm(d[0], d[1], 0x0062), h23 = __byte_perm(d[2], d[3], 0x0062);
+		x0[i] = __byte_perm(p01, p23, 0x5410);
+		x1[i] = __byte_perm(p01, p23, 0x7632);
+		x2[i] = __byte_perm(h01, h23, 0x5410);
+	}
+	// quads past the part multiply zeros; their tile address is clamped into the part
+	uint32_t ta[3];
+#pragma unroll
+	for (int i = 0; i < 3; i++) ta[i] = tile_s + 16u * uint32_t(min(qb + lane + 32 * i, qe - 1));
+#pragma unroll 1
+	for (int g = 0; g < ngroups; g += 2) {
+		PsAcc a0, a1;
+#pragma unroll
+		for (int i = 0; i < 12; i++) a0.v[i] = a1.v[i] = 0;
+		const uint32_t g0 = 16u * uint32_t(g * nq), g1 = 16u * uint32_t(min(g + 1, ngroups - 1) * nq);
+#pragma unroll
+		for (int i = 0; i < 3; i++) {
+			ps_mac(a0, ps_lds128(ta[i] + g0), x0[i], x1[i], x2[i]);
+			ps_mac(a1, ps_lds128(ta[i] + g1), x0[i], x1[i], x2[i]);
+		}
+		const float2 r = ps_finish2(a0, a1);
+		if (lane < 4) {
+			ps_stsf(part_s + 4u * (warp * 16 + 4 * g + lane), r.x * back);
+			if (g + 1 < ngroups) ps_stsf(part_s + 4u * (warp * 16 + 4 * g + 4 + lane), r.y * back);
+		}
+	}
+	if (trace && lane == 0) trace[warp * 4 + 2] = clock64();
+	if (ps_last(cnt_s, PS_NW)) {
+		o.flags = 3;
+		if (lane < 4 * ngroups) {
+#pragma unroll
+			for (int p = 0; p < PS_NW; p++) o.r0 += ps_ldsf(part_s + 4u * (p * 16 + lane));
+		}
+	}
 	if (trace && lane == 0) trace[warp * 4 + 3] = clock64();
 	return o;
 }
@@ -1269,7 +1361,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	uint8_t *smem = reinterpret_cast<uint8_t *>((uintptr_t(smem_raw) + 127) & ~uintptr_t(127));  // the host adds 128 bytes of slack
 	__shared__ uint64_t bar_A, bar_C, bar_D, bar_E, bar_lm[8], emp_lm[8];
 	__shared__ float bred[3 * PS_NW];
-	__shared__ float s_part[PS_NW * 8];
+	__shared__ float s_part[PS_NW * 16];
 	__shared__ int s_cnt[PS_NW + 4];
 	__shared__ float s_xscale;
 	__shared__ int s_abort;
@@ -1279,11 +1371,21 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	__shared__ float wm[3 * PS_NW];  // per-warp (m, l, weight) of the attention merge; also the sampler's per-warp maxima
 	__shared__ PsLayer s_ly[PS_MAX_LAYERS];
 
-	uint8_t *R_A = smem + a.off_A, *R_C = smem + a.off_C, *R_D = smem + a.off_D, *R_E = smem + a.off_E;
-	float *h = reinterpret_cast<float *>(smem + a.off_h);
-	uint32_t *xd = reinterpret_cast<uint32_t *>(smem + a.off_xd);
-	float *att = reinterpret_cast<float *>(smem + a.off_att);  // wo[12][256] | qraw[768] (q_h, k, v) | qs[256]
-	const uint32_t xd_s = ps_smem(xd), part_s = ps_smem(s_part), cnt_s = ps_smem(s_cnt);
+#define R_A (smem + a.off_A)
+#define R_C (smem + a.off_C)
+#define R_D (smem + a.off_D)
+#define R_E (smem + a.off_E)
+	// (recomputed where they are used: a value that lives across the whole token loop costs a register, and the
+	// registers this kernel cannot have are spilled to local memory, which the small L1 left beside 224 KB of
+	// shared memory does not hold)
+#define h (reinterpret_cast<float *>(smem + a.off_h))
+#define xd (reinterpret_cast<uint32_t *>(smem + a.off_xd))
+#define att (reinterpret_cast<float *>(smem + a.off_att))  /* wo[12][256] | qraw[768] (q_h, k, v) | qs[256] */
+#define xd_s (ps_smem(smem + a.off_xd))
+#define part_s (ps_smem(s_part))
+#define cnt_s (ps_smem(s_cnt))
+#define pol (ps_evict_first())
+#define keep (ps_evict_last())
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int cta = blockIdx.x, G = gridDim.x;
@@ -1313,18 +1415,43 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	const PsW pw{&s_abort, a.err, a.wait_clocks, unsigned(a.poll_ns)};
 	unsigned epoch = 0;  // grid barriers passed
 	uint32_t pA = 0, pC = 0, pD = 0, pE = 0, plm = 0, pemp = 0;
-	const uint64_t pol = ps_evict_first(), keep = ps_evict_last();
 
-	const int uA = cta - a.A.cta0, uC = cta - a.C.cta0, uD = cta - a.Dp.cta0, uE = cta - a.E.cta0;
-	const bool hasA = uA >= 0 && uA < a.A.units, hasC = uC >= 0 && uC < a.C.units;
-	const bool hasD = uD >= 0 && uD < a.Dp.units, hasE = uE >= 0 && uE < a.E.units;
-	const int tileA = hasA ? uA % a.A.ntiles : 0;
-	const int tileC = hasC ? uC % a.C.ntiles : 0, splitC = hasC ? uC / a.C.ntiles : 0;
-	const int tileE = hasE ? uE % a.E.ntiles : 0, splitE = hasE ? uE / a.E.ntiles : 0;
-	const int presE = uE < 0 ? cta : cta - a.E.units;  // index of this CTA's presence word (if !hasE)
-	// the unit this CTA fetches for a phase of layer l (one lane issues the copy)
-	const int8_t *srcA = a.tiled + a.tl_A + size_t(hasA ? uA : 0) * a.A.bytes, *srcC = a.tiled + a.tl_C + size_t(hasC ? uC : 0) * a.C.bytes;
-	const int8_t *srcD = a.tiled + a.tl_D + size_t(hasD ? uD : 0) * a.Dp.bytes, *srcE = a.tiled + a.tl_E + size_t(hasE ? uE : 0) * a.E.bytes;
+	__shared__ PsCta s_c;
+	{
+		const int uA = cta - a.A.cta0, uC = cta - a.C.cta0, uD = cta - a.Dp.cta0, uE = cta - a.E.cta0;
+		const bool hA = uA >= 0 && uA < a.A.units, hC = uC >= 0 && uC < a.C.units, hD = uD >= 0 && uD < a.Dp.units, hE = uE >= 0 && uE < a.E.units;
+		if (tid == 0) {
+			s_c.tileA = hA ? uA % a.A.ntiles : 0;
+			s_c.tileC = hC ? uC % a.C.ntiles : 0;
+			s_c.splitC = hC ? uC / a.C.ntiles : 0;
+			s_c.tileE = hE ? uE % a.E.ntiles : 0;
+			s_c.splitE = hE ? uE / a.E.ntiles : 0;
+			s_c.presE = uE < 0 ? cta : cta - a.E.units;  // index of this CTA's presence word (if !hasE)
+			s_c.uD = uD;
+			// the unit this CTA fetches for a phase of layer l (one lane issues the copy)
+			s_c.srcA = a.tiled + a.tl_A + size_t(hA ? uA : 0) * a.A.bytes;
+			s_c.srcC = a.tiled + a.tl_C + size_t(hC ? uC : 0) * a.C.bytes;
+			s_c.srcD = a.tiled + a.tl_D + size_t(hD ? uD : 0) * a.Dp.bytes;
+			s_c.srcE = a.tiled + a.tl_E + size_t(hE ? uE : 0) * a.E.bytes;
+			s_c.has = (hA ? 1 : 0) | (hC ? 2 : 0) | (hD ? 4 : 0) | (hE ? 8 : 0);
+		}
+		__syncthreads();
+	}
+#define hasA ((s_c.has & 1) != 0)
+#define hasC ((s_c.has & 2) != 0)
+#define hasD ((s_c.has & 4) != 0)
+#define hasE ((s_c.has & 8) != 0)
+#define tileA (s_c.tileA)
+#define tileC (s_c.tileC)
+#define splitC (s_c.splitC)
+#define tileE (s_c.tileE)
+#define splitE (s_c.splitE)
+#define presE (s_c.presE)
+#define uD (s_c.uD)
+#define srcA (s_c.srcA)
+#define srcC (s_c.srcC)
+#define srcD (s_c.srcD)
+#define srcE (s_c.srcE)
 
 	if (tid == 0) {
 		if (hasA) ps_issue(R_A, srcA, a.A.bytes, &bar_A, pol, &s_abort);
@@ -1402,6 +1529,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				}
 				if (actE) scE = ps_ldk(ly.sd + colE, keep);
 			}
+			if (a.e_rows && hasE && lane < 4 * a.E.ngroups) scE = ps_ldk(ly.sd + tileE * a.E.ngroups * 4 + lane, keep);
 			// The units were requested a layer ago: test their barriers early, so that the (long) latency of the
 			// test hides behind the hand-off polls instead of following them.
 			const bool rdyA = actA && ps_mbar_test(&bar_A, pA), rdyC = actC && ps_mbar_test(&bar_C, pC);
@@ -1537,7 +1665,27 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 			}
 			// ============================================================ E: down projection
 			{
-				const bool rdyE = actE && ps_mbar_test(&bar_E, pE);
+				const bool rdyE = hasE && ps_mbar_test(&bar_E, pE);
+				if (a.e_rows && hasE) {
+					// no prologue: every warp polls and quantises its own rows inside the product
+					PS_STAMP();
+					PS_GT(8);
+					PS_BEACON(0x51);
+					if (!rdyE) ps_wait_bulk(pw, (l << 4) | 5, &bar_E, pE);
+					PS_STAMP();
+					const PsOut o = ps_product_rows(pw, (l << 4) | 5, ps_smem(R_E), a.E.ngroups, a.E.nq, a.e_wq, llb + a.ll_act + size_t(splitE) * a.E.nq * 4,
+					                                part_s, cnt_s + 4u * (PS_NW + 2),
+					                                (DBG && a.dbg && cta == a.dbg_cta && !more && l == L / 2) ? a.dbg + 3800 : nullptr);
+					if ((o.flags & 1) && lane < 4 * a.E.ngroups && cta != a.fault_cta)
+						ps_st(llb + a.ll_dn + size_t(splitE) * D + tileE * a.E.ngroups * 4 + lane, o.r0 * scE);
+					if (o.flags & 2) PS_GT_WARP(11);
+					PS_STAMP();
+					// every warp has left the up/gate product and this one: both regions are free
+					if (a.sched == 0 && (o.flags & 2) && l + 1 < L && lane == 0) {
+						ps_issue(R_E, srcE + size_t(l + 1) * a.tl_layer, a.E.bytes, &bar_E, pol, &s_abort);
+						if (hasD) ps_issue(R_D, srcD + size_t(l + 1) * a.tl_layer, a.Dp.bytes, &bar_D, pol, &s_abort);
+					}
+				} else {
 				if (hasE) {
 					ps_act_quant(pw, (l << 4) | 5, llb + a.ll_act + size_t(splitE) * a.E.nq * 4, a.E.nq, xd, bred, &s_xscale);
 				} else {
@@ -1560,6 +1708,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 					if (tid == 0) ps_st(llb + a.ll_pres + presE, 0.0f);
 					PS_STAMP();
 					PS_STAMP();
+				}
 				}
 				pE ^= 1;
 				PS_STAMP();
@@ -1612,6 +1761,33 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 		__syncthreads();
 	}
 	if (cta == 0 && tid == 0 && a.log_count) *a.log_count = n_logged;
+#undef h
+#undef xd
+#undef att
+#undef xd_s
+#undef part_s
+#undef cnt_s
+#undef pol
+#undef keep
+#undef R_A
+#undef R_C
+#undef R_D
+#undef R_E
+#undef hasA
+#undef hasC
+#undef hasD
+#undef hasE
+#undef tileA
+#undef tileC
+#undef splitC
+#undef tileE
+#undef splitE
+#undef presE
+#undef uD
+#undef srcA
+#undef srcC
+#undef srcD
+#undef srcE
 }
 
 }  // namespace tg

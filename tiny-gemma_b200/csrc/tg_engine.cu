@@ -1210,6 +1210,8 @@ int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp
 	a.dbg_cta = std::min(std::max(env_int("TG_MEGA_DBG_CTA", 0), 0), s->mega_grid - 1);
 	a.wait_clocks = (long long)(std::max(1, env_int("TG_PS_WAIT_MS", 100))) * 2000000ll;  // ~2 GHz
 	a.fault_cta = env_int("TG_PS_WITHHOLD_CTA", -1);
+	a.e_wq = (a.E.nq + PS_NW - 1) / PS_NW;
+	a.e_rows = (env_int("TG_PS_E_ROWS", 0) && a.E.ngroups <= 4 && a.e_wq <= 96) ? 1 : 0;
 	a.poll_ns = std::max(0, env_int("TG_PS_POLL_NS", 20));
 	a.sched = env_int("TG_PS_SCHED", 0);
 	a.dbg_flags = env_int("TG_PS_DBG_FLAGS", 0);
@@ -2029,10 +2031,12 @@ int tg_state_create(tg_model *m, int batch, int max_pos_global, tg_state **out) 
 		if (mrc != TG_OK) {
 			if (env_int("TG_MEGA", 1) == 2) rc = mrc;  // 2 = required
 			s->mega_ok = false;
-		} else if (env_int("TG_PERSIST", 0)) {
+		} else if (env_int("TG_PERSIST", 1)) {
+			// the dp4a kernel (kernels_persist.cuh) is the batch-1 decode path; a shape it has no plan for falls back
+			// to the fp32-FMA kernel (kernels_mega.cuh), which TG_PERSIST=0 also selects
 			int prc = persist_setup(s);
 			if (prc != TG_OK) {
-				if (env_int("TG_PERSIST", 0) == 2) rc = prc;  // 2 = required
+				if (env_int("TG_PERSIST", 1) == 2) rc = prc;  // 2 = required
 				s->ps_ok = false;
 			}
 		}
