@@ -565,7 +565,7 @@ def run_ours(args):
         return e0.elapsed_time(e1), pre_ms, pos0, n_launch, seq
 
     ms0, pre0, pos0, launches, dev_seq = one_repeat(count_launches=True)
-    R = int(max_over_ranks(env, [repeats_for(ms0)])[0])
+    R = args.repeats if args.repeats > 0 else int(max_over_ranks(env, [repeats_for(ms0)])[0])
     rep_ms, rep_pre = [ms0], [pre0]
     for _ in range(R - 1):
         ms, pre, _, _, _ = one_repeat()
@@ -619,7 +619,7 @@ def run_ours(args):
             torch.cuda.synchronize()
             times.append((time.perf_counter() - t0) * 1e3)
             if Re is None:
-                Re = int(max_over_ranks(env, [repeats_for(times[0])])[0])
+                Re = args.repeats if args.repeats > 0 else int(max_over_ranks(env, [repeats_for(times[0])])[0])
         e2e_reps.append(times)
     clk = clocks.stop()
     st.close()
@@ -824,6 +824,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens; 178 is the benchmark configuration, 16384 the long-context one "
                          "(use --no-extras: the CPU baseline sample would prefill the same prompt)")
+    ap.add_argument("--repeats", type=int, default=0,
+                    help="repeats of the timed loops; 0: as many as it takes to time one second (use 1 under a profiler)")
     ap.add_argument("--sharded", action="store_true", help="with --batch under torchrun: vocab-sharded lm_head")
     ap.add_argument("--phase-clocks", action="store_true", help="per-section timing of one decoded token (in-kernel recorder)")
     ap.add_argument("--greedy", action="store_true", help="with --phase-clocks: argmax instead of the min-p sampler")
