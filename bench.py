@@ -64,7 +64,7 @@ WEIGHT_SEED, PROMPT_SEED = 0, 77
 CACHE = os.environ.get("TG_CACHE_DIR", "/tmp")
 PUBLISHED_DECODE_TOK_S = 16.45  # reference README.md:69, Ryzen 5 5500, 1 thread, real weights
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded token from one ncu capture of the decode kernel
-DRAM_TRAFFIC_PER_STEP = {"1B": 1005668181, "270m": 273534288}
+DRAM_TRAFFIC_PER_STEP = {"1B": 1003642432, "270m": (1080847104 + 9990400) // 4}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
