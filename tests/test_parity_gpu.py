@@ -471,6 +471,35 @@ def test_error_paths(capi, model_270m, synth, tmp_path):
     m.close()
 
 
+def test_weight_load_paths_agree_and_reload_rebuilds_the_decode_copy(capi, synth, weights_270m, tmp_path):
+    """tg_model_load_file (pinned double buffer, chunked copies) and tg_model_load_memory give the same
+    model; loading other weights into the same model invalidates the decode kernel's re-tiled copies
+    (transformer.hpp:99-165 reads the file into the Transformer's own arrays; here it lands in HBM)."""
+    ids = synth.random_prompt(20, 8)
+
+    def run(m):
+        m.build_tables(1 << 20)
+        st = m.state(1, 64)
+        st.prefill(ids, want_logits=False)
+        lg = st.decode(st.sample_argmax())[0].copy()  # one step of the persistent kernel (re-tiled copies)
+        st.close()
+        return lg
+
+    a = capi.Model("270m").load_file(weights_270m)
+    la = run(a)
+    b = capi.Model("270m").load_bytes(np.fromfile(weights_270m, np.uint8))
+    assert np.array_equal(run(b), la)
+    b.close()
+    other = synth.write_random_model(str(tmp_path / "w1.bin"), "270m", seed=1)
+    a.load_file(other)
+    lo = run(a)
+    assert rel_l2(lo, la) > 0.1  # different weights, different logits: the old tiles are not reused
+    c = capi.Model("270m").load_file(other)
+    assert np.array_equal(run(c), lo)
+    a.close()
+    c.close()
+
+
 # ------------------------------------------------------------------ 1B
 def test_long_prompt_vs_live_reference_270m(capi, ref_or_none, weights_270m, synth):
     """2100-token prompt against the compiled reference run live: the local ring wraps four times, global
