@@ -102,3 +102,36 @@ def test_lm_head_top1_eight_slices_one_gpu(capi, synth, weights_270m, batch):
     assert torch.equal(cand2, cand_all)
     st.close()
     m.close()
+
+
+@pytest.mark.gpu
+def test_two_devices_in_one_process(capi, synth, weights_270m):
+    """Models on two GPUs of one process (the C ABI takes the device per model): the kernels' per-device
+    attributes (dynamic shared memory opt-in) must be set on each device, so prefill, the persistent decode
+    kernel, the batch-2 per-phase path and the batched tensor-core step all have to work on device 1 after
+    device 0 has used them, and give the same tokens."""
+    import numpy as np
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = []
+    for dev in (0, 1):
+        m = capi.Model("270m", device=dev).load_file(weights_270m).build_tables(1 << 20)
+        ids = synth.random_prompt(40, 21)
+        st = m.state(1, 128)
+        st.prefill(ids, want_logits=False)
+        t1 = st.generate(st.sample_argmax(), 8).ravel()
+        st.close()
+        st = m.state(2, 128)
+        st.prefill(np.stack([ids, ids[::-1]]), want_logits=False)
+        t2 = st.generate(st.sample_argmax(), 4).ravel()
+        st.close()
+        st = m.state(8, 128)
+        st.prefill(np.stack([synth.random_prompt(40, 30 + b) for b in range(8)]), want_logits=False)
+        t8 = st.generate(st.sample_argmax(), 4).ravel()
+        st.close()
+        m.close()
+        out.append((t1, t2, t8))
+    for a, b in zip(out[0], out[1]):
+        assert np.array_equal(a, b)
