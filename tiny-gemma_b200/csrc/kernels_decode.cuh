@@ -24,6 +24,8 @@ struct EmbedArgs {
 };
 
 __global__ void embed_decode_kernel(EmbedArgs a) {
+	pdl_trigger();
+	pdl_wait();
 	int b = blockIdx.x;
 	int tok = a.tok[b];
 	if (tok < 0 || tok >= a.V) {
@@ -463,6 +465,8 @@ __device__ __forceinline__ void norm_rope_head(const float *x, const float *w, c
 }
 
 __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
+	pdl_trigger();
+	pdl_wait();
 	__shared__ __align__(16) float qs[AT_NH][AT_HD];
 	__shared__ __align__(16) float ks[AT_HD];
 	__shared__ __align__(16) float vs[AT_HD];

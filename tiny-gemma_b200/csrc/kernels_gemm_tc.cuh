@@ -92,6 +92,8 @@ __device__ __forceinline__ void tc_pack8(__nv_bfloat16 *out, size_t term_stride,
 }
 
 __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bfloat16 *out, int M, int K, int m_tiles) {
+	pdl_trigger();
+	pdl_wait();
 	const int k_blocks = K / TC_BK;
 	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);  // one thread per (row, 8 consecutive k)
 	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
@@ -122,6 +124,8 @@ __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bf
 __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
                                                             __nv_bfloat16 *out, int M, int dim, int m_tiles, int nsplit,
                                                             int ldp, const float *tscale) {
+	pdl_trigger();
+	pdl_wait();
 	__shared__ float bred[8];
 	__shared__ float row_s[2048];
 	const int row = blockIdx.x, tid = threadIdx.x;
@@ -208,6 +212,8 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 // columns, then gate columns) and su / sg are the column scales; otherwise gate / up are finished.
 __global__ void __launch_bounds__(256) geglu_pack_kernel(const float *gate, const float *up, __nv_bfloat16 *out, int M, int K,
                                                           int m_tiles, GeluLut lut, int nsplit, const float *su, const float *sg) {
+	pdl_trigger();
+	pdl_wait();
 	const int k_blocks = K / TC_BK;
 	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);
 	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
@@ -368,6 +374,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
                                                                  const __grid_constant__ CUtensorMap wmap2, GemmTcArgs a) {
 	using SH = TcShape<MT, BN>;
 	constexpr int NA = SH::NA, NB = SH::NB;
+	pdl_trigger();
 	extern __shared__ uint8_t tc_smem_raw[];
 	uint8_t *smem = reinterpret_cast<uint8_t *>((uintptr_t(tc_smem_raw) + 1023) & ~uintptr_t(1023));
 	__shared__ uint64_t afull_bar[TcShape<MT, BN>::NA];  // A tiles of the stage landed (transaction bytes)
@@ -433,6 +440,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 	if (warp == 0) {
 		// ------------------------------------------------------------ producer of the A stages
 		if (lane == 0) {
+			// The packed activations are the predecessor's output: wait for it here. The weight producer
+			// (warp 6) does not wait: the weights are nobody's output, its first tiles land meanwhile. Everything
+			// this CTA writes (C, partial sums, tickets) follows MMAs that need these A tiles, so it is ordered
+			// behind the wait as well.
+			pdl_wait();
 			for (int kb = 0; kb < k_blocks; kb++) {
 				const int s = kb % NA, use = kb / NA;
 				if (use > 0 && !tc_wait(&afree_bar[s], (use - 1) & 1, a.err)) { s_fail = 1; break; }

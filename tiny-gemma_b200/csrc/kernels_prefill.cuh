@@ -9,6 +9,8 @@ namespace tg {
 // ops::embedding_prefill, reference ops.hpp:529-571
 __global__ void embed_prefill_kernel(const int8_t *wte, const float *scales, const int *ids, float *h, int S, int D,
                                      int V, float sqrtD, int *err_flag) {
+	pdl_trigger();
+	pdl_wait();
 	int s = blockIdx.x;
 	int tok = ids[s];
 	if (tok < 0 || tok >= V) {
@@ -24,6 +26,8 @@ __global__ void embed_prefill_kernel(const int8_t *wte, const float *scales, con
 // `out` may alias `res` or `in`.
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *out, const float *in, const float *w, const float *res,
                                                             int dim) {
+	pdl_trigger();
+	pdl_wait();
 	__shared__ float bred[8];
 	const size_t off = size_t(blockIdx.x) * dim;
 	float ss = 0.0f;
@@ -171,6 +175,8 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
                                                                     const float *sinT, float *kcache, float *vcache,
                                                                     int S, int slots, const float *part, int nsplit,
                                                                     const float *sq, const float *sk, const float *sv) {
+	pdl_trigger();
+	pdl_wait();
 	const int s = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const float *cosr = cosT + size_t(s) * 256, *sinr = sinT + size_t(s) * 256;
 	const int start = (S >= slots) ? (S - slots) : 0;
@@ -396,6 +402,8 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float
 // the reference (ops.hpp:465-480) up to fp32 rounding.
 __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, const float *q, const float *k, const float *v, int S,
                                                                int is_local, int window) {
+	pdl_trigger();
+	pdl_wait();
 	// two K tiles and two V tiles (64 KiB): the next tile is copied asynchronously while this one is consumed
 	extern __shared__ __align__(16) float ap_smem[];
 	float (*ksb)[AP_TILE][256] = reinterpret_cast<float (*)[AP_TILE][256]>(ap_smem);
@@ -558,6 +566,8 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 // and one exp, instead of five rounds and four sequential (max, exp, exp) updates.
 __global__ void __launch_bounds__(256) attn_prefill_small_kernel(float *o, const float *q, const float *k, const float *v,
                                                                  int S, int is_local, int window) {
+	pdl_trigger();
+	pdl_wait();
 	__shared__ __align__(16) float ks[AP_TILE][256];
 	__shared__ __align__(16) float vs[AP_TILE][256];
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

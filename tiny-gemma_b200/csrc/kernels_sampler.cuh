@@ -34,6 +34,8 @@ __device__ __forceinline__ void emit_token(const SampleArgs &a, int b, int tok) 
 // ops::argmax_logits, reference ops.hpp:744-760: ascending scan with a strict
 // '>' — the lowest index wins ties, NaN never wins, -1 if nothing exceeds -inf.
 __global__ void __launch_bounds__(SM_THREADS) argmax_kernel(SampleArgs a) {
+	pdl_trigger();
+	pdl_wait();
 	__shared__ float sv[SM_NWARPS];
 	__shared__ int si[SM_NWARPS];
 	const int b = blockIdx.x, tid = threadIdx.x;

@@ -71,6 +71,16 @@ __device__ __forceinline__ float inv_rms(float sumsq, int dim) {
 }
 
 // lut::GeLUTable::lookup, reference ops.hpp:41-51
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may be
+// scheduled while its predecessor in the stream still runs; it must call pdl_wait() before it touches
+// anything a predecessor reads or writes (the call returns when every earlier grid has completed and its
+// memory operations are visible). pdl_trigger() tells the scheduler that the NEXT kernel may be scheduled
+// once every CTA of this grid has started. Without the attribute both are no-ops. What overlaps is launch
+// latency, CTA scheduling and each kernel's own set-up (barrier initialisation, TMEM allocation, and in the
+// GEMM the first weight tiles, which no earlier kernel produces).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 struct GeluLut {
 	const float *table;
 	float mn;

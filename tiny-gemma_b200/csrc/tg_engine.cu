@@ -67,6 +67,29 @@ int g_num_sms = 148;
 
 // cudaFuncSetAttribute is per device: "configured once" flags are kept per device index
 constexpr int TG_MAX_DEVICES = 64;
+// Launch with the programmatic-serialization attribute (see pdl_wait in tg_common.cuh): only for kernels that
+// call pdl_wait() before their first global access. TG_PDL=0 launches them as ordinary stream-ordered kernels.
+// The batched decode step switches it off for its own launches (g_pdl_scope_off): replayed from a CUDA graph the
+// step gains nothing from it (measured 3.72 ms with ordinary edges, 3.78 ms with programmatic ones at 256
+// sequences), while the eagerly launched prefill does (178 tokens: 4.00 -> 3.80 ms).
+thread_local bool g_pdl_scope_off = false;
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+	static const int use_env = env_int("TG_PDL", 1);
+	const int use = use_env && !g_pdl_scope_off;
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = grid;
+	cfg.blockDim = block;
+	cfg.dynamicSmemBytes = smem;
+	cfg.stream = st;
+	cudaLaunchAttribute at[1];
+	at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	at[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = at;
+	cfg.numAttrs = use ? 1 : 0;
+	cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);  // errors surface in check_launch (cudaGetLastError)
+}
+
 inline int current_device_slot() {
 	int d = 0;
 	cudaGetDevice(&d);
@@ -1334,7 +1357,7 @@ int enqueue_sampler(tg_state *s, float minp, float temp, bool log_tokens) {
 		count_launch();
 		return check_launch("minp");
 	}
-	argmax_kernel<<<s->B, SM_THREADS, 0, s->stream>>>(a);
+	launch_k(argmax_kernel, dim3(s->B), dim3(SM_THREADS), 0, s->stream, a);
 	count_launch();
 	return check_launch("argmax");
 }
@@ -1415,7 +1438,7 @@ int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStre
 	const int m_tiles = (M + TC_BM - 1) / TC_BM;
 	const size_t chunks = size_t(m_tiles) * TC_BM * (K / 8);
 	const unsigned grid = unsigned(std::min<size_t>((chunks + 255) / 256, size_t(g_num_sms) * 16));
-	split_pack_kernel<<<grid, 256, 0, st>>>(A, sc.apack, M, K, m_tiles);
+	launch_k(split_pack_kernel, dim3(grid), dim3(256), 0, st, A, sc.apack, M, K, m_tiles);
 	count_launch();
 	return check_launch("split_pack");
 }
@@ -1494,9 +1517,9 @@ int launch_gemm_tc_group(int ng, float *const *Cs, const QW *const *ws, const in
 		*raw_nsplit = a.nsplit;
 	}
 	if (wide)
-		qgemm_tc_kernel<1, 256><<<grid, TC_THREADS, TcShape<1, 256>::SMEM, st>>>(wmap[0], wmap[1], wmap[2], a);
+		launch_k(qgemm_tc_kernel<1, 256>, grid, dim3(TC_THREADS), TcShape<1, 256>::SMEM, st, wmap[0], wmap[1], wmap[2], a);
 	else
-		qgemm_tc_kernel<2, 128><<<grid, TC_THREADS, TcShape<2, 128>::SMEM, st>>>(wmap[0], wmap[1], wmap[2], a);
+		launch_k(qgemm_tc_kernel<2, 128>, grid, dim3(TC_THREADS), TcShape<2, 128>::SMEM, st, wmap[0], wmap[1], wmap[2], a);
 	count_launch();
 	TG_TRY(check_launch("qgemm_tc"));
 	if (a.nsplit > 1 && !fused && !raw_nsplit) {
@@ -1537,6 +1560,11 @@ int batched_setup(tg_state *s) {
 }
 
 int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
+	struct PdlOff {
+		bool was = g_pdl_scope_off;
+		PdlOff() { g_pdl_scope_off = true; }
+		~PdlOff() { g_pdl_scope_off = was; }
+	} pdl_off;
 	tg_model *m = s->m;
 	const tg_config &c = m->cfg;
 	const int B = s->B, D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
@@ -1555,12 +1583,12 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 	ea.D = D;
 	ea.V = V;
 	ea.sqrtD = float(std::sqrt(double(D)));
-	embed_decode_kernel<<<B, 256, 0, st>>>(ea);
+	launch_k(embed_decode_kernel, dim3(B), dim3(256), 0, st, ea);
 	count_launch();
 	const int m_tiles = (B + TC_BM - 1) / TC_BM;
 	// t: finished matrix (nsplit 0) or the raw partial sums of the GEMM before (nsplit >= 1, column scales tscale)
 	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre, int nsplit, const float *tscale) {
-		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles, nsplit, D, tscale);
+		launch_k(resnorm_pack_kernel, dim3(m_tiles * TC_BM), dim3(256), 0, st, h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles, nsplit, D, tscale);
 		count_launch();
 	};
 	auto gemm_raw = [&](int ng, const QW *const *ws, int *ns) -> int {
@@ -1598,7 +1626,7 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 			a.tickets = s->attn_tickets;
 			a.out = s->attn_out;
 			a.err_flag = s->err_flag;
-			attn_decode_kernel<<<dim3(a.nsplit, B), AT_THREADS, 0, st>>>(a);
+			launch_k(attn_decode_kernel, dim3(a.nsplit, B), dim3(AT_THREADS), 0, st, a);
 			count_launch();
 			TG_TRY(check_launch("attn_decode"));
 		}
@@ -1613,7 +1641,7 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 			const QW *ws[2] = {&w.U, &w.G};
 			TG_TRY(gemm_raw(2, ws, &ns));
 		}
-		geglu_pack_kernel<<<unsigned((size_t(m_tiles) * TC_BM * (I / 8) + 255) / 256), 256, 0, st>>>(nullptr, s->btc.partial, s->btc.apack, B, I, m_tiles, lut, ns, w.U.s, w.G.s);
+		launch_k(geglu_pack_kernel, dim3(unsigned((size_t(m_tiles) * TC_BM * (I / 8) + 255) / 256)), dim3(256), 0, st, (const float *)nullptr, (const float *)s->btc.partial, s->btc.apack, B, I, m_tiles, lut, ns, w.U.s, w.G.s);
 		count_launch();
 		{
 			const QW *ws[1] = {&w.Dn};
@@ -1622,7 +1650,7 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 		resnorm_pack(s->btc.partial, w.mlp_post, l + 1 < c.n_layers ? m->layers[l + 1].attn_pre : nullptr, ns, w.Dn.s);
 		TG_TRY(check_launch("batched layer"));
 	}
-	rmsnorm_rows_kernel<<<B, 256, 0, st>>>(s->xnorm, h, m->final_norm, nullptr, D);
+	launch_k(rmsnorm_rows_kernel, dim3(B), dim3(256), 0, st, s->xnorm, (const float *)h, m->final_norm, (const float *)nullptr, D);
 	count_launch();
 	if (with_lm_head) {
 		TG_TRY(pack_activations(s->xnorm, B, D, s->btc, st));
@@ -1696,15 +1724,15 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		return launch_gemm_tc(C, w, S, tc, st);
 	};
 
-	embed_prefill_kernel<<<S, 256, 0, st>>>(m->wte, m->wte_s, s->pf_ids + size_t(b) * S, h, S, D, V,
-	                                        float(std::sqrt(double(D))), s->err_flag);
+	launch_k(embed_prefill_kernel, dim3(S), dim3(256), 0, st, m->wte, m->wte_s, (const int *)(s->pf_ids + size_t(b) * S), h, S, D, V,
+	         float(std::sqrt(double(D))), s->err_flag);
 	count_launch();
 	TG_TRY(check_launch("embed_prefill"));
 	const int m_tiles = (S + TC_BM - 1) / TC_BM;
 	// Tensor-core path: the norms are fused with the operand packing of the GEMM that follows them
 	// (resnorm_pack_kernel, geglu_pack_kernel), so a layer is 7 GEMMs (+ their split-K reduces) and 6 other launches.
 	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre, int nsplit, const float *tscale) {
-		resnorm_pack_kernel<<<m_tiles * TC_BM, 256, 0, st>>>(h, t, w_post, w_pre, tc.apack, S, D, m_tiles, nsplit, D, tscale);
+		launch_k(resnorm_pack_kernel, dim3(m_tiles * TC_BM), dim3(256), 0, st, h, t, w_post, w_pre, tc.apack, S, D, m_tiles, nsplit, D, tscale);
 		count_launch();
 	};
 	auto gemm_raw = [&](int ng, const QW *const *ws, int *ns) -> int {
@@ -1729,14 +1757,12 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 			TG_TRY(gemm(k, xn, w.K, false));
 			TG_TRY(gemm(v, xn, w.V, false));
 		}
-		qk_norm_rope_prefill_kernel<<<S, 192, 0, st>>>(q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
-		                                               m->rope[w.is_local ? 1 : 0][1],
-		                                               s->kcache[l] + size_t(b) * slots * AT_HD,
-		                                               s->vcache[l] + size_t(b) * slots * AT_HD, S, slots, tc.partial, ns_qkv,
-		                                               w.Q.s, w.K.s, w.V.s);
+		launch_k(qk_norm_rope_prefill_kernel, dim3(S), dim3(192), 0, st, q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
+		         m->rope[w.is_local ? 1 : 0][1], s->kcache[l] + size_t(b) * slots * AT_HD, s->vcache[l] + size_t(b) * slots * AT_HD, S,
+		         slots, tc.partial, ns_qkv, w.Q.s, w.K.s, w.V.s);
 		count_launch();
 		if (S <= env_int("TG_ATTN_SMALL_MAX", 384))  // short prompts: one (query, head) per warp, S/2 CTAs
-			attn_prefill_small_kernel<<<(S + 1) / 2, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+			launch_k(attn_prefill_small_kernel, dim3((S + 1) / 2), dim3(256), 0, st, ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
 				static bool configured[TG_MAX_DEVICES] = {false};
@@ -1745,7 +1771,7 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 					TG_CUDA(cudaFuncSetAttribute(attn_prefill_blk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_BLK_SMEM));
 					configured[dev] = true;
 				}
-				attn_prefill_blk_kernel<<<(S + 7) / 8, 256, AP_BLK_SMEM, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+				launch_k(attn_prefill_blk_kernel, dim3((S + 7) / 8), dim3(256), AP_BLK_SMEM, st, ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 			} else
 				attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
@@ -1763,7 +1789,8 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 				const QW *ws[2] = {&w.U, &w.G};
 				TG_TRY(gemm_raw(2, ws, &ns));
 			}
-			geglu_pack_kernel<<<unsigned(std::min<size_t>((size_t(m_tiles) * TC_BM * (I / 8) + 255) / 256, 65535 * 16)), 256, 0, st>>>(nullptr, tc.partial, tc.apack, S, I, m_tiles, lut, ns, w.U.s, w.G.s);
+			launch_k(geglu_pack_kernel, dim3(unsigned(std::min<size_t>((size_t(m_tiles) * TC_BM * (I / 8) + 255) / 256, 65535 * 16))), dim3(256), 0, st,
+			         (const float *)nullptr, (const float *)tc.partial, tc.apack, S, I, m_tiles, lut, ns, w.U.s, w.G.s);
 			count_launch();
 			{
 				const QW *ws[1] = {&w.Dn};
