@@ -129,7 +129,6 @@ struct PsArgs {
 	int poll_ns;            // sleep between two rounds of a hand-off poll
 	int sched;              // 0: up/gate and down units of layer l+1 requested in phase E of layer l; 1: units of layer l requested after the Q|K|V product of layer l
 	long long *gt;  // optional: [CTA][12] global-timer marks of one layer (DBG instantiation)
-	int dbg_flags;  // DBG instantiation: bit 0 = run the up/gate product twice (stamps both: cold vs warm code)
 	int *beacon;    // optional (mapped host memory): [CTA][16] progress marks of every warp, for diagnosing a stall
 	int e_rows;     // 1: the down projection runs by K-parts per warp (ps_product_rows), e_wq quads per warp
 	int e_wq;
@@ -1622,35 +1621,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				PS_BEACON(0x41);
 				if (actD && !rdyD) ps_wait_bulk(pw, (l << 4) | 4, &bar_D, pD);
 				PS_STAMP();
-				if constexpr (DBG) {
-					if ((a.dbg_flags & 2) && a.dbg && cta == a.dbg_cta && !more && l == L / 2) {
-						// calibration: 2048 dependent fmas (4 clocks each on this part) and 256 dependent shared loads, every warp
-						float x = s_xscale;
-						const long long c0 = clock64();
-#pragma unroll 1
-						for (int i = 0; i < 256; i++) {
-							x = fmaf(x, 1.0000001f, 1e-9f); x = fmaf(x, 1.0000001f, 1e-9f); x = fmaf(x, 1.0000001f, 1e-9f); x = fmaf(x, 1.0000001f, 1e-9f);
-							x = fmaf(x, 1.0000001f, 1e-9f); x = fmaf(x, 1.0000001f, 1e-9f); x = fmaf(x, 1.0000001f, 1e-9f); x = fmaf(x, 1.0000001f, 1e-9f);
-						}
-						const long long c1 = clock64();
-						uint32_t ix = lane & 7;
-#pragma unroll 1
-						for (int i = 0; i < 256; i++) ix = ps_lds32(cnt_s + 4u * (ix & 7)) & 7;
-						const long long c2 = clock64();
-						if (lane == 0) {
-							a.dbg[3900 + warp * 2] = c1 - c0 + (x == 123.f);
-							a.dbg[3900 + warp * 2 + 1] = c2 - c1 + ix;
-						}
-					}
-					if ((a.dbg_flags & 1) && hasD) {
-						if (actD) ps_wait_bulk(pw, (l << 4) | 4, &bar_D, pD);
-						PS_STAMP();
-						const PsOut o = ps_product(ps_smem(R_D), a.Dp.ngroups, a.Dp.nq, a.Dp.kp, a.Dp.wq, true, xd_s, D / 4, part_s, cnt_s,
-						                           (a.dbg && cta == a.dbg_cta && !more && l == L / 2) ? a.dbg + 3800 : nullptr);
-						if (o.r0 == 1.2345e-30f) ps_st(llb + a.ll_act + colD, 0.0f);
-						PS_STAMP();
-					}
-				}
 				if (hasD) {
 					const PsOut o = ps_product(ps_smem(R_D), a.Dp.ngroups, a.Dp.nq, a.Dp.kp, a.Dp.wq, true, xd_s, D / 4, part_s, cnt_s);
 					if ((o.flags & 1) && lane < 4) {

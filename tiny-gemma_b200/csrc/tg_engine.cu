@@ -1237,7 +1237,6 @@ int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp
 	a.e_rows = (env_int("TG_PS_E_ROWS", 0) && a.E.ngroups <= 4 && a.e_wq <= 96) ? 1 : 0;
 	a.poll_ns = std::max(0, env_int("TG_PS_POLL_NS", 20));
 	a.sched = env_int("TG_PS_SCHED", 0);
-	a.dbg_flags = env_int("TG_PS_DBG_FLAGS", 0);
 	a.gt = (s->mg_dbg && env_int("TG_PS_GT", 0)) ? s->mg_dbg + 2048 : nullptr;  // (the stamp recorder uses < 600 entries)
 	// every word of the hand-off arena starts as "empty" (all ones)
 	TG_CUDA(cudaMemsetAsync(s->ps_ll, 0xFF, s->ps_ll_bytes, s->stream));
