@@ -1061,13 +1061,15 @@ __device__ __noinline__ void ps_attention(const PsW w, int where, float *kcache,
 // lm_head of one token: logits[v] = lm_scale[v] * sum_k x[k] W[k,v]; this CTA takes column tiles cta, cta + G, ...;
 // a tile arrives as lm_nchunk ring stages in `ring`; warp w owns column groups 2w and 2w + 1 of every tile over
 // all of its rows. Returns this lane's best (temperature-scaled) logit and the ring's barrier parities.
+// pre: ring stages the caller has already requested (those that lie inside the up/gate region, which is
+// idle from the last layer's up/gate product on).
 struct PsLmOut {
 	float best;
 	int best_i;
 	uint32_t plm, pemp;
 };
 __device__ __noinline__ PsLmOut ps_lm_head(const PsArgs &a, const PsW pw, uint8_t *ring, const uint32_t *xd, float xs, uint64_t *bar_lm,
-                                           uint64_t *emp_lm, uint32_t plm, uint32_t pemp, uint64_t pol, uint64_t keep) {
+                                           uint64_t *emp_lm, uint32_t plm, uint32_t pemp, uint64_t pol, uint64_t keep, int pre) {
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int cta = blockIdx.x, G = gridDim.x, D = a.D, L = a.L;
 	__builtin_assume(__isShared(ring));
@@ -1087,7 +1089,7 @@ int best_i = -1;
 	};
 	if (tid == PS_THREADS - 32) {
 #pragma unroll 1
-		for (int s = 0; s < nst && s < total; s++) issue_stage(s, s);
+		for (int s = pre; s < nst && s < total; s++) issue_stage(s, s);  // (the first `pre` stages were requested during the last layer)
 	}
 	PsAcc a0, a1;
 	float sc = 0.0f;
@@ -1472,6 +1474,8 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 	const int colD = uD * a.Dp.ngroups * 4 + (warp / a.Dp.kp) * 4 + (lane & 3);
 	const int colE = tileE * a.E.ngroups * 4 + (warp / a.E.kp) * 4 + (lane & 3);
 
+	// ring stages of the lm_head that fit the up/gate region and belong to this CTA's first tile (chunks 0 .. lm_pre - 1)
+	const int lm_pre = (cta < a.lm_ntiles && a.sched == 0) ? min(min(a.lm_stages, a.lm_nchunk), a.Dp.bytes / a.lm_stage_bytes) : 0;
 #pragma unroll 1
 	for (int step = 0; step < a.n_steps; step++) {
 		const bool more = (step + 1 < a.n_steps);
@@ -1663,6 +1667,14 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 				}
 				// the up/gate region is free: request the next layer's unit now that the hand-off loads are done
 				if (a.sched == 0 && tid == 32 && hasD && l + 1 < L) ps_issue(R_D, srcD + size_t(l + 1) * a.tl_layer, a.Dp.bytes, &bar_D, pol, &s_abort);
+				if (tid == 32 && l + 1 == L) {
+					// last layer: the up/gate region is idle until the lm_head, whose ring starts there. Its first stages
+					// are requested now, so that they land under the down projection and the final norm.
+#pragma unroll 1
+					for (int sg = 0; sg < lm_pre; sg++)
+						ps_issue(R_D + size_t(sg) * a.lm_stage_bytes, a.lm_tiled + (size_t(cta) * a.lm_nchunk + sg) * a.lm_stage_bytes, uint32_t(a.lm_stage_bytes),
+						         &bar_lm[sg], pol, &s_abort);
+				}
 				PS_STAMP();
 				PS_GT(8);
 				PS_BEACON(0x51);
@@ -1699,7 +1711,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 		}
 		PS_STAMP();
 		PS_BEACON(0x61);
-		const PsLmOut lo = ps_lm_head(a, pw, R_D, xd, s_xscale, bar_lm, emp_lm, plm, pemp, pol, keep);
+		const PsLmOut lo = ps_lm_head(a, pw, R_D, xd, s_xscale, bar_lm, emp_lm, plm, pemp, pol, keep, lm_pre);
 		plm = lo.plm;
 		pemp = lo.pemp;
 		__syncthreads();
