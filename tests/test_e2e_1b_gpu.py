@@ -260,3 +260,40 @@ def test_append_equals_decode_steps_1b(capi, synth, weights_1b):
     a.close()
     b.close()
     m.close()
+
+
+def test_chained_launches_equal_one_launch_1b(capi, synth, weights_1b):
+    """The persistent decode kernel leaves its hand-off arena and its grid-barrier counter ready for the
+    next launch instead of having the host reset them. 26 layers rotate over three arena copies, so launches
+    of 1, 2 and 3 tokens end on every phase of the rotation; greedy and min-p launches (1 and 3 grid barriers
+    per token) are mixed. The tokens must equal those of single launches over the same steps."""
+    m = capi.Model("1B").load_file(weights_1b)
+    m.build_tables(1 << 20)
+    ids = synth.random_prompt(40, 17)
+    rf = np.random.default_rng(3).random(24, dtype=np.float32)
+
+    def start():
+        st = m.state(1, 128)
+        st.prefill(ids, want_logits=False)
+        return st, st.sample_argmax()
+
+    st, first = start()
+    want_g = st.generate(first, 12).ravel()
+    want_s = st.generate(want_g[-1:], 12, MINP, TEMP, rf[:12]).ravel()
+    st.close()
+    st, first = start()
+    got, tok = [], first
+    for n in (1, 2, 3, 1, 1, 2, 2):
+        out = st.generate(tok, n).ravel()
+        got += [int(t) for t in out]
+        tok = out[-1:]
+    assert got == [int(t) for t in want_g]
+    got, used = [], 0
+    for n in (1, 1, 3, 2, 1, 1, 3):
+        out = st.generate(tok, n, MINP, TEMP, rf[used:used + n]).ravel()
+        got += [int(t) for t in out]
+        tok = out[-1:]
+        used += n
+    assert got == [int(t) for t in want_s]
+    st.close()
+    m.close()

@@ -82,6 +82,13 @@ def test_matvec_is_linear_and_deterministic(capi):
     assert rel_l2(capi.qmatvec(x[0] + x[1], w, s), y0 + y1) <= 5e-6
     assert np.array_equal(capi.qmatvec(np.zeros(K, np.float32), w, s), np.zeros(N, np.float32))
     assert np.array_equal(capi.qmatvec(2.0 * x[0], w, s), 2.0 * y0)  # power-of-two scaling is exact
+    # the same properties on the layer shapes, whose K-splits meet in a thread-block cluster's shared memory
+    for K, N in ((6912, 1152), (1152, 6912), (640, 2048)):
+        x, w, s = cases.linear_case(K, N, 2, seed=3)
+        y0 = capi.qmatvec(x[0], w, s)
+        assert np.array_equal(y0, capi.qmatvec(x[0], w, s))
+        assert np.array_equal(capi.qmatvec(np.zeros(K, np.float32), w, s), np.zeros(N, np.float32))
+        assert np.array_equal(capi.qmatvec(2.0 * x[0], w, s), 2.0 * y0)
 
 
 def test_unsupported_shape_is_an_error(capi):
@@ -420,8 +427,12 @@ def test_bounded_wait_returns_an_error_and_the_context_survives(capi, synth, wei
     with pytest.raises(capi.TgError) as e:
         st.generate(first, 2)
     assert e.value.code == capi.TG_ECUDA and "wait ran out" in str(e.value)
-    st.close()
+    # the same state is usable again: the launch after an error resets the hand-off arena and the barrier count
     monkeypatch.delenv("TG_PS_WITHHOLD_CTA")
+    st.reset()
+    st.prefill(ids, want_logits=False)
+    assert np.array_equal(st.generate(st.sample_argmax(), 6), want)
+    st.close()
     st = m.state(1, 128)
     st.prefill(ids, want_logits=False)
     assert np.array_equal(st.generate(st.sample_argmax(), 6), want)

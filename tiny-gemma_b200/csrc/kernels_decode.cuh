@@ -2,6 +2,8 @@
 // weight-only matvec with fused norm prologues / GeGLU epilogue, and split-KV
 // attention over the cache. All are HBM-bandwidth bound; none uses tensor cores.
 #pragma once
+#include <cooperative_groups.h>
+
 #include "tg_common.cuh"
 
 namespace tg {
@@ -365,6 +367,92 @@ __global__ void __launch_bounds__(MV_THREADS) qmatvec_kernel(MvArgs a) {
 			if (tid == 0) a.tickets[tile] = 0u;
 		}
 		__syncthreads();
+	}
+}
+
+// =========================================================== single-wave matvec (one sequence)
+// y[n] = scale[n] * sum_k x[k] W[k,n] for matrices small enough that one wave of CTAs holds all of W in
+// flight at once (the layer matrices: 0.6 - 8 MB). Such a launch is bound by its chain of dependent memory
+// round trips, so there is exactly one: every CTA requests its whole K-slice of a column tile (and its
+// x values) before it waits for anything. K is split over the CTAs of a thread-block cluster
+// (gridDim.y = cluster size <= 8) whose partial sums meet in the shared memory of the cluster's first CTA
+// (distributed shared memory), added in rank order: no partial-sum buffer, no tickets, no second launch,
+// the same bits on every run.
+// A column tile is 16 * TPR columns (TPR = 1, 2, 4 threads per row, 16 int8 each); thread t takes columns
+// 16 * (t % TPR) .. of rows t / TPR, t / TPR + 512 / TPR, ...; at most MVC_MAX_IT rows per thread.
+constexpr int MVC_THREADS = 512;
+constexpr int MVC_NWARPS = MVC_THREADS / 32;
+constexpr int MVC_MAX_IT = 10;
+constexpr int MVC_MAX_CLUSTER = 8;
+
+template <int TPR>
+__global__ void __launch_bounds__(MVC_THREADS, 1) qmatvec_cluster_kernel(float *y, const float *x, const int8_t *w, const float *scales,
+                                                                         int K, int N, int kc) {
+	namespace cg = cooperative_groups;
+	constexpr int TN = 16 * TPR, ROWS = MVC_THREADS / TPR;
+	cg::cluster_group cluster = cg::this_cluster();
+	__shared__ __align__(16) float red[MVC_NWARPS][TN];
+	__shared__ float part[MVC_MAX_CLUSTER][TN];  // (used in the cluster's first CTA)
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int n0 = blockIdx.x * TN;
+	const int rank = int(cluster.block_rank()), nranks = int(cluster.num_blocks());
+	const int k0 = rank * kc;
+	const int r0 = tid / TPR, cgp = tid % TPR;
+	const int8_t *p = w + size_t(k0 + r0) * N + n0 + cgp * 16;
+	int4 v[MVC_MAX_IT];
+	float xv[MVC_MAX_IT];
+#pragma unroll
+	for (int it = 0; it < MVC_MAX_IT; it++) {
+		const int r = r0 + it * ROWS;
+		v[it] = make_int4(0, 0, 0, 0);
+		xv[it] = 0.0f;
+		if (r < kc) {
+			v[it] = ld_stream_int4(p + size_t(it) * ROWS * N);
+			xv[it] = __ldg(x + k0 + r);
+		}
+	}
+	float sc = 0.0f;
+	if (rank == 0 && tid < TN) sc = __ldg(scales + n0 + tid);
+	float acc[16];
+#pragma unroll
+	for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+#pragma unroll
+	for (int it = 0; it < MVC_MAX_IT; it++) {
+		const uint32_t words[4] = {uint32_t(v[it].x), uint32_t(v[it].y), uint32_t(v[it].z), uint32_t(v[it].w)};
+#pragma unroll
+		for (int j = 0; j < 4; j++) {
+			float f[4];
+			i8x4_to_f32(words[j], f);
+#pragma unroll
+			for (int i = 0; i < 4; i++) acc[4 * j + i] = fmaf(xv[it], f[i], acc[4 * j + i]);
+		}
+	}
+	// over the rows of a warp (lanes with the same column group), then over the warps
+#pragma unroll
+	for (int i = 0; i < 16; i++) {
+		float s = acc[i];
+#pragma unroll
+		for (int o = TPR; o < 32; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+		acc[i] = s;
+	}
+	if (lane < TPR) {
+#pragma unroll
+		for (int i = 0; i < 16; i += 4)
+			*reinterpret_cast<float4 *>(&red[warp][lane * 16 + i]) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+	}
+	__syncthreads();
+	if (tid < TN) {
+		float s = 0.0f;
+#pragma unroll
+		for (int wi = 0; wi < MVC_NWARPS; wi++) s += red[wi][tid];
+		float *dst = cluster.map_shared_rank(&part[rank][tid], 0);  // this rank's row in the first CTA's array
+		*dst = s;
+	}
+	cluster.sync();  // (every thread of every CTA: the stores above are visible to the first CTA behind it)
+	if (rank == 0 && tid < TN) {
+		float s = 0.0f;
+		for (int r = 0; r < nranks; r++) s += part[r][tid];
+		y[n0 + tid] = s * sc;
 	}
 }
 

@@ -114,7 +114,8 @@ struct PsArgs {
 	float *samp_f;
 	int *samp_i;
 	float *xnorm_out;
-	unsigned *bar;
+	unsigned *bar;          // grid-barrier counter: bar_base arrivals so far (it is never reset between launches)
+	unsigned bar_base;
 	int *err;
 	int *tok, *next_pos, *ring_base, *tok_log, *log_count;
 	int log_cap, n_steps, sampler;
@@ -287,10 +288,11 @@ __device__ __noinline__ void ps_grid_sync(const PsW w, int where, unsigned *bar,
 	if (threadIdx.x == 0) {
 		__threadfence();
 		const unsigned old = atomicAdd(bar, 1u);
-		if (old + 1u < target && !*(volatile int *)w.s_abort) {  // the last arriver need not poll
+		// (the counter runs on from launch to launch and may wrap: compare differences, not values)
+		if (old + 1u != target && !*(volatile int *)w.s_abort) {  // the last arriver need not poll
 			const long long t0 = clock64();
 			int spins = 0;
-			while (ps_ld_acquire(bar) < target) {
+			while (int(ps_ld_acquire(bar) - target) < 0) {
 				if ((++spins & 15) == 0 && clock64() - t0 > w.limit) {
 					ps_give_up(w.s_abort, w.err, 4 | (where << 8));
 					break;
@@ -1176,7 +1178,7 @@ __device__ __noinline__ PsSampOut ps_sampler(const PsArgs &a, const PsW pw, floa
 const int wh = (L << 4) | 7;
 int next_tok = 0;
 if (a.sampler == 0) {
-	ps_grid_sync(pw, wh, a.bar, ++epoch * G);  // logits complete
+	ps_grid_sync(pw, wh, a.bar, a.bar_base + ++epoch * G);  // logits complete
 } else {
 	// CTA-local (max, argmax): value descending, index ascending; index -1 never beats a real one
 	auto better = [](float v1, int i1, float v2, int i2) {
@@ -1209,7 +1211,7 @@ if (a.sampler == 0) {
 		__stcg(a.samp_f + cta, best);
 		__stcg(a.samp_i + cta, best_i);
 	}
-	ps_grid_sync(pw, wh, a.bar, ++epoch * G);
+	ps_grid_sync(pw, wh, a.bar, a.bar_base + ++epoch * G);
 	// every CTA reduces the per-CTA results the same way (warp 0)
 	if (warp == 0) {
 		float gmax = -INFINITY;
@@ -1260,7 +1262,7 @@ if (a.sampler == 0) {
 		}
 		ds = block_sum<PS_NW>(ds, bred);
 		if (tid == 0) __stcg(a.samp_f + G + cta, ds);
-		ps_grid_sync(pw, wh, a.bar, ++epoch * G);
+		ps_grid_sync(pw, wh, a.bar, a.bar_base + ++epoch * G);
 		if (cta == 0) {
 			// denominator: per-CTA sums added in a fixed tree by warp 0
 			if (warp == 0) {
@@ -1309,7 +1311,7 @@ if (a.sampler == 0) {
 				*a.randf_count = rc + 1;
 			}
 		}
-		ps_grid_sync(pw, wh, a.bar, ++epoch * G);
+		ps_grid_sync(pw, wh, a.bar, a.bar_base + ++epoch * G);
 		next_tok = __ldcg(a.samp_i + G);
 	}
 	if (cta == 0 && tid == 0) {
@@ -1743,6 +1745,16 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_persist_kernel(const __g
 		__syncthreads();
 	}
 	if (cta == 0 && tid == 0 && a.log_count) *a.log_count = n_logged;
+	// Leave the hand-off arena as the next launch expects it: copy 0 empty (copies 1 and 2 are wiped during
+	// its layers 0 and 1, like every copy a layer before its use). Every CTA is past the last token's grid
+	// barriers, which all CTAs reach only after their last read of the arena.
+	if (!*(volatile int *)&s_abort) {
+		float4 *c0 = reinterpret_cast<float4 *>(a.ll);
+		const int n4 = a.ll_stride / 4, per = (n4 + G - 1) / G;
+		const float e = __uint_as_float(PS_EMPTY);
+#pragma unroll 1
+		for (int i = cta * per + tid; i < min(n4, (cta + 1) * per); i += PS_THREADS) __stcg(c0 + i, make_float4(e, e, e, e));
+	}
 #undef h
 #undef xd
 #undef att

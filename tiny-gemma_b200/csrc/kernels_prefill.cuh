@@ -558,21 +558,26 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
 	}
 }
 
-// Short prompts: with one query per warp the kernels above run on only S/8 CTAs. Here a warp owns one
-// (query, head), a CTA two queries (S/2 CTAs), and four keys are taken per step as in
-// attn_prefill_blk_kernel: the four partial scores of a lane are reduce-scattered over the warp, the
-// running max advances once per block, every lane evaluates one probability, and the four
-// probabilities are broadcast. The dependent chain per step is five shuffle rounds, two for the max
-// and one exp, instead of five rounds and four sequential (max, exp, exp) updates.
-__global__ void __launch_bounds__(256) attn_prefill_small_kernel(float *o, const float *q, const float *k, const float *v,
-                                                                 int S, int is_local, int window) {
+// Short prompts: with one query per warp the kernels above run on only S/8 CTAs, and a (query, head)'s walk
+// over its keys is a chain of dependent shuffles and exponentials that one warp cannot hide. Here a CTA of
+// 32 warps takes two queries; a warp owns one (query, head) and ONE of the four 4-key blocks of every
+// 16-key tile (the keys of a (query, head) are split four ways). Per block, as in attn_prefill_blk_kernel:
+// the four partial scores of a lane are reduce-scattered over the warp, the running max advances once,
+// every lane evaluates one probability, and the four probabilities are broadcast. The four partial
+// results (max, sum, output) of a (query, head) are merged through shared memory at the end.
+constexpr int APS_THREADS = 1024;
+__global__ void __launch_bounds__(APS_THREADS, 1) attn_prefill_small_kernel(float *o, const float *q, const float *k, const float *v,
+                                                                           int S, int is_local, int window) {
 	pdl_trigger();
 	pdl_wait();
-	__shared__ __align__(16) float ks[AP_TILE][256];
-	__shared__ __align__(16) float vs[AP_TILE][256];
+	__shared__ __align__(16) float kv[2][AP_TILE][256];  // K tile, V tile; afterwards the 32 warps' partial outputs
+	__shared__ float ml[32][2];
+	float (*ks)[256] = kv[0];
+	float (*vs)[256] = kv[1];
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int s0 = blockIdx.x * 2;
-	const int s = s0 + (warp >> 2), h = warp & 3;  // this warp's query (may be >= S: then it only helps loading) and head
+	const int part = warp & 3, h = (warp >> 2) & 3;  // this warp's 4-key block of every tile, and its head
+	const int s = s0 + (warp >> 4);                  // its query (may be >= S: then the warp only helps loading)
 	const int s_last = min(S - 1, s0 + 1);
 	int cta_j0 = 0;
 	if (is_local) cta_j0 = (s0 >= window) ? s0 - window : 0;
@@ -587,99 +592,118 @@ __global__ void __launch_bounds__(256) attn_prefill_small_kernel(float *o, const
 		q0.x *= 0.0625f; q0.y *= 0.0625f; q0.z *= 0.0625f; q0.w *= 0.0625f;  // exact: see attn_prefill_kernel
 		q1.x *= 0.0625f; q1.y *= 0.0625f; q1.z *= 0.0625f; q1.w *= 0.0625f;
 	}
-	float4 pk[4], pv[4];
+	// one float4 of K and one of V per thread and tile, fetched a tile ahead
+	const int fr = tid >> 6, fc4 = tid & 63;
+	float4 pk, pv;
 	auto fetch = [&](int jt) {
-#pragma unroll
-		for (int u = 0; u < 4; u++) {
-			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
-			const int j = jt + r;
-			if (j <= s_last) {
-				pk[u] = *reinterpret_cast<const float4 *>(k + size_t(j) * 256 + 4 * c4);
-				pv[u] = *reinterpret_cast<const float4 *>(v + size_t(j) * 256 + 4 * c4);
-			} else {
-				pk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-				pv[u] = pk[u];
-			}
+		const int j = jt + fr;
+		if (j <= s_last) {
+			pk = *reinterpret_cast<const float4 *>(k + size_t(j) * 256 + 4 * fc4);
+			pv = *reinterpret_cast<const float4 *>(v + size_t(j) * 256 + 4 * fc4);
+		} else {
+			pk = make_float4(0.f, 0.f, 0.f, 0.f);
+			pv = pk;
 		}
 	};
 	fetch(cta_j0);
 	for (int jt = cta_j0; jt <= s_last; jt += AP_TILE) {
 		__syncthreads();  // previous tile fully consumed
-#pragma unroll
-		for (int u = 0; u < 4; u++) {
-			const int slot = tid + 256 * u, r = slot >> 6, c4 = slot & 63;
-			*reinterpret_cast<float4 *>(&ks[r][4 * c4]) = pk[u];
-			*reinterpret_cast<float4 *>(&vs[r][4 * c4]) = pv[u];
-		}
+		*reinterpret_cast<float4 *>(&ks[fr][4 * fc4]) = pk;
+		*reinterpret_cast<float4 *>(&vs[fr][4 * fc4]) = pv;
 		__syncthreads();
 		if (jt + AP_TILE <= s_last) fetch(jt + AP_TILE);
-		if (s < S) {
-			const int ja = max(jt, my_j0), jb = min(jt + AP_TILE - 1, s);
-			for (int j4 = ja; j4 <= jb; j4 += 4) {
-				float sc[4];
+		// this warp's block: keys j4 .. j4 + 3, of which [lo, hi] are visible to its query
+		const int j4 = jt + 4 * part;
+		const int lo = max(j4, my_j0), hi = min(j4 + 3, s);
+		if (s < S && lo <= hi) {
+			float sc[4];
 #pragma unroll
-				for (int u = 0; u < 4; u++) {
-					const int r = min(j4 + u, jb) - jt;  // (keys past jb repeat the last one; their scores are not used)
-					const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r][4 * lane]);
-					const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r][128 + 4 * lane]);
-					float t = q0.x * k0v.x;
-					t = fmaf(q0.y, k0v.y, t);
-					t = fmaf(q0.z, k0v.z, t);
-					t = fmaf(q0.w, k0v.w, t);
-					t = fmaf(q1.x, k1v.x, t);
-					t = fmaf(q1.y, k1v.y, t);
-					t = fmaf(q1.z, k1v.z, t);
-					t = fmaf(q1.w, k1v.w, t);
-					sc[u] = t;
-				}
-				// reduce-scatter over the warp (6 shuffles instead of 20): afterwards lane L holds the finished
-				// score of key j4 + (L >> 3)
-				float z;
-				{
-					const bool up = lane & 16, up8 = lane & 8;
-					const float y0 = (up ? sc[2] : sc[0]) + __shfl_xor_sync(0xffffffffu, up ? sc[0] : sc[2], 16);
-					const float y1 = (up ? sc[3] : sc[1]) + __shfl_xor_sync(0xffffffffu, up ? sc[1] : sc[3], 16);
-					z = (up8 ? y1 : y0) + __shfl_xor_sync(0xffffffffu, up8 ? y0 : y1, 8);
-				}
-				z += __shfl_xor_sync(0xffffffffu, z, 4);
-				z += __shfl_xor_sync(0xffffffffu, z, 2);
-				z += __shfl_xor_sync(0xffffffffu, z, 1);
-				if (j4 + (lane >> 3) > jb) z = -INFINITY;  // past this query's last key
-				// one softmax step for the block of four keys: the running max advances per block
-				float mb = fmaxf(z, __shfl_xor_sync(0xffffffffu, z, 8));
-				mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
-				const float mn = fmaxf(m, mb);      // finite: key j4 is visible
-				const float corr = expf(m - mn);    // exp(-inf) = 0 on the first block
-				const float pr = expf(z - mn);      // this lane's key; 0 past the end
-				float p[4];
+			for (int u = 0; u < 4; u++) {
+				const int r = 4 * part + u;  // (rows outside [lo, hi] hold other keys or zeros; their scores are not used)
+				const float4 k0v = *reinterpret_cast<const float4 *>(&ks[r][4 * lane]);
+				const float4 k1v = *reinterpret_cast<const float4 *>(&ks[r][128 + 4 * lane]);
+				float t = q0.x * k0v.x;
+				t = fmaf(q0.y, k0v.y, t);
+				t = fmaf(q0.z, k0v.z, t);
+				t = fmaf(q0.w, k0v.w, t);
+				t = fmaf(q1.x, k1v.x, t);
+				t = fmaf(q1.y, k1v.y, t);
+				t = fmaf(q1.z, k1v.z, t);
+				t = fmaf(q1.w, k1v.w, t);
+				sc[u] = t;
+			}
+			// reduce-scatter over the warp (6 shuffles instead of 20): afterwards lane L holds the finished
+			// score of key j4 + (L >> 3)
+			float z;
+			{
+				const bool up = lane & 16, up8 = lane & 8;
+				const float y0 = (up ? sc[2] : sc[0]) + __shfl_xor_sync(0xffffffffu, up ? sc[0] : sc[2], 16);
+				const float y1 = (up ? sc[3] : sc[1]) + __shfl_xor_sync(0xffffffffu, up ? sc[1] : sc[3], 16);
+				z = (up8 ? y1 : y0) + __shfl_xor_sync(0xffffffffu, up8 ? y0 : y1, 8);
+			}
+			z += __shfl_xor_sync(0xffffffffu, z, 4);
+			z += __shfl_xor_sync(0xffffffffu, z, 2);
+			z += __shfl_xor_sync(0xffffffffu, z, 1);
+			const int jmine = j4 + (lane >> 3);
+			if (jmine < lo || jmine > hi) z = -INFINITY;  // outside this query's window or past its last key
+			// one softmax step for the block of four keys
+			float mb = fmaxf(z, __shfl_xor_sync(0xffffffffu, z, 8));
+			mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+			const float mn = fmaxf(m, mb);      // finite: the block has a visible key
+			const float corr = expf(m - mn);    // exp(-inf) = 0 on this warp's first block
+			const float pr = expf(z - mn);      // this lane's key; 0 when masked
+			float pb[4];
 #pragma unroll
-				for (int u = 0; u < 4; u++) p[u] = __shfl_sync(0xffffffffu, pr, 8 * u);
-				l = fmaf(l, corr, (p[0] + p[1]) + (p[2] + p[3]));
-				m = mn;
-				o0.x *= corr; o0.y *= corr; o0.z *= corr; o0.w *= corr;
-				o1.x *= corr; o1.y *= corr; o1.z *= corr; o1.w *= corr;
+			for (int u = 0; u < 4; u++) pb[u] = __shfl_sync(0xffffffffu, pr, 8 * u);
+			l = fmaf(l, corr, (pb[0] + pb[1]) + (pb[2] + pb[3]));
+			m = mn;
+			o0.x *= corr; o0.y *= corr; o0.z *= corr; o0.w *= corr;
+			o1.x *= corr; o1.y *= corr; o1.z *= corr; o1.w *= corr;
 #pragma unroll
-				for (int u = 0; u < 4; u++) {
-					const int r = min(j4 + u, jb) - jt;  // (past jb: p is 0)
-					const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r][4 * lane]);
-					const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r][128 + 4 * lane]);
-					o0.x = fmaf(p[u], v0v.x, o0.x);
-					o0.y = fmaf(p[u], v0v.y, o0.y);
-					o0.z = fmaf(p[u], v0v.z, o0.z);
-					o0.w = fmaf(p[u], v0v.w, o0.w);
-					o1.x = fmaf(p[u], v1v.x, o1.x);
-					o1.y = fmaf(p[u], v1v.y, o1.y);
-					o1.z = fmaf(p[u], v1v.z, o1.z);
-					o1.w = fmaf(p[u], v1v.w, o1.w);
-				}
+			for (int u = 0; u < 4; u++) {
+				const int r = 4 * part + u;  // (masked keys: p is 0, the row holds finite values)
+				const float4 v0v = *reinterpret_cast<const float4 *>(&vs[r][4 * lane]);
+				const float4 v1v = *reinterpret_cast<const float4 *>(&vs[r][128 + 4 * lane]);
+				o0.x = fmaf(pb[u], v0v.x, o0.x);
+				o0.y = fmaf(pb[u], v0v.y, o0.y);
+				o0.z = fmaf(pb[u], v0v.z, o0.z);
+				o0.w = fmaf(pb[u], v0v.w, o0.w);
+				o1.x = fmaf(pb[u], v1v.x, o1.x);
+				o1.y = fmaf(pb[u], v1v.y, o1.y);
+				o1.z = fmaf(pb[u], v1v.z, o1.z);
+				o1.w = fmaf(pb[u], v1v.w, o1.w);
 			}
 		}
 	}
-	if (s >= S) return;
-	const float inv = 1.0f / l;
-	float *orow = o + size_t(s) * 1024 + h * 256;
-	*reinterpret_cast<float4 *>(orow + 4 * lane) = make_float4(o0.x * inv, o0.y * inv, o0.z * inv, o0.w * inv);
-	*reinterpret_cast<float4 *>(orow + 128 + 4 * lane) = make_float4(o1.x * inv, o1.y * inv, o1.z * inv, o1.w * inv);
+	// merge the four partial results of every (query, head): partial outputs over the K / V tiles
+	__syncthreads();
+	float *po = &kv[0][0][0];  // [32 warps][256]
+	*reinterpret_cast<float4 *>(po + warp * 256 + 4 * lane) = o0;
+	*reinterpret_cast<float4 *>(po + warp * 256 + 128 + 4 * lane) = o1;
+	if (lane == 0) {
+		ml[warp][0] = m;
+		ml[warp][1] = l;
+	}
+	__syncthreads();
+	// 8 (query, head) pairs x 256 values over 1024 threads: two values per thread
+#pragma unroll
+	for (int rep = 0; rep < 2; rep++) {
+		const int idx = tid + rep * APS_THREADS;
+		const int pair = idx >> 8, d = idx & 255;  // pair = warp >> 2 of the four warps that share it
+		const int sq = s0 + (pair >> 2);
+		if (sq >= S) continue;
+		float mm = -INFINITY;
+#pragma unroll
+		for (int t = 0; t < 4; t++) mm = fmaxf(mm, ml[4 * pair + t][0]);  // finite: a query sees itself
+		float den = 0.0f, num = 0.0f;
+#pragma unroll
+		for (int t = 0; t < 4; t++) {
+			const float wgt = expf(ml[4 * pair + t][0] - mm);  // 0 for a part without visible keys (max -inf, sum 0)
+			den = fmaf(ml[4 * pair + t][1], wgt, den);
+			num = fmaf(po[(4 * pair + t) * 256 + d], wgt, num);
+		}
+		o[size_t(sq) * 1024 + (pair & 3) * 256 + d] = num / den;
+	}
 }
 
 }  // namespace tg

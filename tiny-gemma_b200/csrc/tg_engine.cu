@@ -287,6 +287,76 @@ int launch_mv(MvArgs a, int pro, int epi, cudaStream_t st) {
 }
 
 constexpr int MV_MAX_B = 4;
+constexpr int STEP_RANDF = 64;  // uniforms per sequence that fit the state's step block (more: a buffer of their own)
+
+// Single-wave matvec (qmatvec_cluster_kernel): a [K, N] matrix qualifies when a tile width 16 * tpr and a
+// K-split ks (= cluster size) exist with all CTAs resident at once — one per SM, and no more clusters than
+// the device can hold at a time (a cluster needs its SMs inside one GPC) — and at most MVC_MAX_IT rows per
+// thread. Among those the plan with the most CTAs wins, then the smaller cluster, then the wider tile.
+struct MvcPlan {
+	int tpr = 0, ks = 0;
+};
+template <int TPR>
+int mvc_launch_t(float *y, const float *x, const int8_t *w, const float *scales, int K, int N, int ks, cudaStream_t st, int *max_clusters) {
+	cudaLaunchConfig_t cfg{};
+	cfg.gridDim = dim3(N / (16 * TPR), ks);
+	cfg.blockDim = dim3(MVC_THREADS);
+	cfg.dynamicSmemBytes = 0;
+	cfg.stream = st;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeClusterDimension;
+	attr[0].val.clusterDim.x = 1;
+	attr[0].val.clusterDim.y = unsigned(ks);
+	attr[0].val.clusterDim.z = 1;
+	cfg.attrs = attr;
+	cfg.numAttrs = 1;
+	if (max_clusters) {  // query only
+		TG_CUDA(cudaOccupancyMaxActiveClusters(max_clusters, qmatvec_cluster_kernel<TPR>, &cfg));
+		return TG_OK;
+	}
+	TG_CUDA(cudaLaunchKernelEx(&cfg, qmatvec_cluster_kernel<TPR>, y, x, w, scales, K, N, K / ks));
+	count_launch();
+	return check_launch("qmatvec_cluster");
+}
+int mvc_launch(MvcPlan p, float *y, const float *x, const int8_t *w, const float *scales, int K, int N, cudaStream_t st, int *max_clusters = nullptr) {
+	if (p.tpr == 1) return mvc_launch_t<1>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+	if (p.tpr == 2) return mvc_launch_t<2>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+	return mvc_launch_t<4>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+}
+MvcPlan mvc_plan(int K, int N, int dev) {
+	// clusters of each (tile width, size) the device holds at once: asked once per device
+	static int max_active[TG_MAX_DEVICES][3][4];
+	static bool asked[TG_MAX_DEVICES] = {false};
+	const int slot = (dev >= 0 && dev < TG_MAX_DEVICES) ? dev : 0;
+	if (!asked[slot]) {
+		for (int t = 0; t < 3; t++)
+			for (int c = 0; c < 4; c++) {
+				int n = 0;
+				// (grid of one cluster: the answer does not depend on the grid)
+				if (mvc_launch(MvcPlan{1 << t, 1 << c}, nullptr, nullptr, nullptr, nullptr, 1 << c, 16 << t, nullptr, &n) != TG_OK) n = 0;
+				max_active[slot][t][c] = n;
+			}
+		asked[slot] = true;
+	}
+	const int want_tpr = env_int("TG_MVC_TPR", 0), want_ks = env_int("TG_MVC_KS", 0);  // (experiments: fix the plan)
+	MvcPlan best;
+	int best_ctas = 0;
+	for (int c = 0; c < 4; c++)          // smaller clusters first
+		for (int t = 2; t >= 0; t--) {   // wider tiles first
+			const int tpr = 1 << t, ks = 1 << c, tn = 16 * tpr;
+			if (want_tpr && tpr != want_tpr) continue;
+			if (want_ks && ks != want_ks) continue;
+			if (N % tn != 0 || K % ks != 0) continue;
+			const int tiles = N / tn, kc = K / ks;
+			if (kc > MVC_MAX_IT * (MVC_THREADS / tpr)) continue;
+			if (tiles * ks > g_num_sms || tiles > max_active[slot][t][c]) continue;
+			if (tiles * ks > best_ctas) {
+				best_ctas = tiles * ks;
+				best = MvcPlan{tpr, ks};
+			}
+		}
+	return best;
+}
 
 }  // namespace
 
@@ -341,6 +411,16 @@ struct tg_state {
 	int *log_count = nullptr;          // [B]
 	float *randf = nullptr;            // [randf_cap][B]
 	int randf_cap = 0;
+	int randf_valid = 0;               // uniforms per sequence uploaded so far (the largest upload)
+	// One allocation holds the small per-step words, so that a step's inputs go up in ONE copy and its
+	// results come back in ONE: [err_flag, 3 pad][tok B][randf_count B][log_count B][randf STEP_RANDF x B]
+	int *step_blk = nullptr;
+	bool randf_in_blk = false;         // randf still points into step_blk (it moves out when it has to grow)
+	float *randf_blk = nullptr;        // the block's own STEP_RANDF x B uniforms
+	bool lean_randf = false;           // the next persistent launch draws from randf_blk (one-token calls)
+	// persistent kernel: its hand-off arena and grid-barrier counter are left ready by the previous launch
+	bool ps_clean = false;             // false: wipe the arena and zero the counter before the next launch
+	unsigned ps_bar_base = 0;          // arrivals at the grid barrier so far
 	int *randf_count = nullptr;        // [B]
 	int *err_flag = nullptr;
 	int *host_pin = nullptr;           // pinned staging, 64 KiB
@@ -455,10 +535,15 @@ int state_alloc(tg_state *s) {
 	TG_TRY(alloci(&s->step_pos, B));
 	TG_TRY(alloci(&s->next_pos, B));
 	TG_TRY(alloci(&s->ring_base, B));
-	TG_TRY(alloci(&s->tok, B));
-	TG_TRY(alloci(&s->log_count, B));
-	TG_TRY(alloci(&s->randf_count, B));
-	TG_TRY(alloci(&s->err_flag, 1));
+	TG_TRY(alloci(&s->step_blk, 4 + size_t(3 + STEP_RANDF) * B));
+	s->err_flag = s->step_blk;
+	s->tok = s->step_blk + 4;
+	s->randf_count = s->tok + B;
+	s->log_count = s->randf_count + B;
+	s->randf_blk = reinterpret_cast<float *>(s->log_count + B);
+	s->randf = s->randf_blk;
+	s->randf_cap = STEP_RANDF;
+	s->randf_in_blk = true;
 	TG_CUDA(cudaMallocHost(&s->host_pin, 64 * 1024));
 	s->host_pos.assign(B, 0);
 	s->use_graph = env_int("TG_USE_GRAPH", 1) != 0;
@@ -1224,8 +1309,9 @@ int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp
 	a.force_ids = force_ids;
 	a.minp = minp;
 	a.temp = temp;
-	a.randf = s->randf;
-	a.randf_cap = s->randf_cap;
+	a.randf = s->lean_randf ? s->randf_blk : s->randf;
+	a.randf_cap = s->lean_randf ? STEP_RANDF : s->randf_cap;
+	s->lean_randf = false;
 	a.tok_log = log_tokens ? s->tok_log : nullptr;
 	a.log_cap = s->log_cap;
 	a.dbg = s->mg_dbg;
@@ -1238,9 +1324,16 @@ int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp
 	a.poll_ns = std::max(0, env_int("TG_PS_POLL_NS", 20));
 	a.sched = env_int("TG_PS_SCHED", 0);
 	a.gt = (s->mg_dbg && env_int("TG_PS_GT", 0)) ? s->mg_dbg + 2048 : nullptr;  // (the stamp recorder uses < 600 entries)
-	// every word of the hand-off arena starts as "empty" (all ones)
-	TG_CUDA(cudaMemsetAsync(s->ps_ll, 0xFF, s->ps_ll_bytes, s->stream));
-	TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
+	// Every word of the hand-off arena copy 0 starts as "empty" (all ones) and the barrier counter at
+	// bar_base: a launch that ran through leaves both that way. After an error (or before the first
+	// launch) they are set here.
+	if (!s->ps_clean) {
+		TG_CUDA(cudaMemsetAsync(s->ps_ll, 0xFF, s->ps_ll_bytes, s->stream));
+		TG_CUDA(cudaMemsetAsync(s->mg_bar, 0, 4, s->stream));
+		s->ps_bar_base = 0;
+		s->ps_clean = true;
+	}
+	a.bar_base = s->ps_bar_base;
 	// TG_PS_BEACON=1: every warp leaves progress marks in mapped host memory; if the launch has not finished
 	// after two seconds the marks are printed (where each CTA's slowest and fastest warp stand)
 	static int *beacon_host = nullptr, *beacon_dev = nullptr;
@@ -1257,6 +1350,8 @@ int persist_launch(tg_state *s, int n_steps, int sampler, float minp, float temp
 	TG_CUDA(cudaLaunchCooperativeKernel(fn, dim3(s->mega_grid), dim3(PS_THREADS), params, size_t(a.smem_total), s->stream));
 	count_launch();
 	TG_TRY(check_launch("decode_persist"));
+	// grid barriers per token: logits complete / the arg-max, and two more for min-p (denominator, drawn index)
+	s->ps_bar_base += unsigned(n_steps) * unsigned(sampler == 2 ? 3 : 1) * unsigned(s->mega_grid);
 	if (beacon) {
 		for (int ms = 0; ms < 2000 && cudaStreamQuery(s->stream) == cudaErrorNotReady; ms++) {
 			struct timespec ts = {0, 1000000};
@@ -1370,14 +1465,11 @@ int staging_acquire(tg_state *s) {
 	return TG_OK;
 }
 
-int check_err_flag(tg_state *s) {
-	int flag = 0;
-	TG_CUDA(cudaMemcpyAsync(s->host_pin + 8192, s->err_flag, 4, cudaMemcpyDeviceToHost, s->stream));
-	TG_CUDA(cudaStreamSynchronize(s->stream));
-	s->staging_busy = false;
-	flag = s->host_pin[8192];
+// the error word a kernel left (read back by the caller) -> return code; clears the word on the device
+int report_err_flag(tg_state *s, int flag) {
 	if (flag) {
 		cudaMemsetAsync(s->err_flag, 0, 4, s->stream);
+		s->ps_clean = false;  // a launch that gave up leaves its hand-off words and barrier count anywhere
 		if (flag > 0xFF) {  // the persistent kernel reports where it gave up above the code
 			const int where = flag >> 8;
 			const char *what = (flag & 0xFF) == 3 ? "bulk-copy" : ((flag & 0xFF) == 4 ? "grid-barrier" : "hand-off");
@@ -1391,6 +1483,13 @@ int check_err_flag(tg_state *s) {
 		return fail(TG_ECUDA, flag == 3 ? "persistent kernel: a TMA wait ran out" : "persistent kernel: a grid barrier wait ran out");
 	}
 	return TG_OK;
+}
+
+int check_err_flag(tg_state *s) {
+	TG_CUDA(cudaMemcpyAsync(s->host_pin + 8192, s->err_flag, 4, cudaMemcpyDeviceToHost, s->stream));
+	TG_CUDA(cudaStreamSynchronize(s->stream));
+	s->staging_busy = false;
+	return report_err_flag(s, s->host_pin[8192]);
 }
 
 int ensure_log(tg_state *s, int steps) {
@@ -1761,7 +1860,7 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		         slots, tc.partial, ns_qkv, w.Q.s, w.K.s, w.V.s);
 		count_launch();
 		if (S <= env_int("TG_ATTN_SMALL_MAX", 384))  // short prompts: one (query, head) per warp, S/2 CTAs
-			launch_k(attn_prefill_small_kernel, dim3((S + 1) / 2), dim3(256), 0, st, ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+			launch_k(attn_prefill_small_kernel, dim3((S + 1) / 2), dim3(APS_THREADS), 0, st, ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
 		else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
 				static bool configured[TG_MAX_DEVICES] = {false};
@@ -2099,13 +2198,10 @@ int tg_state_free(tg_state *s) {
 	cudaFree(s->step_pos);
 	cudaFree(s->next_pos);
 	cudaFree(s->ring_base);
-	cudaFree(s->tok);
 	cudaFree(s->tok_log);
 	cudaFree(s->force_ids);
-	cudaFree(s->log_count);
-	cudaFree(s->randf);
-	cudaFree(s->randf_count);
-	cudaFree(s->err_flag);
+	if (!s->randf_in_blk) cudaFree(s->randf);
+	cudaFree(s->step_blk);  // err_flag, tok, randf_count, log_count (and the first randf)
 	cudaFree(s->pf);
 	cudaFree(s->pf_ids);
 	cudaFree(s->bx);
@@ -2284,8 +2380,10 @@ int tg_state_set_randf(tg_state *s, const float *randf_host, int n) {
 	if (!s || !randf_host || n < 1) return fail(TG_EINVAL, "bad argument");
 	TG_CUDA(cudaSetDevice(s->m->device));
 	if (n > s->randf_cap) {
-		if (s->randf) cudaFree(s->randf);
+		if (s->randf && !s->randf_in_blk) cudaFree(s->randf);
 		s->randf = nullptr;
+		s->randf_in_blk = false;
+		s->randf_cap = 0;
 		TG_CUDA(cudaMalloc(&s->randf, size_t(n) * s->B * 4));
 		s->randf_cap = n;
 		// captured graphs do not hold this pointer (the sampler is launched outside the graph)
@@ -2293,6 +2391,7 @@ int tg_state_set_randf(tg_state *s, const float *randf_host, int n) {
 	TG_CUDA(cudaMemcpyAsync(s->randf, randf_host, size_t(n) * s->B * 4, cudaMemcpyHostToDevice, s->stream));
 	TG_CUDA(cudaMemsetAsync(s->randf_count, 0, 4 * s->B, s->stream));
 	TG_CUDA(cudaStreamSynchronize(s->stream));
+	s->randf_valid = std::max(s->randf_valid, n);
 	return TG_OK;
 }
 
@@ -2302,6 +2401,7 @@ int tg_sample_minp(tg_state *s, float minp, float temp, const float *randf_host,
 	TG_CUDA(cudaSetDevice(s->m->device));
 	if (s->randf_cap >= 1 && size_t(s->B) * 4 <= 4096) {
 		// one uniform per sequence, staged through pinned memory: no synchronisation before the launch
+		s->randf_valid = std::max(s->randf_valid, 1);
 		float *stage = reinterpret_cast<float *>(s->host_pin + 4096);
 		std::memcpy(stage, randf_host, size_t(s->B) * 4);
 		TG_CUDA(cudaMemcpyAsync(s->randf, stage, size_t(s->B) * 4, cudaMemcpyHostToDevice, s->stream));
@@ -2324,14 +2424,15 @@ int tg_logits_read(tg_state *s, float *logits_host) {
 	return TG_OK;
 }
 
-int tg_generate_async(tg_state *s, int n_steps, float minp, float temp) {
-	if (!s || n_steps < 1) return fail(TG_EINVAL, "bad argument");
+namespace {
+// `counters_zeroed`: the caller's upload has already set log_count (and randf_count) to zero
+int generate_async(tg_state *s, int n_steps, float minp, float temp, bool counters_zeroed) {
 	TG_TRY(check_ready(s->m));
 	TG_CUDA(cudaSetDevice(s->m->device));
 	if (s->host_pos[0] + n_steps > s->max_pos_global) return fail(TG_ESTATE, "global KV cache too small for n_steps");
-	if (minp < 1.0f && s->randf_cap < n_steps) return fail(TG_ESTATE, "upload uniforms first (tg_state_set_randf)");
+	if (minp < 1.0f && s->randf_valid < n_steps) return fail(TG_ESTATE, "upload uniforms first (tg_state_set_randf)");
 	TG_TRY(ensure_log(s, n_steps));
-	TG_CUDA(cudaMemsetAsync(s->log_count, 0, 4 * s->B, s->stream));
+	if (!counters_zeroed) TG_CUDA(cudaMemsetAsync(s->log_count, 0, 4 * s->B, s->stream));
 	if (s->mega_ok) {
 		TG_TRY(mega_launch(s, n_steps, minp < 1.0f ? 2 : 1, minp, temp, true));
 	} else {
@@ -2342,6 +2443,12 @@ int tg_generate_async(tg_state *s, int n_steps, float minp, float temp) {
 	}
 	for (int b = 0; b < s->B; b++) s->host_pos[b] += n_steps;
 	return TG_OK;
+}
+}  // namespace
+
+int tg_generate_async(tg_state *s, int n_steps, float minp, float temp) {
+	if (!s || n_steps < 1) return fail(TG_EINVAL, "bad argument");
+	return generate_async(s, n_steps, minp, temp, false);
 }
 
 int tg_state_tokens(tg_state *s, int n_steps, int *toks_host) {
@@ -2361,9 +2468,37 @@ int tg_generate(tg_state *s, const int *first_ids, int n_steps, float minp, floa
 	const size_t nbytes = size_t(n_steps) * s->B * 4;
 	const bool lean = nbytes <= 16384;
 	TG_TRY(staging_acquire(s));
+	if (minp < 1.0f && !randf_host) return fail(TG_EINVAL, "min-p sampling needs uniforms");
+	if (n_steps == 1 && s->B == 1 && s->ps_ok && env_int("TG_LEAN_STEP", 1)) {
+		// One token per call (a host loop around the sampler): the step's inputs — id, uniform, zeroed
+		// counters — lie next to each other in the state's step block and go up in ONE copy; the error word
+		// and the sampled id lie next to each other too and come back in ONE; the persistent kernel leaves
+		// its arena and barrier ready for the next launch. So the call is upload, launch, read-back, wait.
+		if (first_ids[0] < 0 || first_ids[0] >= s->m->cfg.n_vocab) return fail(TG_EINVAL, "token id out of range");
+		int *up = s->host_pin;
+		up[0] = first_ids[0];  // tok
+		up[1] = 0;             // randf_count
+		up[2] = 0;             // log_count
+		if (minp < 1.0f) {
+			std::memcpy(up + 3, randf_host, 4);
+			s->randf_valid = std::max(s->randf_valid, 1);
+		}
+		TG_CUDA(cudaMemcpyAsync(s->tok, up, minp < 1.0f ? 16 : 12, cudaMemcpyHostToDevice, s->stream));
+		s->lean_randf = true;
+		const int rc = generate_async(s, 1, minp, temp, true);
+		s->lean_randf = false;
+		if (rc) return rc;
+		int *down = s->host_pin + 8192;
+		TG_CUDA(cudaMemcpyAsync(down, s->err_flag, 20, cudaMemcpyDeviceToHost, s->stream));  // err_flag, pad, tok
+		TG_CUDA(cudaStreamSynchronize(s->stream));
+		s->staging_busy = false;
+		TG_TRY(report_err_flag(s, down[0]));
+		if (toks_host) toks_host[0] = down[4];
+		return TG_OK;
+	}
 	if (minp < 1.0f) {
-		if (!randf_host) return fail(TG_EINVAL, "min-p sampling needs uniforms");
 		if (lean && s->randf_cap >= n_steps) {
+			s->randf_valid = std::max(s->randf_valid, n_steps);
 			float *stage = reinterpret_cast<float *>(s->host_pin + 4096);
 			std::memcpy(stage, randf_host, nbytes);
 			TG_CUDA(cudaMemcpyAsync(s->randf, stage, nbytes, cudaMemcpyHostToDevice, s->stream));
@@ -2558,6 +2693,11 @@ int tg_dev_qmatvec(float *y, const float *x, const int8_t *w, const float *scale
 	TG_CUDA(cudaGetDevice(&dev));
 	int sms = 0;
 	if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) g_num_sms = sms;
+	// the layer matrices: one wave of CTAs, K split over a thread-block cluster (TG_MV_CLUSTER=0: the split-K kernel below)
+	if (env_int("TG_MV_CLUSTER", 1)) {
+		const MvcPlan cp = mvc_plan(K, N, dev);
+		if (cp.ks) return mvc_launch(cp, y, x, w, scales, K, N, (cudaStream_t)stream);
+	}
 	// K-split depth capped (measured on the isolated operator: deeper splits only lengthen the last CTA's sum)
 	MvPlan p = plan_matvec(K, N / MV_TN, env_int("TG_MV_TARGET_CTAS", 2 * g_num_sms), env_int("TG_MV_MAX_SPLIT", K >= 4096 ? 32 : 16));
 	size_t need = size_t(p.nsplit) * N;
