@@ -170,20 +170,33 @@ __global__ void geglu_kernel(float *gate, const float *up, size_t n, GeluLut lut
 // With nsplit > 0 the projections arrive as the raw K-split partial sums of the grouped q|k|v GEMM
 // (part[(sp * S + s) * 1536 + n], columns q | k | v) with the column scales sq / sk / sv; the splits are
 // added in ascending order and scaled here, and v is written out as well.
+// Several prompts of the same length share a launch: blockIdx.y is the prompt, its rows are
+// blockIdx.y * S .. of the `rows` rows of q / k / v / part, and its caches follow each other at
+// cache_stride floats.
 __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, float *k, float *v, const float *rmsq,
                                                                     const float *rmsk, const float *cosT,
                                                                     const float *sinT, float *kcache, float *vcache,
                                                                     int S, int slots, const float *part, int nsplit,
-                                                                    const float *sq, const float *sk, const float *sv) {
+                                                                    const float *sq, const float *sk, const float *sv,
+                                                                    int rows, size_t cache_stride) {
 	pdl_trigger();
 	pdl_wait();
 	const int s = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	{
+		const size_t r0 = size_t(blockIdx.y) * S;  // first row of this prompt
+		q += r0 * 1024;
+		k += r0 * 256;
+		v += r0 * 256;
+		if (part) part += r0 * 1536;
+		kcache += blockIdx.y * cache_stride;
+		vcache += blockIdx.y * cache_stride;
+	}
 	const float *cosr = cosT + size_t(s) * 256, *sinr = sinT + size_t(s) * 256;
 	const int start = (S >= slots) ? (S - slots) : 0;
 	const int c = s - start;  // cache slot, if >= 0
 	// raw element n of this position's q|k|v row (n = column in the concatenated 1536), scaled by scale[ns]
 	auto raw = [&](int n, const float *scale, int ns) -> float {
-		return sum_splits(part + size_t(s) * 1536 + n, size_t(S) * 1536, nsplit) * scale[ns];
+		return sum_splits(part + size_t(s) * 1536 + n, size_t(rows) * 1536, nsplit) * scale[ns];
 	};
 	// x: the head's 256 floats (finished projection if nsplit == 0; always the destination)
 	auto norm_rope = [&](float *x, const float *w, int n0, const float *scale, int ns0) {
@@ -193,7 +206,7 @@ __global__ void __launch_bounds__(192) qk_norm_rope_prefill_kernel(float *q, flo
 			// the lane's eight elements x four splits are requested together; splits are added in ascending order
 #pragma unroll
 			for (int i = 0; i < 4; i++) lo[i] = hi[i] = 0.0f;
-			const size_t sstride = size_t(S) * 1536;
+			const size_t sstride = size_t(rows) * 1536;
 			const float *base = part + size_t(s) * 1536 + n0 + 4 * lane;
 			for (int s0 = 0; s0 < nsplit; s0 += 4) {
 				float4 a[4], b[4];
@@ -275,6 +288,13 @@ constexpr int AP_BLK_SMEM = 4 * AP_TILE * 256 * 4;  // attn_prefill_blk_kernel: 
 
 __global__ void __launch_bounds__(256) attn_prefill_kernel(float *o, const float *q, const float *k, const float *v, int S,
                                                            int is_local, int window) {
+	{
+		const size_t r0 = size_t(blockIdx.y) * S;  // several prompts of the same length share a launch: blockIdx.y is the prompt
+		o += r0 * 1024;
+		q += r0 * 1024;
+		k += r0 * 256;
+		v += r0 * 256;
+	}
 	__shared__ __align__(16) float ks[AP_TILE][256];
 	__shared__ __align__(16) float vs[AP_TILE][256];
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -404,6 +424,13 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_blk_kernel(float *o, cons
                                                                int is_local, int window) {
 	pdl_trigger();
 	pdl_wait();
+	{
+		const size_t r0 = size_t(blockIdx.y) * S;  // several prompts of the same length share a launch: blockIdx.y is the prompt
+		o += r0 * 1024;
+		q += r0 * 1024;
+		k += r0 * 256;
+		v += r0 * 256;
+	}
 	// two K tiles and two V tiles (64 KiB): the next tile is copied asynchronously while this one is consumed
 	extern __shared__ __align__(16) float ap_smem[];
 	float (*ksb)[AP_TILE][256] = reinterpret_cast<float (*)[AP_TILE][256]>(ap_smem);
@@ -570,6 +597,13 @@ __global__ void __launch_bounds__(APS_THREADS, 1) attn_prefill_small_kernel(floa
                                                                            int S, int is_local, int window) {
 	pdl_trigger();
 	pdl_wait();
+	{
+		const size_t r0 = size_t(blockIdx.y) * S;  // several prompts of the same length share a launch: blockIdx.y is the prompt
+		o += r0 * 1024;
+		q += r0 * 1024;
+		k += r0 * 256;
+		v += r0 * 256;
+	}
 	__shared__ __align__(16) float kv[2][AP_TILE][256];  // K tile, V tile; afterwards the 32 warps' partial outputs
 	__shared__ float ml[32][2];
 	float (*ks)[256] = kv[0];

@@ -1784,8 +1784,12 @@ int launch_gemm(float *C, const float *A, const QW &w, int M, float *partial, si
 	return TG_OK;
 }
 
-// prefill of one sequence b with S tokens already in s->pf_ids (device)
-int enqueue_prefill_seq(tg_state *s, int b, int S) {
+// prefill of the nb sequences b .. b + nb - 1, S tokens each, already in s->pf_ids (device). Their rows are
+// stacked (row = sequence * S + position): embedding, norms, GEMMs and GeGLU work on all nb * S rows at once —
+// a GEMM over 178 rows runs at a sixth of the tensor throughput of one over thousands — and only the
+// per-sequence steps (RoPE positions, cache fill, causal attention) index by sequence (blockIdx.y).
+int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
+	const int S = S_seq * nb;  // rows
 	tg_model *m = s->m;
 	const tg_config &c = m->cfg;
 	const int D = c.hidden_size, I = c.intermediate_size, V = c.n_vocab;
@@ -1822,7 +1826,7 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		return launch_gemm_tc(C, w, S, tc, st);
 	};
 
-	launch_k(embed_prefill_kernel, dim3(S), dim3(256), 0, st, m->wte, m->wte_s, (const int *)(s->pf_ids + size_t(b) * S), h, S, D, V,
+	launch_k(embed_prefill_kernel, dim3(S), dim3(256), 0, st, m->wte, m->wte_s, (const int *)(s->pf_ids + size_t(b) * S_seq), h, S, D, V,
 	         float(std::sqrt(double(D))), s->err_flag);
 	count_launch();
 	TG_TRY(check_launch("embed_prefill"));
@@ -1855,12 +1859,12 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 			TG_TRY(gemm(k, xn, w.K, false));
 			TG_TRY(gemm(v, xn, w.V, false));
 		}
-		launch_k(qk_norm_rope_prefill_kernel, dim3(S), dim3(192), 0, st, q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
-		         m->rope[w.is_local ? 1 : 0][1], s->kcache[l] + size_t(b) * slots * AT_HD, s->vcache[l] + size_t(b) * slots * AT_HD, S,
-		         slots, tc.partial, ns_qkv, w.Q.s, w.K.s, w.V.s);
+		launch_k(qk_norm_rope_prefill_kernel, dim3(S_seq, nb), dim3(192), 0, st, q, k, v, w.rmsq, w.rmsk, m->rope[w.is_local ? 1 : 0][0],
+		         m->rope[w.is_local ? 1 : 0][1], s->kcache[l] + size_t(b) * slots * AT_HD, s->vcache[l] + size_t(b) * slots * AT_HD, S_seq,
+		         slots, (const float *)tc.partial, ns_qkv, w.Q.s, w.K.s, w.V.s, S, size_t(slots) * AT_HD);
 		count_launch();
-		if (S <= env_int("TG_ATTN_SMALL_MAX", 384))  // short prompts: one (query, head) per warp, S/2 CTAs
-			launch_k(attn_prefill_small_kernel, dim3((S + 1) / 2), dim3(APS_THREADS), 0, st, ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+		if (S_seq <= env_int("TG_ATTN_SMALL_MAX", 384))  // short prompts: a (query, head)'s keys split over four warps, S/2 CTAs
+			launch_k(attn_prefill_small_kernel, dim3((S_seq + 1) / 2, nb), dim3(APS_THREADS), 0, st, ao, q, k, v, S_seq, w.is_local ? 1 : 0, c.n_pos_local);
 		else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
 				static bool configured[TG_MAX_DEVICES] = {false};
@@ -1869,9 +1873,9 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 					TG_CUDA(cudaFuncSetAttribute(attn_prefill_blk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_BLK_SMEM));
 					configured[dev] = true;
 				}
-				launch_k(attn_prefill_blk_kernel, dim3((S + 7) / 8), dim3(256), AP_BLK_SMEM, st, ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+				launch_k(attn_prefill_blk_kernel, dim3((S_seq + 7) / 8, nb), dim3(256), AP_BLK_SMEM, st, ao, q, k, v, S_seq, w.is_local ? 1 : 0, c.n_pos_local);
 			} else
-				attn_prefill_kernel<<<(S + 7) / 8, 256, 0, st>>>(ao, q, k, v, S, w.is_local ? 1 : 0, c.n_pos_local);
+				attn_prefill_kernel<<<dim3((S_seq + 7) / 8, nb), 256, 0, st>>>(ao, q, k, v, S_seq, w.is_local ? 1 : 0, c.n_pos_local);
 		count_launch();
 		TG_TRY(check_launch("attn_prefill"));
 		if (use_tc) {
@@ -1912,8 +1916,19 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		}
 		TG_TRY(check_launch("prefill layer"));
 	}
-	// lm_head on the last position (modules.hpp:232-240)
-	{
+	// lm_head on the last position of every sequence (modules.hpp:232-240)
+	if (nb >= 4 && use_tc) {
+		// a group: the last rows are gathered (one strided copy), normed, and scored by ONE GEMM over the
+		// vocabulary matrix, as the batched decode step does — not nb matvecs that each stream its 302 MB
+		float *last = xn;  // [nb][D] (xn is free: the tensor-core path packs its norm outputs directly)
+		TG_CUDA(cudaMemcpy2DAsync(last, size_t(D) * 4, h + size_t(S_seq - 1) * D, size_t(S_seq) * D * 4, size_t(D) * 4, nb, cudaMemcpyDeviceToDevice, st));
+		launch_k(rmsnorm_rows_kernel, dim3(nb), dim3(256), 0, st, s->xnorm + size_t(b) * D, (const float *)last, m->final_norm, (const float *)nullptr, D);
+		count_launch();
+		TG_TRY(pack_activations(s->xnorm + size_t(b) * D, nb, D, tc, st));
+		TG_TRY(launch_gemm_tc(s->logits + size_t(b) * V, m->lm_head, nb, tc, st, 0, 1));
+		return TG_OK;
+	}
+	for (int i = 0; i < nb; i++) {
 		MvArgs a{};
 		a.seg[0] = MvSeg{m->lm_head.q, m->lm_head.s, V, 0, 0};
 		a.nseg = 1;
@@ -1924,12 +1939,12 @@ int enqueue_prefill_seq(tg_state *s, int b, int S) {
 		a.B = 1;
 		a.part_stride = V;
 		a.out_stride = V;
-		a.h = h + size_t(S - 1) * D;
+		a.h = h + (size_t(i + 1) * S_seq - 1) * D;
 		a.w_pre = m->final_norm;
-		a.x_out = s->xnorm + size_t(b) * D;
+		a.x_out = s->xnorm + size_t(b + i) * D;
 		a.partial = s->partial;
 		a.tickets = s->tickets;
-		a.out = s->logits + size_t(b) * V;
+		a.out = s->logits + size_t(b + i) * V;
 		TG_TRY(launch_mv(a, PRO_NORM, EPI_SCALE, st));
 	}
 	return TG_OK;
@@ -2272,11 +2287,16 @@ int tg_prefill(tg_state *s, const int *ids, int S, float *logits_host) {
 		TG_TRY(tg_decode(s, ids, logits_host));
 		return TG_OK;
 	}
-	size_t need = size_t(S) * (3 * size_t(D) + 2 * qd + 2 * kd + 2 * size_t(I));
-	size_t part = std::max(size_t(4) * S * D, size_t(1) << 22);  // split-K scratch
-	part = std::max(part, std::min(size_t(24) * S * std::max(I, qd), size_t(1) << 28));  // tensor-core GEMM partial sums (<= 1 GiB)
+	// Batches that take the batched decode step prefill their prompts together, up to 16384 rows per pass (the
+	// scratch grows with the rows: 79 KB per row at the 1B shape); smaller batches stay one sequence per pass, so
+	// that a sequence's results do not depend on its neighbours' presence.
+	const int group = (s->batched_ok && env_int("TG_GEMM_TC", 1) && env_int("TG_PREFILL_GROUP", 1)) ? std::max(1, std::min(s->B, 16384 / S)) : 1;
+	const size_t R = size_t(group) * S;  // rows per pass
+	size_t need = R * (3 * size_t(D) + 2 * qd + 2 * kd + 2 * size_t(I));
+	size_t part = std::max(size_t(4) * R * D, size_t(1) << 22);  // split-K scratch
+	part = std::max(part, std::min(size_t(24) * R * std::max(I, qd), size_t(1) << 28));  // tensor-core GEMM partial sums (<= 1 GiB)
 	need += part;
-	need += (tc_pack_bytes(S, std::max(I, std::max(D, qd))) + 3) / 4 + 64;
+	need += (tc_pack_bytes(int(R), std::max(I, std::max(D, qd))) + 3) / 4 + 64;
 	if (need > s->pf_floats) {
 		if (s->pf) cudaFree(s->pf);
 		s->pf = nullptr;
@@ -2292,7 +2312,7 @@ int tg_prefill(tg_state *s, const int *ids, int S, float *logits_host) {
 		s->pf_ids_cap = S * s->B;
 	}
 	TG_CUDA(cudaMemcpyAsync(s->pf_ids, ids, size_t(S) * s->B * 4, cudaMemcpyHostToDevice, s->stream));
-	for (int b = 0; b < s->B; b++) TG_TRY(enqueue_prefill_seq(s, b, S));
+	for (int b = 0; b < s->B; b += group) TG_TRY(enqueue_prefill_seq(s, b, S, std::min(group, s->B - b)));
 	// position_ptr = S; ring base per decode.hpp:98-103
 	std::vector<int> pos(s->B, S), rb(s->B, S >= c.n_pos_local ? S : 0);
 	TG_TRY(staging_acquire(s));
