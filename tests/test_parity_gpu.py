@@ -406,6 +406,35 @@ def test_both_persistent_decode_kernels_agree(capi, synth, weights_270m, weights
     m.close()
 
 
+def test_small_grid_decodes_the_same_tokens(capi, synth, weights_270m, monkeypatch):
+    """TG_MEGA_GRID=48 leaves the persistent decode a third of the SMs. The dp4a kernel has no plan for so few
+    CTAs, so the fp32-FMA kernel runs, with another unit-to-CTA plan than on the full grid (O-projection K-slices
+    of two heads, 16 instead of 116 CTAs left to wipe the hand-off arena during the attention phase).
+    Teacher-forced on the full grid's greedy tokens: the logits of every one of 16 steps within 2e-5, the arg-max
+    equal where the top-2 gap is above that noise."""
+    m = capi.Model("270m").load_file(weights_270m).build_tables(1 << 20)
+    ids = synth.random_prompt(40, 19)
+    st = m.state(1, 128)
+    st.prefill(ids, want_logits=False)
+    feed = [st.sample_argmax()]
+    want = []
+    for _ in range(16):
+        want.append(st.decode(feed[-1])[0].copy())
+        feed.append(st.sample_argmax())
+    st.close()
+    monkeypatch.setenv("TG_MEGA_GRID", "48")
+    st = m.state(1, 128)
+    st.prefill(ids, want_logits=False)
+    for i in range(16):
+        lg = st.decode(feed[i])[0]
+        assert rel_l2(lg, want[i]) <= 2e-5, i
+        t2 = np.partition(want[i], -2)[-2:]
+        assert int(st.sample_argmax()[0]) == int(feed[i + 1][0]) or float(t2[1] - t2[0]) < 1e-3, i
+    st.close()
+    monkeypatch.delenv("TG_MEGA_GRID")
+    m.close()
+
+
 def test_bounded_wait_returns_an_error_and_the_context_survives(capi, synth, weights_270m, monkeypatch):
     """The persistent decode kernel's waits are bounded by a host-settable limit (TG_PS_WAIT_MS). With one
     producer CTA told to withhold its down-projection hand-off (TG_PS_WITHHOLD_CTA, a debug argument of the

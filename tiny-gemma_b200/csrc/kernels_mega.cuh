@@ -743,11 +743,12 @@ __device__ __noinline__ void mg_attn_merge(const MgArgs &a, MgCtx &ctx, const fl
 	}
 	if (worker) *reinterpret_cast<float4 *>(red + grp * a.C.kc + 4 * c4) = acc;
 	__syncthreads();
-	if (tid < a.C.kc) {
+#pragma unroll 1
+	for (int d = tid; d < a.C.kc; d += MG_THREADS) {  // (a K-slice of two heads has more rows than the CTA has threads)
 		float O = 0.0f;
 #pragma unroll 1
-		for (int g = 0; g < ngrp; g++) O += red[g * a.C.kc + tid];
-		xs[tid] = O;
+		for (int g = 0; g < ngrp; g++) O += red[g * a.C.kc + d];
+		xs[d] = O;
 	}
 	__syncthreads();
 
