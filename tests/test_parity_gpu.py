@@ -605,14 +605,15 @@ def test_long_context_16384_independent_paths_agree(capi, synth, weights_270m, w
 
 @pytest.mark.parametrize("S", [300, 700, 1500])
 def test_prefill_attention_kernels_agree(capi, synth, weights_270m, S, monkeypatch):
-    """The three prefill attention kernels (one (query, head) per warp; one query per warp with four keys
-    per step; one query per warp, key by key) on the same prompt: a sliding-window layer sees every one of
-    them with ragged first and last key blocks."""
+    """The four prefill attention kernels (short-prompt kernel; tcgen05 kernel with bf16-split operands; one
+    query per warp with four keys per step; one query per warp, key by key) on the same prompt: a
+    sliding-window layer sees every one of them with ragged first and last key blocks."""
     m = capi.Model("270m").load_file(weights_270m)
     m.build_tables(1 << 20)
     ids = synth.random_prompt(S, 99)
     logits = []
-    for env in ({"TG_ATTN_SMALL_MAX": "100000"}, {"TG_ATTN_SMALL_MAX": "0"}, {"TG_ATTN_SMALL_MAX": "0", "TG_ATTN_BLOCK4": "0"}):
+    for env in ({"TG_ATTN_SMALL_MAX": "100000"}, {"TG_ATTN_SMALL_MAX": "0", "TG_ATTN_TC_MIN": "0"}, {"TG_ATTN_SMALL_MAX": "0", "TG_ATTN_TC": "0"},
+                {"TG_ATTN_SMALL_MAX": "0", "TG_ATTN_TC": "0", "TG_ATTN_BLOCK4": "0"}):
         for k, v in env.items():
             monkeypatch.setenv(k, v)
         st = m.state(1, S + 16)
@@ -620,8 +621,8 @@ def test_prefill_attention_kernels_agree(capi, synth, weights_270m, S, monkeypat
         st.close()
         for k in env:
             monkeypatch.delenv(k)
-    assert rel_l2(logits[0], logits[2]) <= 2e-5
-    assert rel_l2(logits[1], logits[2]) <= 2e-5
+    for i in range(3):
+        assert rel_l2(logits[i], logits[3]) <= 2e-5, i
     m.close()
 
 

@@ -20,6 +20,7 @@
 #include "kernels_mega.cuh"
 #include "kernels_persist.cuh"
 #include "kernels_gemm_tc.cuh"
+#include "kernels_attn_tc.cuh"
 #include "kernels_prefill.cuh"
 #include "kernels_sampler.cuh"
 
@@ -1531,6 +1532,23 @@ size_t tc_pack_bytes(int M, int K) {
 	return 3 * m_tiles * size_t(K / TC_BK) * TC_TILE_BYTES;
 }
 
+// packed operands of the tensor-core prefill attention for one prompt of S tokens: Q (4 S rows), K (S rows), V
+struct AttnTcPlan {
+	int q_tiles, k_tiles, v_blocks;
+	size_t q_bytes, k_bytes, v_bytes;
+	size_t total() const { return q_bytes + k_bytes + v_bytes; }
+};
+AttnTcPlan attn_tc_plan(int S) {
+	AttnTcPlan p;
+	p.q_tiles = (4 * S + TC_BM - 1) / TC_BM;
+	p.k_tiles = (S + TC_BM - 1) / TC_BM;
+	p.v_blocks = 2 * ((S + AT_TC_KT - 1) / AT_TC_KT);
+	p.q_bytes = size_t(3) * p.q_tiles * 8 * TC_TILE_BYTES;
+	p.k_bytes = size_t(3) * p.k_tiles * 8 * TC_TILE_BYTES;
+	p.v_bytes = size_t(3) * p.v_blocks * 16384;
+	return p;
+}
+
 int pack_activations(const float *A, int M, int K, const TcScratch &sc, cudaStream_t st) {
 	if (tc_pack_bytes(M, K) > sc.apack_bytes) return fail(TG_ENOMEM, "tensor-core GEMM scratch too small");
 	const int m_tiles = (M + TC_BM - 1) / TC_BM;
@@ -1815,6 +1833,19 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 		tc.err = s->err_flag;
 		p += (tc.apack_bytes + 3) / 4;
 	}
+	// long prompts, one sequence per pass: attention on the tensor cores, from packed copies of q, k and v
+	// (from 1024 tokens on: below, the three packing launches cost what the tensor cores save)
+	const bool attn_tc = use_tc && nb == 1 && S_seq > env_int("TG_ATTN_SMALL_MAX", 384) && env_int("TG_ATTN_TC", 1) &&
+	                     S_seq >= env_int("TG_ATTN_TC_MIN", 1024);
+	const AttnTcPlan atp = attn_tc_plan(S_seq);
+	__nv_bfloat16 *at_q = nullptr, *at_k = nullptr, *at_v = nullptr;
+	if (attn_tc) {
+		p = reinterpret_cast<float *>((uintptr_t(p) + 1023) & ~uintptr_t(1023));
+		at_q = reinterpret_cast<__nv_bfloat16 *>(p);
+		at_k = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<uint8_t *>(p) + atp.q_bytes);
+		at_v = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<uint8_t *>(p) + atp.q_bytes + atp.k_bytes);
+		p += (atp.total() + 3) / 4;
+	}
 	float *part = p;
 	size_t part_floats = s->pf_floats - size_t(part - s->pf);
 	tc.partial = part;
@@ -1865,7 +1896,38 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 		count_launch();
 		if (S_seq <= env_int("TG_ATTN_SMALL_MAX", 384))  // short prompts: a (query, head)'s keys split over four warps, S/2 CTAs
 			launch_k(attn_prefill_small_kernel, dim3((S_seq + 1) / 2, nb), dim3(APS_THREADS), 0, st, ao, q, k, v, S_seq, w.is_local ? 1 : 0, c.n_pos_local);
-		else
+		else if (attn_tc) {
+			static bool at_configured[TG_MAX_DEVICES] = {false};
+			const int dev = current_device_slot();
+			if (!at_configured[dev]) {
+				TG_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_TC_SMEM));
+				at_configured[dev] = true;
+			}
+			auto pack_rows = [&](const float *src, __nv_bfloat16 *dst, int rows, int tiles) {
+				const size_t chunks = size_t(tiles) * TC_BM * (256 / 8);
+				launch_k(split_pack_kernel, dim3(unsigned(std::min<size_t>((chunks + 255) / 256, size_t(g_num_sms) * 16))), dim3(256), 0, st, src, dst, rows,
+				         256, tiles);
+				count_launch();
+			};
+			pack_rows(q, at_q, 4 * S_seq, atp.q_tiles);  // rows = (query, head) pairs as they lie in q [S][4][256]
+			pack_rows(k, at_k, S_seq, atp.k_tiles);
+			launch_k(attn_pack_v_kernel, dim3(unsigned(std::min<size_t>((size_t(atp.v_blocks) * 1024 + 255) / 256, size_t(g_num_sms) * 16))), dim3(256), 0,
+			         st, (const float *)v, at_v, S_seq, atp.v_blocks);
+			count_launch();
+			AttnTcArgs aa{};
+			aa.qp = at_q;
+			aa.kp = at_k;
+			aa.vp = at_v;
+			aa.o = ao;
+			aa.S = S_seq;
+			aa.q_tiles = atp.q_tiles;
+			aa.k_tiles = atp.k_tiles;
+			aa.v_blocks = atp.v_blocks;
+			aa.is_local = w.is_local ? 1 : 0;
+			aa.window = c.n_pos_local;
+			aa.err = s->err_flag;
+			launch_k(attn_prefill_tc_kernel, dim3(atp.q_tiles), dim3(AT_TC_THREADS), size_t(AT_TC_SMEM), st, aa);
+		} else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
 				static bool configured[TG_MAX_DEVICES] = {false};
 				const int dev = current_device_slot();
@@ -2297,6 +2359,7 @@ int tg_prefill(tg_state *s, const int *ids, int S, float *logits_host) {
 	part = std::max(part, std::min(size_t(24) * R * std::max(I, qd), size_t(1) << 28));  // tensor-core GEMM partial sums (<= 1 GiB)
 	need += part;
 	need += (tc_pack_bytes(int(R), std::max(I, std::max(D, qd))) + 3) / 4 + 64;
+	need += (attn_tc_plan(S).total() + 3) / 4 + 512;  // packed q, k, v of the tensor-core attention (long prompts)
 	if (need > s->pf_floats) {
 		if (s->pf) cudaFree(s->pf);
 		s->pf = nullptr;
