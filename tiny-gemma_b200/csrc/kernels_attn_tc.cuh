@@ -16,31 +16,38 @@
 // matrices), so that the CTA fetches them with plain bulk copies:
 //     Q, K: split_pack_kernel ([3 terms][128-row tiles][8 blocks of 32 dimensions][8 KiB], K-major; a 64-key
 //           tile is one half of a 128-row tile)
-//     V:    attn_pack_v_kernel ([3 terms][32-key blocks][16 KiB], N-major like the GEMM's weight operand)
-// Warps 0-3: softmax and epilogue (TMEM lanes 32 w ..); warp 4: one thread issues the bulk copies and the MMAs.
-// Per key tile the ring carries eight Q|K blocks (one per 32 dimensions) and two V blocks (32 keys each);
-// the V blocks land while the softmax runs. All waits are bounded; a wait that runs out sets *err, and the
-// CTA lets its copies land and frees its TMEM before it returns.
+//     V:    attn_pack_v_kernel ([3 terms][16-key blocks][8 KiB], N-major like the GEMM's weight operand)
+// Warps 0-7: softmax and epilogue (two threads per row: warps w and w + 4 share the TMEM lanes 32 (w % 4) ..
+// and take half of a tile's keys each); warp 8: one thread issues the MMAs; warp 9: one thread issues the bulk
+// copies, up to four ring blocks ahead of the MMAs.
+// Per key tile the ring carries eight Q|K blocks (one per 32 dimensions) and four V blocks (16 keys each).
+// S is double-buffered in TMEM and the MMAs are issued as Q K_0^T, Q K_1^T, P V_0, Q K_2^T, P V_1, ...: while the
+// softmax warps work on tile t the tensor core runs Q K_{t+1}^T and P V_{t-1}. The running max is only moved (and
+// O rescaled, a TMEM round trip) when a row's new max exceeds the one in use by more than 8: the probabilities
+// are then at most e^8, far inside fp32, and the final division by the row sum removes the common factor.
+// All waits are bounded; a wait that runs out sets *err, and the CTA lets its copies land and frees its
+// TMEM before it returns.
 #pragma once
 #include "kernels_gemm_tc.cuh"
 
 namespace tg {
 
 constexpr int AT_TC_KT = 64;                       // keys per tile
-constexpr int AT_TC_STAGE = 3 * 16384;             // ring stage: Q (3 x 8 KiB) + K (3 x 4 KiB), or V (3 x 16 KiB)
-constexpr int AT_TC_NS = 3;                        // ring stages
+constexpr int AT_TC_STAGE = 36 * 1024;             // ring stage: Q (3 x 8 KiB) + K (3 x 4 KiB), or V (3 x 8 KiB)
+constexpr int AT_TC_NS = 4;                        // ring stages
 constexpr int AT_TC_PBYTES = 3 * 2 * TC_TILE_BYTES;  // P: 3 terms x 2 blocks of 32 keys x [128][32] bf16
 constexpr int AT_TC_SMEM = AT_TC_NS * AT_TC_STAGE + AT_TC_PBYTES + 1024;
-constexpr int AT_TC_THREADS = 160;
-constexpr int AT_TC_BLOCKS = 10;                   // ring blocks per key tile: 8 of Q|K, 2 of V
+constexpr int AT_TC_THREADS = 320;                 // 8 softmax warps, the MMA-issuing warp, the copy-issuing warp
+constexpr int AT_TC_BLOCKS = 12;                   // ring blocks per key tile: 8 of Q|K (32 dimensions each), 4 of V (16 keys each)
+constexpr int AT_TC_VBYTES = 8192;                 // one term of a V block: [16 keys][256 dimensions] bf16
 
-// v fp32 [S][256] -> three bf16 terms in the N-major operand layout, one 16 KiB tile per 32 keys:
-// byte offset of (key k, dimension n) = (n / 8) * 512 + (k / 8) * 128 + (k % 8) * 16 + (n % 8) * 2. Keys >= S are zero.
+// v fp32 [S][256] -> three bf16 terms in the N-major operand layout, one 8 KiB tile per 16 keys (one MMA K-step):
+// byte offset of (key k, dimension n) = (n / 8) * 256 + (k / 8) * 128 + (k % 8) * 16 + (n % 8) * 2. Keys >= S are zero.
 __global__ void __launch_bounds__(256) attn_pack_v_kernel(const float *v, __nv_bfloat16 *out, int S, int nblocks) {
 	pdl_trigger();
 	pdl_wait();
-	const size_t term_stride = size_t(nblocks) * 8192;  // elements
-	const size_t n_items = size_t(nblocks) * 32 * 32;   // (key, 8 consecutive dimensions)
+	const size_t term_stride = size_t(nblocks) * 4096;  // elements
+	const size_t n_items = size_t(nblocks) * 16 * 32;   // (key, 8 consecutive dimensions)
 	for (size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_items; c += size_t(gridDim.x) * blockDim.x) {
 		const int key = int(c >> 5), n8 = int(c & 31);
 		float x[8];
@@ -60,8 +67,8 @@ __global__ void __launch_bounds__(256) attn_pack_v_kernel(const float *v, __nv_b
 			mid[i] = __float2bfloat16_rn(r1);
 			lo[i] = __float2bfloat16_rn(r1 - __bfloat162float(mid[i]));
 		}
-		const int kb = key >> 5, k = key & 31;
-		const size_t off = size_t(kb) * 8192 + n8 * 256 + (k >> 3) * 64 + (k & 7) * 8;  // elements
+		const int kb = key >> 4, k = key & 15;
+		const size_t off = size_t(kb) * 4096 + n8 * 128 + (k >> 3) * 64 + (k & 7) * 8;  // elements
 		*reinterpret_cast<uint4 *>(out + off) = *reinterpret_cast<const uint4 *>(hi);
 		*reinterpret_cast<uint4 *>(out + term_stride + off) = *reinterpret_cast<const uint4 *>(mid);
 		*reinterpret_cast<uint4 *>(out + 2 * term_stride + off) = *reinterpret_cast<const uint4 *>(lo);
@@ -71,6 +78,16 @@ __global__ void __launch_bounds__(256) attn_pack_v_kernel(const float *v, __nv_b
 // instruction descriptor: D fp32, A and B bf16, A K-major, B K-major (b_mn = 0) or N-major (1), M = 128, N = n
 __device__ __forceinline__ uint32_t at_idesc(int n, int b_mn) {
 	return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(b_mn) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
+}
+// shared-memory matrix descriptor of a V block: no swizzle, 128 B between the two 8-key groups, 256 B between
+// groups of 8 dimensions
+__device__ __forceinline__ uint64_t at_vdesc(uint32_t smem_addr) {
+	uint64_t d = 0;
+	d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+	d |= uint64_t(128 >> 4) << 16;
+	d |= uint64_t(256 >> 4) << 32;
+	d |= uint64_t(1) << 46;
+	return d;
 }
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
 	asm volatile(
@@ -95,10 +112,32 @@ __device__ __forceinline__ bool at_wait(uint64_t *bar, uint32_t parity, int *err
 	return true;
 }
 
+// The two threads of a row hand each other one float through shared memory: value, then tag; the reader
+// polls the partner's tag (bounded like every wait here).
+__device__ __forceinline__ bool at_exchange(float *val, int *tag, int me, float v, int t, float *other, int *err, volatile int *s_fail) {
+	volatile float *xv = val;
+	volatile int *xg = tag;
+	xv[me] = v;
+	__threadfence_block();
+	xg[me] = t;
+	int spins = 0;
+	while (xg[me ^ 1] != t) {
+		if ((++spins & 1023) == 0 && *s_fail) return false;
+		if (spins > TC_SPIN_CAP) {
+			atomicExch(err, 6);
+			*s_fail = 1;
+			return false;
+		}
+	}
+	__threadfence_block();
+	*other = xv[me ^ 1];
+	return true;
+}
+
 struct AttnTcArgs {
 	const __nv_bfloat16 *qp;  // [3][q_tiles][8][8 KiB]
 	const __nv_bfloat16 *kp;  // [3][k_tiles][8][8 KiB]
-	const __nv_bfloat16 *vp;  // [3][v_blocks][16 KiB]
+	const __nv_bfloat16 *vp;  // [3][v_blocks][8 KiB]
 	float *o;                 // [S][4][256]
 	int S, q_tiles, k_tiles, v_blocks;
 	int is_local, window;
@@ -112,11 +151,14 @@ __global__ void __launch_bounds__(AT_TC_THREADS, 1) attn_prefill_tc_kernel(AttnT
 	uint8_t *pbuf = smem + AT_TC_NS * AT_TC_STAGE;
 	__shared__ uint64_t full_bar[AT_TC_NS];  // the stage's copies landed
 	__shared__ uint64_t free_bar[AT_TC_NS];  // the MMAs that read the stage have completed
-	__shared__ uint64_t s_bar;               // S = Q K^T of this key tile is complete (and every earlier MMA)
-	__shared__ uint64_t p_bar;               // the four softmax warps wrote P and rescaled O
+	__shared__ uint64_t s_bar[2];            // S = Q K^T of a key tile is complete (two S buffers, tiles alternate)
+	__shared__ uint64_t p_bar;               // the eight softmax warps wrote P and rescaled O
+	__shared__ uint64_t pv_bar;              // P V of a key tile is complete: P may be overwritten, O read
 	__shared__ uint64_t o_bar;               // all MMAs done
 	__shared__ uint32_t tmem_base_s;
 	__shared__ int s_fail;
+	__shared__ float xm[2][128][2];          // half-row maxima (by tile parity), row sums at the end
+	__shared__ int xt[2][128][2];            // their tags: the exchange between the two threads of a row is a bounded poll
 
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int tile = int(gridDim.x) - 1 - int(blockIdx.x);  // the tiles with the most keys start first
@@ -132,13 +174,16 @@ __global__ void __launch_bounds__(AT_TC_THREADS, 1) attn_prefill_tc_kernel(AttnT
 			mbar_init(&full_bar[s], 1);
 			mbar_init(&free_bar[s], 1);
 		}
-		mbar_init(&s_bar, 1);
-		mbar_init(&p_bar, 4);
+		mbar_init(&s_bar[0], 1);
+		mbar_init(&s_bar[1], 1);
+		mbar_init(&p_bar, 8);
+		mbar_init(&pv_bar, 1);
 		mbar_init(&o_bar, 1);
 		s_fail = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
-	if (warp == 4) {  // TMEM: S in columns 0..63, O in columns 128..383
+	for (int i = tid; i < 2 * 128 * 2; i += AT_TC_THREADS) (&xt[0][0][0])[i] = 0;
+	if (warp == 8) {  // TMEM: S in columns 0..63 and 64..127 (alternating tiles), O in columns 128..383
 		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512) : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 	}
@@ -148,23 +193,34 @@ __global__ void __launch_bounds__(AT_TC_THREADS, 1) attn_prefill_tc_kernel(AttnT
 	const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128u;
 	volatile int *fail = &s_fail;
 
-	if (warp == 4) {
-		// ------------------------------------------------------------ copies and MMAs (one thread)
+	// MMA order: QK(0), then for t = 1 .. n: QK(t) (if t < n), PV(t - 1). Ring block g in that order:
+	// g < 8: QK(0) block g; else g' = g - 8, t = 1 + g' / 12, r = g' % 12: QK(t) block r (r < 8, t < n) or PV(t - 1)
+	// block r - 8 (t < n), and the last four blocks are PV(n - 1).
+	struct Blk {
+		int qk, tile, i;  // qk: 1 = Q|K block i (dimensions 32 i ..) of key tile `tile`, 0 = V block i (keys 16 i ..) of it
+	};
+	auto blk = [&](int g) -> Blk {
+		if (g < 8) return Blk{1, 0, g};
+		const int gp = g - 8, t = 1 + gp / AT_TC_BLOCKS, r = gp % AT_TC_BLOCKS;
+		if (t >= ntiles) return Blk{0, ntiles - 1, r};
+		return r < 8 ? Blk{1, t, r} : Blk{0, t - 1, r - 8};
+	};
+	const int total = ntiles * AT_TC_BLOCKS;
+	if (warp == 9) {
+		// ------------------------------------------------------------ bulk copies (one thread), up to AT_TC_NS blocks ahead
 		if (lane == 0) {
 			pdl_wait();  // the packed operands are the predecessors' output
-			const uint32_t idesc_qk = at_idesc(AT_TC_KT, 0), idesc_pv = at_idesc(256, 1);
 			const size_t q_term = size_t(a.q_tiles) * 8 * TC_TILE_BYTES, k_term = size_t(a.k_tiles) * 8 * TC_TILE_BYTES,
-			             v_term = size_t(a.v_blocks) * 16384;  // bytes
+			             v_term = size_t(a.v_blocks) * AT_TC_VBYTES;  // bytes
 			const uint8_t *qp = reinterpret_cast<const uint8_t *>(a.qp), *kp = reinterpret_cast<const uint8_t *>(a.kp),
 			              *vp = reinterpret_cast<const uint8_t *>(a.vp);
-			const int total = ntiles * AT_TC_BLOCKS;
-			// ring block g: key tile j_lo + g / 10; i = g % 10 < 8: the Q|K block of dimensions 32 i ..; else V block i - 8
-			auto issue_load = [&](int g) -> bool {
+			for (int g = 0; g < total; g++) {
 				const int st = g % AT_TC_NS, use = g / AT_TC_NS;
-				if (use > 0 && !at_wait(&free_bar[st], (use - 1) & 1, a.err, fail)) return false;
-				const int j = j_lo + g / AT_TC_BLOCKS, i = g % AT_TC_BLOCKS;
+				if (use > 0 && !at_wait(&free_bar[st], (use - 1) & 1, a.err, fail)) break;
+				const Blk b = blk(g);
+				const int j = j_lo + b.tile, i = b.i;
 				uint8_t *dst = smem + size_t(st) * AT_TC_STAGE;
-				if (i < 8) {
+				if (b.qk) {
 					mbar_expect_tx(&full_bar[st], 3u * TC_TILE_BYTES + 3u * (TC_TILE_BYTES / 2));
 					for (int t = 0; t < 3; t++) {
 						bulk_load(dst + t * TC_TILE_BYTES, qp + t * q_term + (size_t(tile) * 8 + i) * TC_TILE_BYTES, TC_TILE_BYTES, &full_bar[st]);
@@ -173,108 +229,136 @@ __global__ void __launch_bounds__(AT_TC_THREADS, 1) attn_prefill_tc_kernel(AttnT
 						          &full_bar[st]);
 					}
 				} else {
-					mbar_expect_tx(&full_bar[st], 3u * 16384u);
+					mbar_expect_tx(&full_bar[st], 3u * AT_TC_VBYTES);
 					for (int t = 0; t < 3; t++)
-						bulk_load(dst + t * 16384, vp + t * v_term + (size_t(2 * j + (i - 8))) * 16384, 16384, &full_bar[st]);
+						bulk_load(dst + t * AT_TC_VBYTES, vp + t * v_term + (size_t(4 * j + i)) * AT_TC_VBYTES, AT_TC_VBYTES, &full_bar[st]);
 				}
-				return true;
-			};
-			bool ok = true;
-			for (int g = 0; g < AT_TC_NS - 1 && g < total && ok; g++) ok = issue_load(g);
+			}
+		}
+	} else if (warp == 8) {
+		// ------------------------------------------------------------ MMAs (one thread)
+		if (lane == 0) {
+			const uint32_t idesc_qk = at_idesc(AT_TC_KT, 0), idesc_pv = at_idesc(256, 1);
 			// the six term products (A term, B term)
 			const int ta[6] = {0, 0, 1, 1, 0, 2}, tb[6] = {0, 1, 0, 1, 2, 0};
+			bool ok = true;
 			for (int g = 0; g < total && ok; g++) {
-				const int i = g % AT_TC_BLOCKS, jt = g / AT_TC_BLOCKS;
-				if (g + AT_TC_NS - 1 < total) ok = issue_load(g + AT_TC_NS - 1);
-				if (!ok) break;
-				if (i == 8 && !at_wait(&p_bar, jt & 1, a.err, fail)) { ok = false; break; }  // P written, O rescaled
+				const Blk b = blk(g);
+				if (!b.qk && b.i == 0 && !at_wait(&p_bar, b.tile & 1, a.err, fail)) { ok = false; break; }  // P written, O rescaled
 				const int st = g % AT_TC_NS, use = g / AT_TC_NS;
 				if (!at_wait(&full_bar[st], use & 1, a.err, fail)) { ok = false; break; }
 				tc_fence_after();
 				const uint32_t base = smem_u32(smem + size_t(st) * AT_TC_STAGE);
-				if (i < 8) {
+				if (b.qk) {
+					const uint32_t d_s = tmem_s + uint32_t((b.tile & 1) * AT_TC_KT);
 #pragma unroll
 					for (int c = 0; c < 6; c++) {
 						const uint32_t qa = base + ta[c] * TC_TILE_BYTES, kb_ = base + 3 * TC_TILE_BYTES + tb[c] * (TC_TILE_BYTES / 2);
 #pragma unroll
 						for (int j2 = 0; j2 < 2; j2++)
-							tc_mma(tmem_s, tc_smem_desc(qa + j2 * 256), tc_smem_desc(kb_ + j2 * 256), idesc_qk, (i > 0 || c > 0 || j2 > 0) ? 1u : 0u);
+							tc_mma(d_s, tc_smem_desc(qa + j2 * 256), tc_smem_desc(kb_ + j2 * 256), idesc_qk, (b.i > 0 || c > 0 || j2 > 0) ? 1u : 0u);
 					}
 					tc_commit(&free_bar[st]);
-					if (i == 7) tc_commit(&s_bar);
+					if (b.i == 7) tc_commit(&s_bar[b.tile & 1]);
 				} else {
-					const int vb = i - 8;
+					const int vb = b.i;  // keys 16 vb ..: K-step vb % 2 of P's 32-key block vb / 2
 					const uint32_t pb = smem_u32(pbuf);
 #pragma unroll
 					for (int c = 0; c < 6; c++) {
-						const uint32_t pa = pb + (ta[c] * 2 + vb) * TC_TILE_BYTES, vv = base + tb[c] * 16384;
-#pragma unroll
-						for (int j2 = 0; j2 < 2; j2++)
-							tc_mma(tmem_o, tc_smem_desc(pa + j2 * 256), tc_smem_desc(vv + j2 * 256), idesc_pv, (jt > 0 || vb > 0 || c > 0 || j2 > 0) ? 1u : 0u);
+						const uint32_t pa = pb + (ta[c] * 2 + (vb >> 1)) * TC_TILE_BYTES + (vb & 1) * 256, vv = base + tb[c] * AT_TC_VBYTES;
+						tc_mma(tmem_o, tc_smem_desc(pa), at_vdesc(vv), idesc_pv, (b.tile > 0 || vb > 0 || c > 0) ? 1u : 0u);
 					}
 					tc_commit(&free_bar[st]);
+					if (vb == 3) tc_commit(&pv_bar);
 				}
 			}
 			tc_commit(&o_bar);
 		}
 	} else {
-		// ------------------------------------------------------------ softmax (thread = row = TMEM lane)
-		const int r = tid;                         // row of the tile
+		// ------------------------------------------------------------ softmax (two threads per row = TMEM lane)
+		// warps w and w + 4 share the TMEM lanes 32 (w % 4) ..: thread (w, lane) owns row 32 (w % 4) + lane and the
+		// 32 keys 32 (w / 4) .. of every tile (= one of P's two 32-key blocks), and half of O's columns
+		const int qd = warp & 3, hf = warp >> 2;
+		const int r = qd * 32 + lane;              // row of the tile
 		const int qi = q0 + (r >> 2);              // this row's query
 		const bool row_ok = qi < a.S;
 		const int k_min = a.is_local ? max(0, qi - a.window) : 0;
-		const uint32_t lane_base = uint32_t(warp * 32) << 16;
-		float m = -INFINITY, l = 0.0f;
+		const uint32_t lane_base = uint32_t(qd * 32) << 16;
+		float m = -INFINITY, l = 0.0f;             // max in use (the same in both threads of a row), sum over this thread's keys
 		bool ok = true;
 		for (int jt = 0; jt < ntiles && ok; jt++) {
-			if (!at_wait(&s_bar, jt & 1, a.err, fail)) { ok = false; break; }
+			if (!at_wait(&s_bar[jt & 1], (jt >> 1) & 1, a.err, fail)) { ok = false; break; }
 			tc_fence_after();
-			uint32_t s0[32], s1[32];
-			tc_ld32(tmem_s + lane_base, s0);
-			tc_ld32(tmem_s + lane_base + 32u, s1);
+			uint32_t sv[32];
+			tc_ld32(tmem_s + lane_base + uint32_t((jt & 1) * AT_TC_KT + 32 * hf), sv);
 			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-			const int kbase = (j_lo + jt) * AT_TC_KT;
+			const int kbase = (j_lo + jt) * AT_TC_KT + 32 * hf;
+			// (most tiles lie wholly inside every row's key range: no per-key test there)
+			const bool all_vis = (j_lo + jt) * AT_TC_KT + AT_TC_KT - 1 <= q0 && (!a.is_local || (j_lo + jt) * AT_TC_KT >= q0 + 31 - a.window);
 			float mt = -INFINITY;
+			if (all_vis) {
 #pragma unroll
-			for (int c = 0; c < 64; c++) {
-				const int key = kbase + c;
-				const bool vis = row_ok && key <= qi && key >= k_min;
-				float sv = __uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]) * 0.0625f;  // 1 / sqrt(256), exact
-				sv = vis ? sv : -INFINITY;
-				if (c < 32) s0[c & 31] = __float_as_uint(sv); else s1[c & 31] = __float_as_uint(sv);
-				mt = fmaxf(mt, sv);
-			}
-			const float mn = fmaxf(m, mt);
-			const bool none = mn == -INFINITY;            // no visible key so far
-			const float corr = none ? 1.0f : expf(m - mn);  // exp(-inf) = 0 at the row's first visible tile
-			float sum = 0.0f;
-			// probabilities -> three bf16 terms in the A-operand layout: P[term][block of 32 keys] tiles of [128][32]
-#pragma unroll
-			for (int kc = 0; kc < 8; kc++) {  // 8 keys at a time
-				__align__(16) __nv_bfloat16 hi[8], mid[8], lo[8];
-#pragma unroll
-				for (int u = 0; u < 8; u++) {
-					const int c = 8 * kc + u;
-					const float sv = __uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]);
-					const float p = none ? 0.0f : expf(sv - mn);  // exp(-inf) = 0 for masked keys
-					sum += p;
-					hi[u] = __float2bfloat16_rn(p);
-					const float r1 = p - __bfloat162float(hi[u]);
-					mid[u] = __float2bfloat16_rn(r1);
-					lo[u] = __float2bfloat16_rn(r1 - __bfloat162float(mid[u]));
+				for (int c = 0; c < 32; c++) {
+					const float x = __uint_as_float(sv[c]) * 0.0625f;  // 1 / sqrt(256), exact
+					sv[c] = __float_as_uint(x);
+					mt = fmaxf(mt, x);
 				}
-				const int vb = kc >> 2, k8 = kc & 3;
-				uint8_t *dst = pbuf + vb * TC_TILE_BYTES + (r >> 3) * 512 + k8 * 128 + (r & 7) * 16;
-				*reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(hi);
-				*reinterpret_cast<uint4 *>(dst + 2 * TC_TILE_BYTES) = *reinterpret_cast<const uint4 *>(mid);
-				*reinterpret_cast<uint4 *>(dst + 4 * TC_TILE_BYTES) = *reinterpret_cast<const uint4 *>(lo);
+			} else {
+#pragma unroll
+				for (int c = 0; c < 32; c++) {
+					const int key = kbase + c;
+					const bool vis = row_ok && key <= qi && key >= k_min;
+					const float x = vis ? __uint_as_float(sv[c]) * 0.0625f : -INFINITY;
+					sv[c] = __float_as_uint(x);
+					mt = fmaxf(mt, x);
+				}
+			}
+			// the row's max over both halves
+			{
+				float other;
+				if (!at_exchange(xm[jt & 1][r], xt[jt & 1][r], hf, mt, jt + 1, &other, a.err, fail)) { ok = false; break; }
+				mt = fmaxf(mt, other);
+			}
+			// the max in use moves only when the new one exceeds it by more than 8 (or at the row's first visible key)
+			const float mn = (mt > m + 8.0f || m == -INFINITY) ? fmaxf(m, mt) : m;
+			const bool none = mn == -INFINITY;            // no visible key so far
+			const float corr = none ? 1.0f : expf(m - mn);  // exp(-inf) = 0 at the row's first visible tile; 1 when the max stays
+			// probabilities and their three bf16 terms by truncation (p >= 0; hi + mid + lo = p exactly: 8 + 8 + 8 bits)
+			float sum = 0.0f;
+			uint32_t ph[16], pm[16], pl[16];  // bf16 pairs
+#pragma unroll
+			for (int c = 0; c < 32; c += 2) {
+				uint32_t hb[2], mb[2], lb[2];
+#pragma unroll
+				for (int u = 0; u < 2; u++) {
+					const float pv = none ? 0.0f : expf(__uint_as_float(sv[c + u]) - mn);  // exp(-inf) = 0 for masked keys
+					sum += pv;
+					hb[u] = __float_as_uint(pv) & 0xFFFF0000u;
+					const float r1 = pv - __uint_as_float(hb[u]);
+					mb[u] = __float_as_uint(r1) & 0xFFFF0000u;
+					lb[u] = __float_as_uint(r1 - __uint_as_float(mb[u]));  // at most 8 significant bits: exact in bf16
+				}
+				ph[c / 2] = __byte_perm(hb[0], hb[1], 0x7632);
+				pm[c / 2] = __byte_perm(mb[0], mb[1], 0x7632);
+				pl[c / 2] = __byte_perm(lb[0], lb[1], 0x7632);
 			}
 			l = fmaf(l, corr, sum);
 			m = mn;
-			// O = corr * O (the previous tile's P V has completed: s_bar follows it in the issue order)
+			// the previous tile's P V reads P (and accumulates into O) until pv_bar: wait for it before touching either
+			if (jt > 0 && !at_wait(&pv_bar, (jt - 1) & 1, a.err, fail)) { ok = false; break; }
+			tc_fence_after();
+			// P[term][block hf] tiles of [128][32] in the A-operand layout
+#pragma unroll
+			for (int k8 = 0; k8 < 4; k8++) {
+				uint8_t *dst = pbuf + hf * TC_TILE_BYTES + (r >> 3) * 512 + k8 * 128 + (r & 7) * 16;
+				*reinterpret_cast<uint4 *>(dst) = make_uint4(ph[4 * k8], ph[4 * k8 + 1], ph[4 * k8 + 2], ph[4 * k8 + 3]);
+				*reinterpret_cast<uint4 *>(dst + 2 * TC_TILE_BYTES) = make_uint4(pm[4 * k8], pm[4 * k8 + 1], pm[4 * k8 + 2], pm[4 * k8 + 3]);
+				*reinterpret_cast<uint4 *>(dst + 4 * TC_TILE_BYTES) = make_uint4(pl[4 * k8], pl[4 * k8 + 1], pl[4 * k8 + 2], pl[4 * k8 + 3]);
+			}
+			// O = corr * O: this thread's half of the row's 256 columns
 			if (jt > 0 && !__all_sync(0xffffffffu, corr == 1.0f)) {
 #pragma unroll 1
-				for (int c8 = 0; c8 < 8; c8++) {
+				for (int c8 = 4 * hf; c8 < 4 * hf + 4; c8++) {
 					uint32_t ov[32];
 					tc_ld32(tmem_o + lane_base + uint32_t(32 * c8), ov);
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -292,10 +376,13 @@ __global__ void __launch_bounds__(AT_TC_THREADS, 1) attn_prefill_tc_kernel(AttnT
 		// ------------------------------------------------------------ epilogue: o = O / l
 		if (ok && at_wait(&o_bar, 0, a.err, fail)) {
 			tc_fence_after();
-			const float inv = row_ok ? 1.0f / l : 0.0f;  // (a visible key always exists: the query itself)
+			float l_other = 0.0f;  // (the partner is past its last read of slot 0: it arrived at p_bar, which o_bar follows)
+			const bool got = at_exchange(xm[0][r], xt[0][r], hf, l, 0x40000000, &l_other, a.err, fail);
+			const float lt = l + l_other;
+			const float inv = (row_ok && got) ? 1.0f / lt : 0.0f;  // (a visible key always exists: the query itself)
 			float *orow = a.o + (size_t(tile) * 128 + r) * 256;
 #pragma unroll 1
-			for (int c8 = 0; c8 < 8; c8++) {
+			for (int c8 = 4 * hf; c8 < 4 * hf + 4; c8++) {
 				uint32_t ov[32];
 				tc_ld32(tmem_o + lane_base + uint32_t(32 * c8), ov);
 				asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -319,7 +406,7 @@ __global__ void __launch_bounds__(AT_TC_THREADS, 1) attn_prefill_tc_kernel(AttnT
 		}
 		__syncthreads();
 	}
-	if (warp == 4) {
+	if (warp == 8) {
 		__syncwarp();
 		tc_fence_after();
 		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(512) : "memory");

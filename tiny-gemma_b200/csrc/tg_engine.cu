@@ -1542,10 +1542,10 @@ AttnTcPlan attn_tc_plan(int S) {
 	AttnTcPlan p;
 	p.q_tiles = (4 * S + TC_BM - 1) / TC_BM;
 	p.k_tiles = (S + TC_BM - 1) / TC_BM;
-	p.v_blocks = 2 * ((S + AT_TC_KT - 1) / AT_TC_KT);
+	p.v_blocks = 4 * ((S + AT_TC_KT - 1) / AT_TC_KT);  // 16 keys each
 	p.q_bytes = size_t(3) * p.q_tiles * 8 * TC_TILE_BYTES;
 	p.k_bytes = size_t(3) * p.k_tiles * 8 * TC_TILE_BYTES;
-	p.v_bytes = size_t(3) * p.v_blocks * 16384;
+	p.v_bytes = size_t(3) * p.v_blocks * AT_TC_VBYTES;
 	return p;
 }
 
@@ -1911,7 +1911,7 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 			};
 			pack_rows(q, at_q, 4 * S_seq, atp.q_tiles);  // rows = (query, head) pairs as they lie in q [S][4][256]
 			pack_rows(k, at_k, S_seq, atp.k_tiles);
-			launch_k(attn_pack_v_kernel, dim3(unsigned(std::min<size_t>((size_t(atp.v_blocks) * 1024 + 255) / 256, size_t(g_num_sms) * 16))), dim3(256), 0,
+			launch_k(attn_pack_v_kernel, dim3(unsigned(std::min<size_t>((size_t(atp.v_blocks) * 512 + 255) / 256, size_t(g_num_sms) * 16))), dim3(256), 0,
 			         st, (const float *)v, at_v, S_seq, atp.v_blocks);
 			count_launch();
 			AttnTcArgs aa{};
