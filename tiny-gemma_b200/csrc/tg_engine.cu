@@ -1834,9 +1834,9 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 		p += (tc.apack_bytes + 3) / 4;
 	}
 	// long prompts, one sequence per pass: attention on the tensor cores, from packed copies of q, k and v
-	// (from 1024 tokens on: below, the three packing launches cost what the tensor cores save)
+	// (from 640 tokens on: below, the three packing launches cost what the tensor cores save)
 	const bool attn_tc = use_tc && nb == 1 && S_seq > env_int("TG_ATTN_SMALL_MAX", 384) && env_int("TG_ATTN_TC", 1) &&
-	                     S_seq >= env_int("TG_ATTN_TC_MIN", 1024);
+	                     S_seq >= env_int("TG_ATTN_TC_MIN", 640);
 	const AttnTcPlan atp = attn_tc_plan(S_seq);
 	__nv_bfloat16 *at_q = nullptr, *at_k = nullptr, *at_v = nullptr;
 	if (attn_tc) {
