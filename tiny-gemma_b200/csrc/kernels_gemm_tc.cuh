@@ -91,6 +91,17 @@ __device__ __forceinline__ void tc_pack8(__nv_bfloat16 *out, size_t term_stride,
 	*reinterpret_cast<uint4 *>(out + 2 * term_stride + off) = *reinterpret_cast<const uint4 *>(lo);
 }
 
+// Work item c of a packing kernel -> (row, group of 8 consecutive k). Eight consecutive items are the eight rows
+// of a core matrix at the same k group, so that a warp's 16-byte stores fill whole 128-byte lines of the packed
+// tile (items in row-major order wrote every other 16 bytes of a line); each thread still reads 32 contiguous
+// bytes of its row (one sector).
+__device__ __forceinline__ void tc_chunk_to_row_k8(size_t c, int k8s, int &row, int &k8) {
+	const size_t g = c / (size_t(8) * k8s);          // group of 8 rows
+	const int w = int(c - g * (size_t(8) * k8s));    // item inside the group
+	row = int(g) * 8 + (w & 7);
+	k8 = w >> 3;
+}
+
 __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bfloat16 *out, int M, int K, int m_tiles) {
 	pdl_trigger();
 	pdl_wait();
@@ -98,7 +109,8 @@ __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bf
 	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);  // one thread per (row, 8 consecutive k)
 	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
 	for (size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += size_t(gridDim.x) * blockDim.x) {
-		const int row = int(c / (K / 8)), k8 = int(c % (K / 8));
+		int row, k8;
+		tc_chunk_to_row_k8(c, K / 8, row, k8);
 		float x[8];
 		if (row < M) {
 			const float4 a = *reinterpret_cast<const float4 *>(A + size_t(row) * K + 8 * k8);
@@ -218,7 +230,8 @@ __global__ void __launch_bounds__(256) geglu_pack_kernel(const float *gate, cons
 	const size_t n_chunks = size_t(m_tiles) * TC_BM * (K / 8);
 	const size_t term_stride = size_t(m_tiles) * k_blocks * (TC_TILE_BYTES / 2);
 	for (size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += size_t(gridDim.x) * blockDim.x) {
-		const int row = int(c / (K / 8)), k8 = int(c % (K / 8));
+		int row, k8;
+		tc_chunk_to_row_k8(c, K / 8, row, k8);
 		float x[8];
 		if (row < M && nsplit > 0) {
 			float4 u0 = make_float4(0.f, 0.f, 0.f, 0.f), u1 = u0, g0 = u0, g1 = u0;
