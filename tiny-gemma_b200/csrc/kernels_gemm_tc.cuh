@@ -127,18 +127,23 @@ __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bf
 // Residual + sandwich norms of one row, fused with the operand packing of the next GEMM:
 //   if t:  h += rmsnorm(t; w_post)            (reference modules.hpp: post-norm, then the residual add)
 //   if w_pre: pack( rmsnorm(h; w_pre) )       (the pre-norm of the following matmuls)
-// One CTA per row of the padded [m_tiles * 128] range (rows >= M are written as zeros). The sums run
-// over d = tid, tid + 256, ... exactly like rmsnorm_rows_kernel, so the values are the ones the
-// separate kernels produce. dim <= 2048, dim % 8 == 0.
+// One CTA of NT threads per row of the padded [m_tiles * 128] range (rows >= M are written as zeros). NT = 256:
+// the sums run over d = tid, tid + 256, ... exactly like rmsnorm_rows_kernel, so the values are the ones the
+// separate kernels produce. NT = 128 (thousands of rows): a row is a chain of dependent memory round trips and
+// barriers that no amount of threads shortens, so the SM holds twice as many rows in flight instead.
+// dim <= 2048, dim % 8 == 0.
 // The branch output t is either a finished [M][dim] matrix (nsplit == 0) or the raw K-split partial
 // sums of the GEMM that produced it: t[d] = tscale[d] * sum_sp tpart[(sp * M + row) * ldp + d], splits
 // added in ascending order as the reduce kernel does.
-__global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
+template <int NT>
+__global__ void __launch_bounds__(NT, NT == 128 ? 6 : 1) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
                                                             __nv_bfloat16 *out, int M, int dim, int m_tiles, int nsplit,
                                                             int ldp, const float *tscale) {
 	pdl_trigger();
 	pdl_wait();
-	__shared__ float bred[8];
+	constexpr int PER = 2048 / NT;         // values of a row per thread, at most
+	constexpr int QB = NT == 256 ? 9 : 3;  // splits requested together (registers: the narrow variant wants six CTAs per SM)
+	__shared__ float bred[NT / 32];
 	__shared__ float row_s[2048];
 	const int row = blockIdx.x, tid = threadIdx.x;
 	const int k_blocks = dim / TC_BK;
@@ -146,7 +151,7 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 	if (row >= M) {
 		if (w_pre) {
 			const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-			for (int k8 = tid; k8 < dim / 8; k8 += 256) tc_pack8(out, term_stride, k_blocks, row, k8, z);
+			for (int k8 = tid; k8 < dim / 8; k8 += NT) tc_pack8(out, term_stride, k_blocks, row, k8, z);
 		}
 		return;
 	}
@@ -158,26 +163,26 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 			// Thread tid owns d = tid, tid + 256, ... (at most 8 values). The partial sums of up to nine splits
 			// (the deepest split in use) for all of them are requested together: a row costs one L2 round
 			// trip, not nsplit * 8. The splits are added in ascending order.
-			float acc[8];
+			float acc[PER];
 #pragma unroll
-			for (int j = 0; j < 8; j++) acc[j] = 0.0f;
+			for (int j = 0; j < PER; j++) acc[j] = 0.0f;
 			const size_t sstride = size_t(M) * ldp;
 			const float *base = t + size_t(row) * ldp + tid;
-			for (int s0 = 0; s0 < nsplit; s0 += 9) {
-				float a[9][8];
+			for (int s0 = 0; s0 < nsplit; s0 += QB) {
+				float a[QB][PER];
 #pragma unroll
-				for (int q = 0; q < 9; q++)
+				for (int q = 0; q < QB; q++)
 #pragma unroll
-					for (int j = 0; j < 8; j++)
-						a[q][j] = (s0 + q < nsplit && tid + 256 * j < dim) ? base[size_t(s0 + q) * sstride + 256 * j] : 0.0f;
+					for (int j = 0; j < PER; j++)
+						a[q][j] = (s0 + q < nsplit && tid + NT * j < dim) ? base[size_t(s0 + q) * sstride + NT * j] : 0.0f;
 #pragma unroll
-				for (int q = 0; q < 9; q++)
+				for (int q = 0; q < QB; q++)
 #pragma unroll
-					for (int j = 0; j < 8; j++) acc[j] += a[q][j];
+					for (int j = 0; j < PER; j++) acc[j] += a[q][j];
 			}
 #pragma unroll
-			for (int j = 0; j < 8; j++) {
-				const int d = tid + 256 * j;
+			for (int j = 0; j < PER; j++) {
+				const int d = tid + NT * j;
 				if (d < dim) {
 					const float v = acc[j] * tscale[d];
 					t_s[d] = v;
@@ -185,33 +190,33 @@ __global__ void __launch_bounds__(256) resnorm_pack_kernel(float *h, const float
 				}
 			}
 		} else {
-			for (int d = tid; d < dim; d += 256) {
+			for (int d = tid; d < dim; d += NT) {
 				const float v = t[off + d];
 				t_s[d] = v;
 				ss = fmaf(v, v, ss);
 			}
 		}
-		ss = block_sum<8>(ss, bred);
+		ss = block_sum<NT / 32>(ss, bred);
 		const float r = inv_rms(ss, dim);
-		for (int d = tid; d < dim; d += 256) {
+		for (int d = tid; d < dim; d += NT) {
 			const float y = (t_s[d] * r) * (w_post[d] + 1.0f);
 			const float hn = h[off + d] + y;
 			h[off + d] = hn;
 			row_s[d] = hn;
 		}
 	} else {
-		for (int d = tid; d < dim; d += 256) row_s[d] = h[off + d];
+		for (int d = tid; d < dim; d += NT) row_s[d] = h[off + d];
 	}
 	if (!w_pre) return;
 	__syncthreads();
 	float ss = 0.0f;
-	for (int d = tid; d < dim; d += 256) {
+	for (int d = tid; d < dim; d += NT) {
 		const float v = row_s[d];
 		ss = fmaf(v, v, ss);
 	}
-	ss = block_sum<8>(ss, bred);
+	ss = block_sum<NT / 32>(ss, bred);
 	const float r = inv_rms(ss, dim);
-	for (int k8 = tid; k8 < dim / 8; k8 += 256) {
+	for (int k8 = tid; k8 < dim / 8; k8 += NT) {
 		float x[8];
 #pragma unroll
 		for (int i = 0; i < 8; i++) x[i] = (row_s[8 * k8 + i] * r) * (w_pre[8 * k8 + i] + 1.0f);

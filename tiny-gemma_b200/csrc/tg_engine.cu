@@ -1704,7 +1704,7 @@ int enqueue_decode_batched(tg_state *s, bool with_lm_head) {
 	const int m_tiles = (B + TC_BM - 1) / TC_BM;
 	// t: finished matrix (nsplit 0) or the raw partial sums of the GEMM before (nsplit >= 1, column scales tscale)
 	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre, int nsplit, const float *tscale) {
-		launch_k(resnorm_pack_kernel, dim3(m_tiles * TC_BM), dim3(256), 0, st, h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles, nsplit, D, tscale);
+		launch_k(resnorm_pack_kernel<256>, dim3(m_tiles * TC_BM), dim3(256), 0, st, h, t, w_post, w_pre, s->btc.apack, B, D, m_tiles, nsplit, D, tscale);
 		count_launch();
 	};
 	auto gemm_raw = [&](int ng, const QW *const *ws, int *ns) -> int {
@@ -1865,7 +1865,10 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 	// Tensor-core path: the norms are fused with the operand packing of the GEMM that follows them
 	// (resnorm_pack_kernel, geglu_pack_kernel), so a layer is 7 GEMMs (+ their split-K reduces) and 6 other launches.
 	auto resnorm_pack = [&](const float *t, const float *w_post, const float *w_pre, int nsplit, const float *tscale) {
-		launch_k(resnorm_pack_kernel, dim3(m_tiles * TC_BM), dim3(256), 0, st, h, t, w_post, w_pre, tc.apack, S, D, m_tiles, nsplit, D, tscale);
+		if (S >= env_int("TG_RESNORM_NARROW_MIN", 1024))
+			launch_k(resnorm_pack_kernel<128>, dim3(m_tiles * TC_BM), dim3(128), 0, st, h, t, w_post, w_pre, tc.apack, S, D, m_tiles, nsplit, D, tscale);
+		else
+			launch_k(resnorm_pack_kernel<256>, dim3(m_tiles * TC_BM), dim3(256), 0, st, h, t, w_post, w_pre, tc.apack, S, D, m_tiles, nsplit, D, tscale);
 		count_launch();
 	};
 	auto gemm_raw = [&](int ng, const QW *const *ws, int *ns) -> int {
