@@ -626,6 +626,25 @@ def test_prefill_attention_kernels_agree(capi, synth, weights_270m, S, monkeypat
     m.close()
 
 
+def test_grouped_long_prompts_use_the_same_attention(capi, synth, weights_270m):
+    """Four 700-token prompts prefilled together (stacked rows, the tensor-core attention kernel run once per
+    sequence from packed copies that are reused) against each prompt prefilled alone: the GEMMs see other row
+    counts (other tile shapes and K-splits), so the logits agree to rounding, not bit for bit."""
+    m = capi.Model("270m").load_file(weights_270m)
+    m.build_tables(1 << 20)
+    S = 700
+    prompts = np.stack([synth.random_prompt(S, 300 + i) for i in range(4)])
+    st4 = m.state(4, S + 16)
+    l4 = st4.prefill(prompts)
+    st4.close()
+    for i in range(4):
+        st1 = m.state(1, S + 16)
+        l1 = st1.prefill(prompts[i])[0]
+        assert rel_l2(l4[i], l1) <= 2e-5, i
+        st1.close()
+    m.close()
+
+
 def test_e2e_1b_vs_live_reference(capi, ref_or_none, weights_1b, synth):
     if ref_or_none is None:
         pytest.skip("needs oracle/_ref/libtgref.so")

@@ -1833,9 +1833,9 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 		tc.err = s->err_flag;
 		p += (tc.apack_bytes + 3) / 4;
 	}
-	// long prompts, one sequence per pass: attention on the tensor cores, from packed copies of q, k and v
+	// long prompts: attention on the tensor cores, from packed copies of q, k and v, one sequence after the other
 	// (from 640 tokens on: below, the three packing launches cost what the tensor cores save)
-	const bool attn_tc = use_tc && nb == 1 && S_seq > env_int("TG_ATTN_SMALL_MAX", 384) && env_int("TG_ATTN_TC", 1) &&
+	const bool attn_tc = use_tc && S_seq > env_int("TG_ATTN_SMALL_MAX", 384) && env_int("TG_ATTN_TC", 1) &&
 	                     S_seq >= env_int("TG_ATTN_TC_MIN", 640);
 	const AttnTcPlan atp = attn_tc_plan(S_seq);
 	__nv_bfloat16 *at_q = nullptr, *at_k = nullptr, *at_v = nullptr;
@@ -1912,16 +1912,18 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 				         256, tiles);
 				count_launch();
 			};
-			pack_rows(q, at_q, 4 * S_seq, atp.q_tiles);  // rows = (query, head) pairs as they lie in q [S][4][256]
-			pack_rows(k, at_k, S_seq, atp.k_tiles);
+			for (int i = 0; i < nb; i++) {  // (the packed copies are reused from sequence to sequence: stream order)
+			const float *qi = q + size_t(i) * S_seq * qd, *ki = k + size_t(i) * S_seq * kd, *vi = v + size_t(i) * S_seq * kd;
+			pack_rows(qi, at_q, 4 * S_seq, atp.q_tiles);  // rows = (query, head) pairs as they lie in q [S][4][256]
+			pack_rows(ki, at_k, S_seq, atp.k_tiles);
 			launch_k(attn_pack_v_kernel, dim3(unsigned(std::min<size_t>((size_t(atp.v_blocks) * 512 + 255) / 256, size_t(g_num_sms) * 16))), dim3(256), 0,
-			         st, (const float *)v, at_v, S_seq, atp.v_blocks);
+			         st, vi, at_v, S_seq, atp.v_blocks);
 			count_launch();
 			AttnTcArgs aa{};
 			aa.qp = at_q;
 			aa.kp = at_k;
 			aa.vp = at_v;
-			aa.o = ao;
+			aa.o = ao + size_t(i) * S_seq * qd;
 			aa.S = S_seq;
 			aa.q_tiles = atp.q_tiles;
 			aa.k_tiles = atp.k_tiles;
@@ -1930,6 +1932,8 @@ int enqueue_prefill_seq(tg_state *s, int b, int S_seq, int nb = 1) {
 			aa.window = c.n_pos_local;
 			aa.err = s->err_flag;
 			launch_k(attn_prefill_tc_kernel, dim3(atp.q_tiles), dim3(AT_TC_THREADS), size_t(AT_TC_SMEM), st, aa);
+			if (i + 1 < nb) count_launch();
+			}
 		} else
 			if (env_int("TG_ATTN_BLOCK4", 1)) {  // long prompts: four keys per step (TG_ATTN_BLOCK4=0: the per-key kernel)
 				static bool configured[TG_MAX_DEVICES] = {false};
