@@ -6,7 +6,7 @@
 // operand: row r of tile t is query 32 t + r / 4, head r % 4 — the rows of q [S][4][256] as they lie.
 // One CTA owns a row tile and walks its keys in tiles of 64:
 //     S = Q K_j^T                    M128 x N64, contraction over the 256 head dimensions
-//     online softmax on S            (running max m, sum l per row; one thread per row = one TMEM lane)
+//     online softmax on S            (max in use m and sum l per row; a row = one TMEM lane, two threads)
 //     O = corr * O + P V_j           M128 x N256, contraction over the 64 keys
 // fp32 accuracy on bf16 tensor cores as in the GEMM (kernels_gemm_tc.cuh): every fp32 operand is split into
 // three bf16 terms x = hi + mid + lo and a product a * b is the six term products whose weight reaches
