@@ -379,17 +379,16 @@ __global__ void __launch_bounds__(MV_THREADS) qmatvec_kernel(MvArgs a) {
 // (distributed shared memory), added in rank order: no partial-sum buffer, no tickets, no second launch,
 // the same bits on every run.
 // A column tile is 16 * TPR columns (TPR = 1, 2, 4 threads per row, 16 int8 each); thread t takes columns
-// 16 * (t % TPR) .. of rows t / TPR, t / TPR + 512 / TPR, ...; at most MVC_MAX_IT rows per thread.
-constexpr int MVC_THREADS = 512;
-constexpr int MVC_NWARPS = MVC_THREADS / 32;
+// 16 * (t % TPR) .. of rows t / TPR, t / TPR + threads / TPR, ...; at most MVC_MAX_IT rows per thread
+// (512 or 256 threads per CTA).
 constexpr int MVC_MAX_IT = 10;
 constexpr int MVC_MAX_CLUSTER = 8;
 
-template <int TPR>
+template <int TPR, int MVC_THREADS>
 __global__ void __launch_bounds__(MVC_THREADS, 1) qmatvec_cluster_kernel(float *y, const float *x, const int8_t *w, const float *scales,
                                                                          int K, int N, int kc) {
 	namespace cg = cooperative_groups;
-	constexpr int TN = 16 * TPR, ROWS = MVC_THREADS / TPR;
+	constexpr int TN = 16 * TPR, ROWS = MVC_THREADS / TPR, MVC_NWARPS = MVC_THREADS / 32;
 	cg::cluster_group cluster = cg::this_cluster();
 	__shared__ __align__(16) float red[MVC_NWARPS][TN];
 	__shared__ float part[MVC_MAX_CLUSTER][TN];  // (used in the cluster's first CTA)

@@ -295,13 +295,13 @@ constexpr int STEP_RANDF = 64;  // uniforms per sequence that fit the state's st
 // the device can hold at a time (a cluster needs its SMs inside one GPC) — and at most MVC_MAX_IT rows per
 // thread. Among those the plan with the most CTAs wins, then the smaller cluster, then the wider tile.
 struct MvcPlan {
-	int tpr = 0, ks = 0;
+	int tpr = 0, ks = 0, nt = 512;
 };
-template <int TPR>
+template <int TPR, int NT>
 int mvc_launch_t(float *y, const float *x, const int8_t *w, const float *scales, int K, int N, int ks, cudaStream_t st, int *max_clusters) {
 	cudaLaunchConfig_t cfg{};
 	cfg.gridDim = dim3(N / (16 * TPR), ks);
-	cfg.blockDim = dim3(MVC_THREADS);
+	cfg.blockDim = dim3(NT);
 	cfg.dynamicSmemBytes = 0;
 	cfg.stream = st;
 	cudaLaunchAttribute attr[1];
@@ -312,17 +312,22 @@ int mvc_launch_t(float *y, const float *x, const int8_t *w, const float *scales,
 	cfg.attrs = attr;
 	cfg.numAttrs = 1;
 	if (max_clusters) {  // query only
-		TG_CUDA(cudaOccupancyMaxActiveClusters(max_clusters, qmatvec_cluster_kernel<TPR>, &cfg));
+		TG_CUDA(cudaOccupancyMaxActiveClusters(max_clusters, qmatvec_cluster_kernel<TPR, NT>, &cfg));
 		return TG_OK;
 	}
-	TG_CUDA(cudaLaunchKernelEx(&cfg, qmatvec_cluster_kernel<TPR>, y, x, w, scales, K, N, K / ks));
+	TG_CUDA(cudaLaunchKernelEx(&cfg, qmatvec_cluster_kernel<TPR, NT>, y, x, w, scales, K, N, K / ks));
 	count_launch();
 	return check_launch("qmatvec_cluster");
 }
 int mvc_launch(MvcPlan p, float *y, const float *x, const int8_t *w, const float *scales, int K, int N, cudaStream_t st, int *max_clusters = nullptr) {
-	if (p.tpr == 1) return mvc_launch_t<1>(y, x, w, scales, K, N, p.ks, st, max_clusters);
-	if (p.tpr == 2) return mvc_launch_t<2>(y, x, w, scales, K, N, p.ks, st, max_clusters);
-	return mvc_launch_t<4>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+	if (p.nt == 256) {
+		if (p.tpr == 1) return mvc_launch_t<1, 256>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+		if (p.tpr == 2) return mvc_launch_t<2, 256>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+		return mvc_launch_t<4, 256>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+	}
+	if (p.tpr == 1) return mvc_launch_t<1, 512>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+	if (p.tpr == 2) return mvc_launch_t<2, 512>(y, x, w, scales, K, N, p.ks, st, max_clusters);
+	return mvc_launch_t<4, 512>(y, x, w, scales, K, N, p.ks, st, max_clusters);
 }
 MvcPlan mvc_plan(int K, int N, int dev) {
 	// clusters of each (tile width, size) the device holds at once: asked once per device
@@ -334,28 +339,34 @@ MvcPlan mvc_plan(int K, int N, int dev) {
 			for (int c = 0; c < 4; c++) {
 				int n = 0;
 				// (grid of one cluster: the answer does not depend on the grid)
-				if (mvc_launch(MvcPlan{1 << t, 1 << c}, nullptr, nullptr, nullptr, nullptr, 1 << c, 16 << t, nullptr, &n) != TG_OK) n = 0;
+				if (mvc_launch(MvcPlan{1 << t, 1 << c, 512}, nullptr, nullptr, nullptr, nullptr, 1 << c, 16 << t, nullptr, &n) != TG_OK) n = 0;
 				max_active[slot][t][c] = n;
 			}
 		asked[slot] = true;
 	}
-	const int want_tpr = env_int("TG_MVC_TPR", 0), want_ks = env_int("TG_MVC_KS", 0);  // (experiments: fix the plan)
+	const int want_tpr = env_int("TG_MVC_TPR", 0), want_ks = env_int("TG_MVC_KS", 0), want_nt = env_int("TG_MVC_NT", 0);  // (experiments: fix the plan)
+	// CTAs of 256 threads where a plan exists with them (the small matrices: 3.5 - 4.2 us against 4.1 - 5.0 with 512:
+	// half the warps to launch and to reduce over); 512 threads reach K-slices of up to 1280 rows per 16 columns
 	MvcPlan best;
-	int best_ctas = 0;
-	for (int c = 0; c < 4; c++)          // smaller clusters first
-		for (int t = 2; t >= 0; t--) {   // wider tiles first
-			const int tpr = 1 << t, ks = 1 << c, tn = 16 * tpr;
-			if (want_tpr && tpr != want_tpr) continue;
-			if (want_ks && ks != want_ks) continue;
-			if (N % tn != 0 || K % ks != 0) continue;
-			const int tiles = N / tn, kc = K / ks;
-			if (kc > MVC_MAX_IT * (MVC_THREADS / tpr)) continue;
-			if (tiles * ks > g_num_sms || tiles > max_active[slot][t][c]) continue;
-			if (tiles * ks > best_ctas) {
-				best_ctas = tiles * ks;
-				best = MvcPlan{tpr, ks};
+	for (int nt : {256, 512}) {
+		if (want_nt && nt != want_nt) continue;
+		int best_ctas = 0;
+		for (int c = 0; c < 4; c++)          // smaller clusters first
+			for (int t = 2; t >= 0; t--) {   // wider tiles first
+				const int tpr = 1 << t, ks = 1 << c, tn = 16 * tpr;
+				if (want_tpr && tpr != want_tpr) continue;
+				if (want_ks && ks != want_ks) continue;
+				if (N % tn != 0 || K % ks != 0) continue;
+				const int tiles = N / tn, kc = K / ks;
+				if (kc > MVC_MAX_IT * (nt / tpr)) continue;
+				if (tiles * ks > g_num_sms || tiles > max_active[slot][t][c]) continue;  // (the table was asked for 512 threads)
+				if (tiles * ks > best_ctas) {
+					best_ctas = tiles * ks;
+					best = MvcPlan{tpr, ks, nt};
+				}
 			}
-		}
+		if (best.ks) break;
+	}
 	return best;
 }
 
