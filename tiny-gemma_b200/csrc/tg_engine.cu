@@ -331,17 +331,18 @@ int mvc_launch(MvcPlan p, float *y, const float *x, const int8_t *w, const float
 }
 MvcPlan mvc_plan(int K, int N, int dev) {
 	// clusters of each (tile width, size) the device holds at once: asked once per device
-	static int max_active[TG_MAX_DEVICES][3][4];
+	static int max_active[TG_MAX_DEVICES][2][3][4];  // [256 / 512 threads][tile width][cluster size]
 	static bool asked[TG_MAX_DEVICES] = {false};
 	const int slot = (dev >= 0 && dev < TG_MAX_DEVICES) ? dev : 0;
 	if (!asked[slot]) {
-		for (int t = 0; t < 3; t++)
-			for (int c = 0; c < 4; c++) {
-				int n = 0;
-				// (grid of one cluster: the answer does not depend on the grid)
-				if (mvc_launch(MvcPlan{1 << t, 1 << c, 512}, nullptr, nullptr, nullptr, nullptr, 1 << c, 16 << t, nullptr, &n) != TG_OK) n = 0;
-				max_active[slot][t][c] = n;
-			}
+		for (int h = 0; h < 2; h++)
+			for (int t = 0; t < 3; t++)
+				for (int c = 0; c < 4; c++) {
+					int n = 0;
+					// (grid of one cluster: the answer does not depend on the grid)
+					if (mvc_launch(MvcPlan{1 << t, 1 << c, h ? 512 : 256}, nullptr, nullptr, nullptr, nullptr, 1 << c, 16 << t, nullptr, &n) != TG_OK) n = 0;
+					max_active[slot][h][t][c] = n;
+				}
 		asked[slot] = true;
 	}
 	const int want_tpr = env_int("TG_MVC_TPR", 0), want_ks = env_int("TG_MVC_KS", 0), want_nt = env_int("TG_MVC_NT", 0);  // (experiments: fix the plan)
@@ -359,7 +360,9 @@ MvcPlan mvc_plan(int K, int N, int dev) {
 				if (N % tn != 0 || K % ks != 0) continue;
 				const int tiles = N / tn, kc = K / ks;
 				if (kc > MVC_MAX_IT * (nt / tpr)) continue;
-				if (tiles * ks > g_num_sms || tiles > max_active[slot][t][c]) continue;  // (the table was asked for 512 threads)
+				// (one CTA per SM: 256-thread CTAs fit three to an SM, but two resident waves of them measured slower on
+				// five of the six layer shapes; TG_MVC_WAVES=2 allows them)
+				if (tiles * ks > (nt == 256 ? env_int("TG_MVC_WAVES", 1) : 1) * g_num_sms || tiles > max_active[slot][nt == 512][t][c]) continue;
 				if (tiles * ks > best_ctas) {
 					best_ctas = tiles * ks;
 					best = MvcPlan{tpr, ks, nt};
