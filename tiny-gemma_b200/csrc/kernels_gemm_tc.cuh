@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) split_pack_kernel(const float *A, __nv_bf
 // sums of the GEMM that produced it: t[d] = tscale[d] * sum_sp tpart[(sp * M + row) * ldp + d], splits
 // added in ascending order as the reduce kernel does.
 template <int NT>
-__global__ void __launch_bounds__(NT, NT == 128 ? 6 : 1) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
+__global__ void __launch_bounds__(NT, NT == 128 ? 6 : 2) resnorm_pack_kernel(float *h, const float *t, const float *w_post, const float *w_pre,
                                                             __nv_bfloat16 *out, int M, int dim, int m_tiles, int nsplit,
                                                             int ldp, const float *tscale) {
 	pdl_trigger();
@@ -156,6 +156,28 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 6 : 1) resnorm_pack_kernel(flo
 		return;
 	}
 	const size_t off = size_t(row) * dim;
+	// The wide variant serves a few hundred rows, all resident at once: a row's time is its chain of dependent
+	// memory round trips. Everything that does not depend on the partial sums (residual stream, norm weights,
+	// column scales) is requested before them, not after the barriers that follow.
+	constexpr bool PRE = NT == 256;
+	float hv[PER], wp[PER], ts[PER];
+	float4 wq0 = make_float4(0.f, 0.f, 0.f, 0.f), wq1 = wq0;
+	if (PRE && t && nsplit > 0) {
+#pragma unroll
+		for (int j = 0; j < PER; j++) {
+			const int d = tid + NT * j;
+			hv[j] = wp[j] = ts[j] = 0.0f;
+			if (d < dim) {
+				hv[j] = h[off + d];
+				wp[j] = w_post[d];
+				ts[j] = tscale[d];
+			}
+		}
+		if (w_pre && tid < dim / 8) {
+			wq0 = *reinterpret_cast<const float4 *>(w_pre + 8 * tid);
+			wq1 = *reinterpret_cast<const float4 *>(w_pre + 8 * tid + 4);
+		}
+	}
 	if (t) {
 		__shared__ float t_s[2048];
 		float ss = 0.0f;
@@ -184,7 +206,7 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 6 : 1) resnorm_pack_kernel(flo
 			for (int j = 0; j < PER; j++) {
 				const int d = tid + NT * j;
 				if (d < dim) {
-					const float v = acc[j] * tscale[d];
+					const float v = acc[j] * (PRE ? ts[j] : tscale[d]);
 					t_s[d] = v;
 					ss = fmaf(v, v, ss);
 				}
@@ -198,11 +220,24 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 6 : 1) resnorm_pack_kernel(flo
 		}
 		ss = block_sum<NT / 32>(ss, bred);
 		const float r = inv_rms(ss, dim);
-		for (int d = tid; d < dim; d += NT) {
-			const float y = (t_s[d] * r) * (w_post[d] + 1.0f);
-			const float hn = h[off + d] + y;
-			h[off + d] = hn;
-			row_s[d] = hn;
+		if (PRE && nsplit > 0) {
+#pragma unroll
+			for (int j = 0; j < PER; j++) {
+				const int d = tid + NT * j;
+				if (d < dim) {
+					const float y = (t_s[d] * r) * (wp[j] + 1.0f);
+					const float hn = hv[j] + y;
+					h[off + d] = hn;
+					row_s[d] = hn;
+				}
+			}
+		} else {
+			for (int d = tid; d < dim; d += NT) {
+				const float y = (t_s[d] * r) * (w_post[d] + 1.0f);
+				const float hn = h[off + d] + y;
+				h[off + d] = hn;
+				row_s[d] = hn;
+			}
 		}
 	} else {
 		for (int d = tid; d < dim; d += NT) row_s[d] = h[off + d];
@@ -216,6 +251,16 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 6 : 1) resnorm_pack_kernel(flo
 	}
 	ss = block_sum<NT / 32>(ss, bred);
 	const float r = inv_rms(ss, dim);
+	if (PRE && t && nsplit > 0) {  // (dim / 8 <= 256: one group of eight per thread, its weights already here)
+		if (tid < dim / 8) {
+			const float wq[8] = {wq0.x, wq0.y, wq0.z, wq0.w, wq1.x, wq1.y, wq1.z, wq1.w};
+			float x[8];
+#pragma unroll
+			for (int i = 0; i < 8; i++) x[i] = (row_s[8 * tid + i] * r) * (wq[i] + 1.0f);
+			tc_pack8(out, term_stride, k_blocks, row, tid, x);
+		}
+		return;
+	}
 	for (int k8 = tid; k8 < dim / 8; k8 += NT) {
 		float x[8];
 #pragma unroll
