@@ -115,7 +115,12 @@ int tg_state_position(tg_state *s, int b, int *position);
 /* gemma::forward_prefill, transformer.hpp:49-73. ids_host is [batch, n_tokens]
  * row-major; every sequence of the batch has the same prompt length. Needs
  * empty caches (decode.hpp:78-79) else TG_ESTATE. logits_host may be NULL;
- * otherwise receives [batch, n_vocab] fp32 for the last prompt position. */
+ * otherwise receives [batch, n_vocab] fp32 for the last prompt position.
+ * Batches of 4 and more are prefilled together (their rows stacked, up to 16384
+ * rows per pass): a sequence's logits then agree with those of a
+ * single-sequence state to rounding (the GEMMs tile and split other row counts
+ * differently), not bit for bit; batches below 4 are prefilled one sequence
+ * per pass and are bit-identical to it. */
 int tg_prefill(tg_state *s, const int *ids_host, int n_tokens, float *logits_host);
 
 /* gemma::forward_decode, transformer.hpp:75-97: one token per sequence.
